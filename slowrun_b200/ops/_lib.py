@@ -1,0 +1,91 @@
+"""ctypes loader for the in-tree sm_100a kernel library (`slowrun_b200/_kernels.so`).
+
+The kernels are launched through `extern "C"` entry points that take raw device pointers and a CUDA stream, so
+no torch C++ extension is involved. On a machine with a GPU the library is mandatory: ops raise if it is missing
+rather than silently running a PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_SO = os.path.join(_PKG, "_kernels.so")
+_lock = threading.Lock()
+_lib = None
+_status = {}
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel abandoned a bounded wait and reported it through its status word."""
+
+
+def library_path() -> str:
+    return _SO
+
+
+def available() -> bool:
+    """True when CUDA kernels can run here (a GPU is present)."""
+    return torch.cuda.is_available()
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(_SO):
+                from ..csrc import build as _build
+                _build.build()
+            _lib = ctypes.CDLL(_SO)
+    return _lib
+
+
+def fn(name: str, argtypes, restype=c_int):
+    f = getattr(lib(), name)
+    if f.argtypes is None:
+        f.argtypes = argtypes
+        f.restype = restype
+    return f
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def status_buffer(device=None) -> torch.Tensor:
+    """int32[4] device buffer shared by every kernel launched from this process on `device`."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    buf = _status.get(key)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=dev)
+        _status[key] = buf
+    return buf
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Synchronising check of the status word; raises KernelStatusError if any kernel gave up a wait."""
+    buf = status_buffer(device)
+    vals = buf.tolist()
+    if vals[0] != 0:
+        if reset:
+            buf.zero_()
+        raise KernelStatusError(
+            f"kernel status: code={vals[0]} site={vals[1]} block={vals[2]} detail={vals[3]} "
+            "(1 = mbarrier wait ran out, 2 = peer wait ran out, 3 = bad argument)")
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what}: launcher returned {rc}")

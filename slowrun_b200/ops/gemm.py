@@ -1,0 +1,112 @@
+"""Python face of the tcgen05 bf16 GEMM (`csrc/gemm_tcgen05.cu`) plus its plain-PyTorch reference.
+
+`gemm()` computes ``out[b] = alpha * op(A[b]) @ op(B[b]).T + beta * cin[b]`` with A an (M x K) operand and B an
+(N x K) operand. Each operand is given as stored: ``a_mn=False`` means the tensor is [.., M, K] (K contiguous),
+``a_mn=True`` means it is [.., K, M] (M contiguous). The reference reaches cuBLAS for the same products through
+F.linear / torch.bmm (train.py:286-323, 614-621).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_ARGTYPES = [
+    _lib.c_void_p, _lib.c_void_p, _lib.c_void_p, _lib.c_void_p,  # A B C Cin
+    _lib.c_int, _lib.c_int, _lib.c_int, _lib.c_int,  # M N K batch
+    _lib.c_ll, _lib.c_ll, _lib.c_ll, _lib.c_ll,  # lda ldb ldc ldcin
+    _lib.c_ll, _lib.c_ll, _lib.c_ll, _lib.c_ll,  # strides
+    _lib.c_int, _lib.c_int, _lib.c_int, _lib.c_int,  # a_mn b_mn c_fp32 cin_fp32
+    _lib.c_float, _lib.c_float, _lib.c_int, _lib.c_int, _lib.c_int,  # alpha beta sym bn max_ctas
+    _lib.c_void_p, _lib.c_void_p,  # status stream
+]
+
+
+def _as3d(t: torch.Tensor):
+    if t.dim() == 2:
+        return t.unsqueeze(0)
+    if t.dim() == 3:
+        return t
+    raise ValueError(f"expected a 2-D or 3-D tensor, got {tuple(t.shape)}")
+
+
+def _check_operand(t: torch.Tensor, name: str):
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name} must have a contiguous last dimension")
+
+
+def gemm_reference(a, b, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, out_dtype=torch.bfloat16):
+    """fp32 PyTorch statement of `gemm` (the numerics oracle; runs on CPU or GPU)."""
+    A = _as3d(a).float()
+    B = _as3d(b).float()
+    if a_mn:
+        A = A.transpose(-1, -2)
+    if b_mn:
+        B = B.transpose(-1, -2)
+    out = alpha * torch.matmul(A, B.transpose(-1, -2))
+    if cin is not None:
+        out = out + beta * _as3d(cin).float()
+    out = out.to(out_dtype)
+    return out if a.dim() == 3 else out[0]
+
+
+def gemm(a, b, out=None, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, sym=False,
+         out_dtype=torch.bfloat16, bn=0, max_ctas=0):
+    """Launch the tcgen05 GEMM on the current stream. See the module docstring for operand conventions."""
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    A, B = _as3d(a), _as3d(b)
+    batch = A.shape[0]
+    if a_mn:
+        K, M = A.shape[1], A.shape[2]
+    else:
+        M, K = A.shape[1], A.shape[2]
+    if b_mn:
+        Kb, N = B.shape[1], B.shape[2]
+    else:
+        N, Kb = B.shape[1], B.shape[2]
+    if Kb != K or B.shape[0] != batch:
+        raise ValueError(f"shape mismatch: A {tuple(a.shape)} (a_mn={a_mn}) vs B {tuple(b.shape)} (b_mn={b_mn})")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+        if a.dim() == 2:
+            out = out[0]
+    O = _as3d(out)
+    if O.shape != (batch, M, N) or O.stride(-1) != 1:
+        raise ValueError(f"bad output shape/stride {tuple(out.shape)}")
+    if O.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("output must be bfloat16 or float32")
+    CI = None
+    if cin is not None:
+        CI = _as3d(cin)
+        if CI.shape != (batch, M, N) or CI.stride(-1) != 1 or CI.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("bad cin")
+    f = _lib.fn("sr_gemm_bf16", _ARGTYPES)
+    rc = f(A.data_ptr(), B.data_ptr(), O.data_ptr(), _lib.ptr(CI), M, N, K, batch,
+           A.stride(1), B.stride(1), O.stride(1), CI.stride(1) if CI is not None else 0,
+           A.stride(0), B.stride(0), O.stride(0), CI.stride(0) if CI is not None else 0,
+           int(a_mn), int(b_mn), int(O.dtype == torch.float32),
+           int(CI is not None and CI.dtype == torch.float32),
+           float(alpha), float(beta), int(sym), int(bn), int(max_ctas),
+           _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "sr_gemm_bf16")
+    return out
+
+
+def mm_nt(x, w, **kw):
+    """x[M,K] @ w[N,K].T"""
+    return gemm(x, w, **kw)
+
+
+def mm_nn(x, w, **kw):
+    """x[M,K] @ w[K,N]"""
+    return gemm(x, w, b_mn=True, **kw)
+
+
+def mm_tn(x, y, **kw):
+    """x[K,M].T @ y[K,N]"""
+    return gemm(x, y, a_mn=True, b_mn=True, **kw)
