@@ -48,6 +48,7 @@ class ModelConfig:
     lm_head_transposed: bool = False  # tiny stores lm_head as (n_embd, vocab) bf16
     resid_lambda_init: float = 1.0
     cproj_zero_init: bool = False
+    attn_gate_adamw: bool = False     # tiny steps attn_gate with AdamW; the other tracks hand it to Muon
     fp8_lm_head: bool = False         # e4m3 forward / e5m2 gradient lm-head GEMMs (tiny training path)
     mlp_hidden: Optional[int] = None  # override; default 256*ceil((8d/3)/256)
     label_smoothing: float = 0.0      # unlimited
@@ -179,7 +180,8 @@ def track_defaults(track: str) -> TrainConfig:
         m = ModelConfig(n_layer=16, n_head=8, n_kv_head=8, n_embd=1024, dropout=0.1, mlp_dropout=False,
                         stoch_depth=0.0, use_iha=False, iha_mix_v=False, logit_cap=15.0, mtp_weight=0.0,
                         xsa_mode="all", key_offset=True, rope_truncate=True, num_iterations=2, fused_mtp=True,
-                        lm_head_transposed=True, resid_lambda_init=1.1, cproj_zero_init=True, fp8_lm_head=True)
+                        lm_head_transposed=True, resid_lambda_init=1.1, cproj_zero_init=True, fp8_lm_head=True,
+                        attn_gate_adamw=True)
         return TrainConfig(track="tiny", model=m, device_batch_size=32, num_epochs=15, scalar_lr=0.25,
                            unembedding_lr=0.001, lr_multiplier=0.8, weight_decay=0.8, warmdown_ratio=0.4,
                            warmdown_power=1.0, swa_last_epochs=4, logit_avg=0, dupe_start_epoch=10 ** 9)

@@ -46,6 +46,7 @@ struct GemmParams {
   long long ldcin, strideCin;
   int cin_fp32;
   float alpha, beta;
+  const float* alpha_ptr;  // optional device scalar multiplied into alpha
   int sym;
   int* status;
 };
@@ -221,6 +222,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       ok = mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, 300);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM loads
       if (!ok) break;
+      const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
       tc_fence_after();
       const int r = mi * BM + q * 32 + lane;
       const bool row_ok = r < p.M;
@@ -237,7 +239,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (row_ok && c0 < p.N) {
           float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = p.alpha * __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j) f[j] = alpha * __uint_as_float(v[j]);
           const bool full = (c0 + 32 <= p.N);
           if (cinbase) {
             if (p.cin_fp32) {
@@ -401,14 +403,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int max_
 // out[b] = alpha * op(A[b]) op(B[b])^T + beta * Cin[b]; see the file header.
 //   a_mn / b_mn : 0 = operand stored [rows, K] (K contiguous), 1 = stored [K, rows] (rows contiguous)
 //   lda / ldb   : leading dimension (elements) of the stored 2-D array; stride* : per-batch element stride
+//   alpha_ptr   : optional device fp32 scalar; the product is scaled by alpha * (*alpha_ptr)
 //   bn          : N tile (128 or 256), 0 = choose
 //   status      : device int[4]; written only when a bounded wait ran out (see sm100_common.cuh)
 // Returns 0 on successful launch, negative on bad arguments / launch failure.
 extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                             long long lda, long long ldb, long long ldc, long long ldcin, long long strideA,
                             long long strideB, long long strideC, long long strideCin, int a_mn, int b_mn,
-                            int c_fp32, int cin_fp32, float alpha, float beta, int sym, int bn, int max_ctas,
-                            int* status, cudaStream_t stream) {
+                            int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr, int sym,
+                            int bn, int max_ctas, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if (sym && M != N) return -6;
   GemmParams p{};
@@ -416,7 +419,7 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.C = C; p.ldc = ldc; p.strideC = strideC; p.c_fp32 = c_fp32;
   p.Cin = Cin; p.ldcin = ldcin; p.strideCin = strideCin; p.cin_fp32 = cin_fp32;
-  p.alpha = alpha; p.beta = beta; p.sym = sym; p.status = status;
+  p.alpha = alpha; p.beta = beta; p.alpha_ptr = alpha_ptr; p.sym = sym; p.status = status;
   if (bn == 0) {
     // prefer the 256-wide tile unless it leaves most of a wave idle
     const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256) * batch;

@@ -19,7 +19,7 @@ _ARGTYPES = [
     _lib.c_ll, _lib.c_ll, _lib.c_ll, _lib.c_ll,  # lda ldb ldc ldcin
     _lib.c_ll, _lib.c_ll, _lib.c_ll, _lib.c_ll,  # strides
     _lib.c_int, _lib.c_int, _lib.c_int, _lib.c_int,  # a_mn b_mn c_fp32 cin_fp32
-    _lib.c_float, _lib.c_float, _lib.c_int, _lib.c_int, _lib.c_int,  # alpha beta sym bn max_ctas
+    _lib.c_float, _lib.c_float, _lib.c_void_p, _lib.c_int, _lib.c_int, _lib.c_int,  # alpha beta alpha_ptr sym bn max_ctas
     _lib.c_void_p, _lib.c_void_p,  # status stream
 ]
 
@@ -54,9 +54,13 @@ def gemm_reference(a, b, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.
     return out if a.dim() == 3 else out[0]
 
 
-def gemm(a, b, out=None, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, sym=False,
+def gemm(a, b, out=None, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, alpha_t=None, sym=False,
          out_dtype=torch.bfloat16, bn=0, max_ctas=0):
-    """Launch the tcgen05 GEMM on the current stream. See the module docstring for operand conventions."""
+    """Launch the tcgen05 GEMM on the current stream. See the module docstring for operand conventions.
+
+    `alpha_t` is an optional 0-dim fp32 CUDA tensor multiplied into alpha on the device (no host sync)."""
+    if alpha_t is not None and (alpha_t.dtype != torch.float32 or not alpha_t.is_cuda):
+        raise TypeError("alpha_t must be a float32 CUDA tensor")
     _check_operand(a, "a")
     _check_operand(b, "b")
     A, B = _as3d(a), _as3d(b)
@@ -91,7 +95,7 @@ def gemm(a, b, out=None, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.
            A.stride(0), B.stride(0), O.stride(0), CI.stride(0) if CI is not None else 0,
            int(a_mn), int(b_mn), int(O.dtype == torch.float32),
            int(CI is not None and CI.dtype == torch.float32),
-           float(alpha), float(beta), int(sym), int(bn), int(max_ctas),
+           float(alpha), float(beta), _lib.ptr(alpha_t), int(sym), int(bn), int(max_ctas),
            _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "sr_gemm_bf16")
     return out

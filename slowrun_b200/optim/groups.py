@@ -1,0 +1,72 @@
+"""Parameter grouping: which parameters Muon orthogonalises, which AdamW steps, with which learning rates.
+
+Same membership, order and hyper-parameters as the reference's `setup_optimizer` (limited: train.py:461-512,
+tiny: tiny/train.py:627-664). Muon groups are one per distinct matrix shape, in sorted shape order, members in
+module registration order — the order also fixes which rank owns which matrix.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..config import TrainConfig
+
+
+def _iha_params(model):
+    out = []
+    for block in model.all_blocks():
+        a = block.attn
+        if a.use_iha:
+            out += [a.q_mix, a.k_mix]
+            if a.iha_mix_v:
+                out.append(a.v_mix)
+    return out
+
+
+def muon_matrix_params(model) -> List[torch.nn.Parameter]:
+    """Every parameter that the reference hands to Muon, in its order."""
+    if model.config.attn_gate_adamw:
+        gate_ids = {id(b.attn.attn_gate.weight) for b in model.transformer.h}
+        ps = list(model.transformer.h.parameters()) + list(model.ve_projs.parameters())
+        return [p for p in ps if id(p) not in gate_ids]
+    iha_ids = {id(p) for p in _iha_params(model)}
+    ps = [p for p in model.transformer.h.parameters() if id(p) not in iha_ids] + list(model.ve_projs.parameters())
+    if model.mtp_weight > 0:
+        ps += [p for p in list(model.mtp_block.parameters()) + list(model.mtp_proj.parameters()) if id(p) not in iha_ids]
+    return ps
+
+
+def muon_shape_groups(model):
+    ps = muon_matrix_params(model)
+    return [(shape, [p for p in ps if p.shape == shape]) for shape in sorted({p.shape for p in ps})]
+
+
+def build_param_groups(model, cfg: TrainConfig):
+    lrs = cfg.lrs
+    wd = cfg.weight_decay
+    betas = tuple(cfg.adam_betas)
+    A = dict(kind="adamw", eps=1e-10)
+    groups = [
+        dict(A, name="lm_head", params=[model.lm_head.weight], lr=lrs["unembedding"], betas=betas, weight_decay=wd),
+        dict(A, name="wte", params=list(model.transformer.wte.parameters()), lr=lrs["embedding"], betas=betas, weight_decay=wd),
+        dict(A, name="resid", params=[model.resid_lambdas], lr=lrs["scalar"] * 0.01, betas=betas, weight_decay=0.0),
+        dict(A, name="x0", params=[model.x0_lambdas], lr=lrs["scalar"], betas=(0.96, 0.95), weight_decay=0.0),
+        dict(A, name="skip", params=[model.skip_weights], lr=lrs["scalar"] * 0.01, betas=betas, weight_decay=0.0),
+    ]
+    if model.config.attn_gate_adamw:
+        gates = [b.attn.attn_gate.weight for b in model.transformer.h]
+        groups.append(dict(A, name="attn_gate", params=gates, lr=lrs["scalar"], betas=(0.9, 0.99), weight_decay=0.0))
+        if model.config.xsa_mode != "off":
+            groups.append(dict(A, name="xsa", params=[model.xsa_alphas], lr=lrs["scalar"], betas=(0.9, 0.95), weight_decay=0.0))
+    else:
+        iha = _iha_params(model)
+        if iha:
+            groups.append(dict(A, name="iha", params=iha, lr=cfg.iha_lr, betas=betas, weight_decay=0.0))
+    for shape, ps in muon_shape_groups(model):
+        groups.append(dict(kind="muon", name=f"muon{tuple(shape)}", params=ps, lr=lrs["matrix"], momentum=cfg.muon_momentum,
+                           ns_steps=cfg.ns_steps, beta2=0.95, weight_decay=wd))
+    for g in groups:
+        g["initial_lr"] = g["lr"]
+        g["initial_wd"] = g["weight_decay"]
+    return groups

@@ -1,0 +1,371 @@
+"""Sharded Muon + AdamW (optimizer state and update work split over data-parallel ranks).
+
+Update rule and hyper-parameter plumbing follow the reference's DistMuonAdamW (train.py:594-760): Nesterov momentum,
+MuonEq-R row normalisation, five "Polar Express" Newton-Schulz iterations in bf16, NorMuon variance reduction and
+cautious weight decay for matrices; AdamW (decay first, bias-corrected) for embeddings, head and scalars.
+
+What is organised differently:
+  * gradients, parameters and bf16 shadows live in stacked arenas (`arena.py`), so reduce-scatter inputs and the
+    owned stacks are slices, never copies;
+  * the Newton-Schulz products run on the tcgen05 GEMM with symmetric-output tiles (X X^T and bA + cA^2 only compute
+    the upper triangle) and the polynomial/axpy terms fused into the GEMM epilogue;
+  * what is all-gathered is the bf16 orthogonalised update, applied by every rank to its own replica
+    (`P -= lr*U + lr*wd*P*[U*P >= 0]`), instead of the updated fp32 parameters: half the bytes, and no padding
+    traffic for one-matrix groups beyond the zero chunk;
+  * all small parameters share one gradient buffer and one all-reduce.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..ops import _lib
+from ..ops.gemm import gemm
+from .arena import ParamArena, SMALL_NUMEL
+
+# Polar Express coefficients (train.py:586-592)
+POLAR_EXPRESS_COEFFS = [
+    (8.156554524902461, -22.48329292557795, 15.878769915207462),
+    (4.042929935166739, -2.808917465908714, 0.5000178451051316),
+    (3.8916678022926607, -2.772484153217685, 0.5060648178503393),
+    (3.285753657755655, -2.3681294933425376, 0.46449024233003106),
+    (2.3465413258596377, -1.7097828382687081, 0.42323551169305323),
+]
+
+c_void_p, c_int, c_long, c_float = _lib.c_void_p, _lib.c_int, _lib.ctypes.c_long, _lib.c_float
+
+
+def _bf16(x: float) -> float:
+    return float(torch.tensor(x, dtype=torch.float32).to(torch.bfloat16).float())
+
+
+# ----------------------------------------------------------------------------- plain-PyTorch statements (oracle / CPU path)
+def newton_schulz_ref(X: torch.Tensor, ns_steps: int) -> torch.Tensor:
+    """X: [n, r, c] bf16 (already Frobenius-normalised). Returns the orthogonalised stack in bf16."""
+    if X.size(-2) > X.size(-1):
+        for a, b, c in POLAR_EXPRESS_COEFFS[:ns_steps]:
+            A = X.mT @ X
+            X = a * X + X @ (b * A + c * (A @ A))
+    else:
+        for a, b, c in POLAR_EXPRESS_COEFFS[:ns_steps]:
+            A = X @ X.mT
+            X = a * X + (b * A + c * (A @ A)) @ X
+    return X
+
+
+def muon_update_ref(G, M, S, momentum, beta2, ns_steps):
+    """Reference math of train.py:603-634 up to the variance-reduced update U (bf16). Updates M and S in place.
+    G: [n, r, c] fp32 averaged gradient (consumed), M: momentum, S: second moment ([n,r,1] or [n,1,c])."""
+    M.lerp_(G, 1 - momentum)
+    g = G.lerp_(M, momentum)
+    g = g / g.float().norm(dim=-1, keepdim=True).clamp_min(1e-7)
+    X = g.bfloat16()
+    X = X / (X.float().norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6).to(X.dtype)
+    X = newton_schulz_ref(X, ns_steps)
+    red_dim = -1 if G.size(-2) >= G.size(-1) else -2
+    v_mean = X.float().square().mean(dim=red_dim, keepdim=True)
+    red = X.size(red_dim)
+    v_norm = (v_mean.sum(dim=(-2, -1), keepdim=True) * red).sqrt()
+    S.lerp_(v_mean.to(S.dtype), 1 - beta2)
+    step = S.clamp_min(1e-10).rsqrt()
+    v_norm_new = ((v_mean * red) * step.float().square()).sum(dim=(-2, -1), keepdim=True).sqrt()
+    final_scale = step * (v_norm / v_norm_new.clamp_min(1e-10))
+    return X * final_scale.to(X.dtype)
+
+
+def muon_apply_ref(P, U, lr_eff, wd):
+    """Cautious weight decay + apply (train.py:635-639); lr and wd are rounded to bf16 as in the reference."""
+    lr_b = _bf16(lr_eff)
+    lrwd_b = _bf16(lr_b * _bf16(wd))
+    g = U.float()
+    upd = (lr_b * U).float() if U.dtype == torch.bfloat16 else (lr_b * g).bfloat16().float()
+    mask = (g * P) >= 0
+    P.sub_(upd + lrwd_b * P * mask)
+
+
+def adamw_ref(p, grad, m, v, step, lr, b1, b2, eps, wd):
+    """train.py:594-601"""
+    p.mul_(1 - lr * wd)
+    g = grad.to(p.dtype)
+    m.lerp_(g, 1 - b1)
+    v.lerp_(g.square(), 1 - b2)
+    bias1 = 1 - b1 ** step
+    bias2 = 1 - b2 ** step
+    p.add_(m / ((v / bias2).sqrt() + eps), alpha=-(lr / bias1))
+
+
+# ----------------------------------------------------------------------------- CUDA Newton-Schulz on the tcgen05 GEMM
+class _NSWorkspace:
+    def __init__(self, n, r, c, device):
+        g = min(r, c)
+        self.X2 = torch.empty((n, r, c), dtype=torch.bfloat16, device=device)
+        self.A = torch.empty((n, g, g), dtype=torch.bfloat16, device=device)
+        self.B = torch.empty((n, g, g), dtype=torch.bfloat16, device=device)
+
+
+def newton_schulz_cuda(X: torch.Tensor, ns_steps: int, ws: _NSWorkspace, sym: bool = True) -> torch.Tensor:
+    """In: X [n, r, c] bf16. Three GEMMs per iteration; the gram and polynomial products are symmetric and only
+    their upper-triangular tiles are computed; `aX + ...` and `bA + ...` ride in the epilogues."""
+    n, r, c = X.shape
+    tall = r > c
+    src, dst = X, ws.X2[:n]
+    A, B = ws.A[:n], ws.B[:n]
+    for a_, b_, c_ in POLAR_EXPRESS_COEFFS[:ns_steps]:
+        if tall:
+            gemm(src, src, out=A, a_mn=True, b_mn=True, sym=sym)                    # A = X^T X
+            gemm(A, A, out=B, cin=A, alpha=c_, beta=b_, sym=sym)                    # B = bA + cA^2
+            gemm(src, B, out=dst, cin=src, alpha=1.0, beta=a_)                      # X' = aX + X B
+        else:
+            gemm(src, src, out=A, sym=sym)                                          # A = X X^T
+            gemm(A, A, out=B, cin=A, alpha=c_, beta=b_, sym=sym)
+            gemm(B, src, out=dst, cin=src, b_mn=True, alpha=1.0, beta=a_)           # X' = aX + B X
+        src, dst = dst, src
+    return src
+
+
+# ----------------------------------------------------------------------------- optimizer
+class ShardedMuonAdamW:
+    """`param_groups` is the list from `groups.build_param_groups`; the training loop rewrites lr / weight_decay /
+    momentum in it every step exactly as with a torch optimizer."""
+
+    def __init__(self, model, param_groups: List[dict], comm, use_cuda_kernels=None):
+        self.model = model
+        self.arena: ParamArena = model.arena
+        self.param_groups = param_groups
+        self.comm = comm
+        self.rank, self.world = comm.rank, comm.world
+        dev = model.get_device()
+        self.cuda = dev.type == "cuda" if use_cuda_kernels is None else use_cuda_kernels
+        self.device = dev
+        self.state = {}
+        self.step_count = 0
+        if self.arena.world_size != self.world:
+            raise ValueError(f"arena was laid out for world size {self.arena.world_size}, comm has {self.world}")
+        self._init_state()
+
+    # ------------------------------------------------------------------ state
+    def _init_state(self):
+        dev, W = self.device, self.world
+        for g in self.param_groups:
+            if g["kind"] == "muon":
+                ga = self.arena.groups[tuple(g["params"][0].shape)]
+                r, c = ga.shape
+                st = dict(arena=ga,
+                          momentum=torch.zeros((ga.chunk, r, c), dtype=torch.float32, device=dev),
+                          second=torch.zeros((ga.chunk, r, 1) if r >= c else (ga.chunk, 1, c), dtype=torch.float32, device=dev),
+                          grad_chunk=torch.empty((ga.chunk, r, c), dtype=torch.float32, device=dev) if W > 1 else None,
+                          U=torch.zeros((ga.chunk, r, c), dtype=torch.bfloat16, device=dev),
+                          U_all=torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev) if W > 1 else None)
+                if self.cuda and ga.W16 is not None:
+                    st["X"] = torch.empty((ga.chunk, r, c), dtype=torch.bfloat16, device=dev)
+                    st["ws"] = _NSWorkspace(ga.chunk, r, c, dev)
+                    ln = r if r >= c else c
+                    st["scratch"] = torch.empty((3, ga.chunk, max(ln, 1)), dtype=torch.float32, device=dev)
+                    st["sumsq"] = torch.empty(ga.chunk, dtype=torch.float32, device=dev)
+                self.state[g["name"]] = st
+            else:
+                for p in g["params"]:
+                    small = id(p) in self.arena.small_offsets
+                    sharded = (not small) and W > 1 and p.shape[0] % W == 0
+                    rows = p.shape[0] // W if sharded else p.shape[0]
+                    shp = (rows,) + tuple(p.shape[1:])
+                    self.state[id(p)] = dict(m=torch.zeros(shp, dtype=p.dtype, device=dev), v=torch.zeros(shp, dtype=p.dtype, device=dev),
+                                             sharded=sharded, small=small, rows=rows)
+
+    def num_owned(self, ga) -> int:
+        return min(ga.chunk, max(0, ga.n - self.rank * ga.chunk))
+
+    # ------------------------------------------------------------------ gradient source for AdamW params
+    def _grad_of(self, p):
+        if p is self.model.lm_head.weight:
+            return self.arena.head_grad
+        return p.grad
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self):
+        self.step_count += 1
+        W, rank, comm = self.world, self.rank, self.comm
+        gscale = 1.0 / W
+        pending = []
+        # phase 1: launch every gradient reduction
+        small_h = comm.all_reduce_sum(self.arena.small_grads) if W > 1 else None
+        for g in self.param_groups:
+            if g["kind"] == "muon":
+                st = self.state[g["name"]]
+                ga = st["arena"]
+                st["h"] = comm.reduce_scatter_sum(st["grad_chunk"], ga.G) if W > 1 else None
+            else:
+                for p in g["params"]:
+                    st = self.state[id(p)]
+                    if st["small"] or W == 1:
+                        st["h"] = None
+                        continue
+                    grad = self._grad_of(p)
+                    if st["sharded"]:
+                        st["gslice"] = torch.empty((st["rows"],) + tuple(p.shape[1:]), dtype=grad.dtype, device=grad.device)
+                        st["h"] = comm.reduce_scatter_sum(st["gslice"], grad)
+                    else:
+                        st["h"] = comm.all_reduce_sum(grad)
+        # phase 2: compute per group, launch gathers
+        if small_h is not None:
+            small_h.wait()
+        for g in self.param_groups:
+            if g["kind"] == "muon":
+                self._muon_compute(g, gscale, pending)
+            else:
+                self._adamw_compute(g, gscale, pending)
+        # phase 3: finish gathers, apply matrix updates everywhere
+        for item in pending:
+            item()
+
+    # ------------------------------------------------------------------ AdamW
+    def _adamw_launch(self, p_t, g_t, m_t, v_t, shadow, grp, gscale):
+        lr, wd = float(grp["lr"]), float(grp["weight_decay"])
+        b1, b2 = grp["betas"]
+        t = self.step_count
+        if self.cuda:
+            g32 = g_t if g_t.dtype == torch.float32 else g_t.float()
+            rc = _lib.fn("sr_adamw", [c_void_p] * 5 + [c_long, c_int] + [c_float] * 8 + [c_void_p])(
+                p_t.data_ptr(), g32.data_ptr(), m_t.data_ptr(), v_t.data_ptr(), _lib.ptr(shadow), p_t.numel(),
+                int(p_t.dtype == torch.bfloat16), lr, wd, b1, b2, float(grp["eps"]), 1 - b1 ** t, 1 - b2 ** t, gscale,
+                _lib.stream_ptr())
+            _lib.check_rc(rc, "sr_adamw")
+        else:
+            adamw_ref(p_t, g_t.float() * gscale, m_t, v_t, t, lr, b1, b2, float(grp["eps"]), wd)
+            if shadow is not None:
+                shadow.copy_(p_t)
+
+    def _adamw_compute(self, grp, gscale, pending):
+        W, rank = self.world, self.rank
+        arena = self.arena
+        head = self.model.lm_head.weight
+        smalls = [p for p in grp["params"] if self.state[id(p)]["small"]]
+        if smalls:
+            # merge parameters that are adjacent in the flat small-parameter buffer into one launch
+            segs = sorted(arena.small_offsets[id(p)] for p in smalls)
+            merged = []
+            for off, n in segs:
+                if merged and merged[-1][0] + merged[-1][1] == off:
+                    merged[-1][1] += n
+                else:
+                    merged.append([off, n])
+            if "small_m" not in self.state:
+                self.state["small_m"] = torch.zeros_like(arena.small_P)
+                self.state["small_v"] = torch.zeros_like(arena.small_P)
+            for off, n in merged:
+                sl = slice(off, off + n)
+                self._adamw_launch(arena.small_P[sl], arena.small_grads[sl], self.state["small_m"][sl],
+                                   self.state["small_v"][sl], None, grp, gscale)
+        for p in grp["params"]:
+            st = self.state[id(p)]
+            if st["small"]:
+                continue
+            if st.get("h") is not None:
+                st["h"].wait()
+            shadow_full = arena.head_w16 if (p is head and arena.head_w16 is not None) else None
+            if st["sharded"]:
+                rows = st["rows"]
+                sl = slice(rank * rows, (rank + 1) * rows)
+                p_slice = p.data[sl]
+                self._adamw_launch(p_slice, st["gslice"], st["m"], st["v"], None, grp, gscale)
+                h = self.comm.all_gather(p.data, p_slice)
+                def fin(h=h, shadow_full=shadow_full, p=p):
+                    h.wait()
+                    if shadow_full is not None:
+                        shadow_full.copy_(p.data)
+                pending.append(fin)
+            else:
+                self._adamw_launch(p.data, self._grad_of(p), st["m"], st["v"], shadow_full, grp, gscale)
+
+    # ------------------------------------------------------------------ Muon
+    def _muon_compute(self, grp, gscale, pending):
+        st = self.state[grp["name"]]
+        ga = st["arena"]
+        W, rank = self.world, self.rank
+        r, c = ga.shape
+        if st.get("h") is not None:
+            st["h"].wait()
+        n_own = self.num_owned(ga)
+        G = st["grad_chunk"] if W > 1 else ga.G
+        U = st["U"]
+        mu, beta2, ns = float(grp["momentum"]), float(grp["beta2"]), int(grp["ns_steps"])
+        if n_own > 0:
+            if self.cuda and "X" in st:
+                X = st["X"][:n_own]
+                sc = st["scratch"]
+                rc = _lib.fn("sr_muon_pre", [c_void_p] * 4 + [c_int, c_int, c_int, c_float, c_float, c_void_p])(
+                    G.data_ptr(), st["momentum"].data_ptr(), X.data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, mu, gscale,
+                    _lib.stream_ptr())
+                _lib.check_rc(rc, "sr_muon_pre")
+                Xo = newton_schulz_cuda(X, ns, st["ws"])
+                rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
+                    Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), U.data_ptr(), n_own, r, c,
+                    beta2, _lib.stream_ptr())
+                _lib.check_rc(rc, "sr_muon_post")
+            else:
+                g_own = G[:n_own].mul(gscale) if gscale != 1.0 else G[:n_own].clone()
+                U[:n_own].copy_(muon_update_ref(g_own, st["momentum"][:n_own], st["second"][:n_own], mu, beta2, ns))
+        lr_eff = float(grp["lr"]) * max(1.0, r / c) ** 0.5
+        wd = float(grp["weight_decay"])
+        if W > 1:
+            h = self.comm.all_gather(st["U_all"], U)
+        else:
+            h = None
+
+        def fin():
+            if h is not None:
+                h.wait()
+            Uall = st["U_all"][:ga.n] if W > 1 else U[:ga.n]
+            if self.cuda and ga.W16 is not None:
+                lr_b = _bf16(lr_eff)
+                lrwd_b = _bf16(lr_b * _bf16(wd))
+                rc = _lib.fn("sr_muon_apply", [c_void_p] * 3 + [c_long, c_float, c_float, c_void_p])(
+                    ga.P.data_ptr(), Uall.data_ptr(), ga.W16.data_ptr(), ga.P.numel(), lr_b, lrwd_b, _lib.stream_ptr())
+                _lib.check_rc(rc, "sr_muon_apply")
+            else:
+                muon_apply_ref(ga.P, Uall, lr_eff, wd)
+                if ga.W16 is not None:
+                    ga.W16.copy_(ga.P)
+        pending.append(fin)
+
+    # ------------------------------------------------------------------ (de)serialisation of the owned state
+    def state_dict(self):
+        out = {"step_count": self.step_count, "groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+        tensors = {}
+        for g in self.param_groups:
+            if g["kind"] == "muon":
+                st = self.state[g["name"]]
+                tensors[g["name"] + ".momentum"] = st["momentum"]
+                tensors[g["name"] + ".second"] = st["second"]
+            else:
+                for i, p in enumerate(g["params"]):
+                    st = self.state[id(p)]
+                    if not st["small"]:
+                        tensors[f"{g['name']}.{i}.m"] = st["m"]
+                        tensors[f"{g['name']}.{i}.v"] = st["v"]
+        if "small_m" in self.state:
+            tensors["small_m"], tensors["small_v"] = self.state["small_m"], self.state["small_v"]
+        out["tensors"] = {k: v.detach().cpu() for k, v in tensors.items()}
+        return out
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step_count"]
+        for g, saved in zip(self.param_groups, sd["groups"]):
+            g.update(saved)
+        t = sd["tensors"]
+        for g in self.param_groups:
+            if g["kind"] == "muon":
+                st = self.state[g["name"]]
+                st["momentum"].copy_(t[g["name"] + ".momentum"])
+                st["second"].copy_(t[g["name"] + ".second"])
+            else:
+                for i, p in enumerate(g["params"]):
+                    st = self.state[id(p)]
+                    if not st["small"]:
+                        st["m"].copy_(t[f"{g['name']}.{i}.m"])
+                        st["v"].copy_(t[f"{g['name']}.{i}.v"])
+        if "small_m" in t:
+            self.state["small_m"] = t["small_m"].to(self.device)
+            self.state["small_v"] = t["small_v"].to(self.device)

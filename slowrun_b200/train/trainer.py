@@ -1,0 +1,296 @@
+"""Training driver for the limited, two-hour and tiny tracks.
+
+`Trainer.train_step()` is one optimizer step: `grad_accum` micro-batches of forward/backward with local fp32
+gradient accumulation, the schedules, then the sharded optimizer step (the only place gradients cross GPUs), as in
+the reference loop (train.py:1146-1254, tiny/train.py:1400-1470). `Trainer.fit()` adds evaluation at epoch
+boundaries, the checkpoint ring, dupe-layer / window / recurrence switches, early stopping and the post-training
+averaging passes. Log lines keep the reference's format so existing parsers work.
+"""
+from __future__ import annotations
+
+import gc
+import json
+import math
+import os
+import shutil
+import sys
+import time
+from typing import Optional
+
+import torch
+
+from ..config import TrainConfig, MAX_SEQ_LEN
+from ..data.loader import TokenLoader
+from ..models.gpt import build_model
+from ..optim.groups import build_param_groups
+from ..optim.muon_adamw import ShardedMuonAdamW
+from ..ops import _lib
+from ..parallel.comm import DistInfo, TorchComm, init_distributed, print0
+from ..utils.logging import RunLogger
+from .checkpoint import CheckpointRing, WeightEMA, average_checkpoints_into, recency_weights
+from .evaluate import default_token_bytes, evaluate_bpb, evaluate_prob_avg
+from .schedules import Schedules, parse_window_schedule, window_stage_for_epoch
+
+
+def make_comm(cfg: TrainConfig, info: DistInfo):
+    """Collective backend: peer-memory kernels on multi-GPU CUDA jobs unless --comm nccl, else torch.distributed."""
+    if info.world_size > 1 and info.device.type == "cuda" and cfg.comm in ("auto", "fused"):
+        try:
+            from ..parallel.fused import FusedComm
+            return FusedComm()
+        except Exception as e:  # noqa: BLE001 - fall back to the library path, loudly
+            if cfg.comm == "fused":
+                raise
+            print0(f"[comm] peer-memory collectives unavailable ({type(e).__name__}: {e}); using NCCL")
+    return TorchComm()
+
+
+class Trainer:
+    def __init__(self, cfg: TrainConfig, info: Optional[DistInfo] = None, quiet: bool = False):
+        self.cfg = cfg
+        self.info = info or init_distributed()
+        info = self.info
+        self.device = info.device
+        self.master = info.rank == 0
+        self.quiet = quiet
+        c = cfg
+        seed = c.seed if c.track == "unlimited" else 42
+        self.model = build_model(c.model, self.device, seed=seed, world_size=info.world_size)
+        self.comm = make_comm(c, info)
+        self.param_groups = build_param_groups(self.model, c)
+        self.optimizer = ShardedMuonAdamW(self.model, self.param_groups, self.comm)
+        train_path = c.input_bin or os.path.join(c.data_dir, "fineweb_train.pt")
+        self.val_path = c.input_val_bin or os.path.join(c.data_dir, "fineweb_val.pt")
+        T = c.model.sequence_len
+        self.train_loader = TokenLoader(train_path, c.device_batch_size, T, device=self.device,
+                                        doc_shuffle=not c.no_doc_shuffle, rank=info.rank, world_size=info.world_size)
+        self.tokens_per_epoch = self.train_loader.total_tokens
+        tokens_per_fwdbwd = c.device_batch_size * T * info.world_size
+        assert c.total_batch_size % tokens_per_fwdbwd == 0, "total batch must be a multiple of B*T*world"
+        self.grad_accum = c.total_batch_size // tokens_per_fwdbwd
+        self.sched = Schedules(c, self.tokens_per_epoch)
+        self.window_schedule = parse_window_schedule(c.window_schedule, T) if c.track == "two_hour" else ()
+        self.step = 0
+        self.current_epoch = 1
+        self.smooth_loss = 0.0
+        self.dupe_active = False
+        self.x, self.y, self.current_epoch = next(self.train_loader)
+        self._pending_epoch = self.current_epoch
+        self.flops_per_token = self.model.estimate_flops()
+        self.token_bytes = None
+        self.ema = None
+        if c.track == "tiny" and c.update_ema_every > 0:
+            self.ema = WeightEMA(self.model, c.ema_decay_per_epoch, c.update_ema_every, self.sched.steps_per_epoch)
+        st = window_stage_for_epoch(self.window_schedule, self.current_epoch)
+        if st is not None:
+            self.model.set_window_sizes(st.short_window, st.long_window)
+        self.model.train()
+        self.h2d_bytes_per_step = self.train_loader.h2d_bytes_per_batch * self.grad_accum
+        self.d2h_bytes_per_step = 4
+
+    # ------------------------------------------------------------------ one optimizer step
+    def _maybe_switch_structure(self):
+        c = self.cfg
+        if c.track in ("limited", "two_hour") and not self.dupe_active and self.current_epoch >= c.dupe_start_epoch:
+            self.model.set_dupe_layers(c.dupe_layers_start, c.dupe_layers_end, c.dupe_loops)
+            self.dupe_active = True
+            self.flops_per_token = self.model.estimate_flops()
+            if not self.quiet:
+                print0(f"\n=== Enabling dupe-layers at epoch {self.current_epoch} ===")
+                print0(f"Dupe layers {c.dupe_layers_start}-{c.dupe_layers_end - 1}: {c.dupe_loops} extra replays ({c.dupe_loops + 1} total passes)")
+
+    def train_step(self, sync: bool = True):
+        """Runs one optimizer step. Returns a dict with the (host) loss of the last micro-batch when `sync`."""
+        c, model = self.cfg, self.model
+        self._maybe_switch_structure()
+        tiny = c.track == "tiny"
+        n_iter = self.sched.num_recurrences(self.step) if tiny else None
+        mtp_w = None
+        if tiny and c.model.fused_mtp:
+            mtp_w = torch.tensor(self.sched.mtp_weights(self.step), dtype=torch.float32, device=self.device)
+        metrics = {}
+        loss_t = None
+        epoch = self._pending_epoch
+        for _ in range(self.grad_accum):
+            if tiny:
+                loss = model(self.x, self.y, num_iterations=n_iter, mtp_weights=mtp_w)
+            else:
+                loss, metrics = model(self.x, self.y)
+            loss_t = loss.detach()
+            (loss / self.grad_accum).backward()
+            self.x, self.y, epoch = next(self.train_loader)
+        self._pending_epoch = epoch
+        self.sched.apply(self.param_groups, self.step)
+        self.optimizer.step()
+        model.zero_grad_arena()
+        if self.ema is not None:
+            self.ema.maybe_update(self.step)
+        self.step += 1
+        out = {"loss_tensor": loss_t, "metrics": metrics, "epoch": epoch, "num_iterations": n_iter}
+        if sync:
+            out["loss"] = loss_t.item()
+            if self.device.type == "cuda":
+                _lib.check_status(self.device)
+        return out
+
+    # ------------------------------------------------------------------ evaluation helpers
+    def build_val_loader(self):
+        c = self.cfg
+        return TokenLoader(self.val_path, c.device_batch_size, c.model.sequence_len, device=self.device,
+                           rank=self.info.rank, world_size=self.info.world_size, prefetch=False)
+
+    def evaluate(self, num_iterations=None):
+        c = self.cfg
+        if self.token_bytes is None:
+            self.token_bytes = default_token_bytes(self.device, c.model.vocab_size)
+        steps = max(1, c.eval_tokens // (c.device_batch_size * c.model.sequence_len * self.info.world_size))
+        self.model.eval()
+        bpb, loss = evaluate_bpb(self.model, self.build_val_loader(), steps, self.token_bytes,
+                                 self.comm if self.info.world_size > 1 else None, num_iterations=num_iterations)
+        self.model.train()
+        return bpb, loss
+
+    def sync_epoch(self, epoch: int) -> int:
+        if self.info.world_size > 1:
+            t = torch.tensor([epoch], dtype=torch.long, device=self.device)
+            self.comm.all_reduce_max(t)
+            return int(t.item())
+        return epoch
+
+    # ------------------------------------------------------------------ full run
+    def fit(self):
+        c, info = self.cfg, self.info
+        log = RunLogger(c, info, quiet=self.quiet)
+        self.log = log
+        log.hyperparameters(c, self.model, self.flops_per_token)
+        world = info.world_size
+        N = self.sched.N
+        target_steps = c.max_train_steps if (c.track == "tiny" and c.max_train_steps > 0) else N
+        print0(f"Batch size: {c.total_batch_size:,} tokens, grad accum: {self.grad_accum} steps")
+        print0(f"Training for {c.num_epochs} epoch(s) (~{N} steps estimated)")
+        print0(f"Eval set: {c.eval_tokens:,} tokens")
+        min_bpb = min_loss = float("inf")
+        val_bpb = val_loss = float("inf")
+        bad_epochs = 0
+        total_time, timed_steps, timing_start = 0.0, 0, 4
+        keep = c.logit_avg if c.track in ("limited", "two_hour") else c.swa_last_epochs
+        ring_dir = c.logit_avg_dir if c.track in ("limited", "two_hour") else os.path.join(log.run_dir, "checkpoints")
+        ring = CheckpointRing(ring_dir, keep, self.master)
+        max_iters = c.model.num_iterations if c.track == "tiny" else None
+        if not c.eval_logit_avg:
+            val_bpb, val_loss = self.evaluate(max_iters)
+            print0(f"Step {self.step:05d} | Val BPB: {val_bpb:.6f} | Val Loss: {val_loss:.6f}")
+            log.metrics({"step": self.step, "val/bpb": val_bpb, "val/loss": val_loss})
+            min_bpb, min_loss = val_bpb, val_loss
+        synchronize = torch.cuda.synchronize if self.device.type == "cuda" else (lambda: None)
+        while not c.eval_logit_avg and self.current_epoch <= c.num_epochs:
+            if c.max_steps >= 0 and self.step >= c.max_steps:
+                break
+            was_dupe = self.dupe_active
+            synchronize()
+            t0 = time.time()
+            out = self.train_step(sync=True)
+            synchronize()
+            dt = time.time() - t0
+            if self.dupe_active and not was_dupe:
+                timing_start = self.step + 3
+            step = self.step
+            self.smooth_loss = 0.9 * self.smooth_loss + 0.1 * out["loss"]
+            debiased = self.smooth_loss / (1 - 0.9 ** step)
+            tok_s = int(c.total_batch_size / dt)
+            mfu = 100 * self.flops_per_token * c.total_batch_size / dt / (log.peak_flops * world)
+            if step >= timing_start:
+                total_time += dt
+                timed_steps += 1
+            eta = f" | eta: {(target_steps - step) * total_time / timed_steps / 60:.1f}m" if timed_steps > 0 else ""
+            tag = " [DUPE]" if self.dupe_active else ""
+            it_s = f" | iters: {out['num_iterations']}" if out["num_iterations"] is not None else ""
+            print0(f"step {step:05d} ({100 * step / target_steps:.2f}%) | loss: {debiased:.6f} | dt: {dt * 1000:.2f}ms | "
+                   f"tok/sec: {tok_s:,} | bf16_mfu: {mfu:.2f}%{it_s}{tag}{eta}")
+            log.metrics({"step": step, "train/loss": debiased, "train/mfu": mfu, "train/tok_per_sec": tok_s,
+                         **{f"train/{k}": float(v) for k, v in out["metrics"].items()}})
+            epoch = self.sync_epoch(out["epoch"])
+            if epoch != self.current_epoch:
+                val_bpb, val_loss = self.evaluate(max_iters)
+                print0(f"Step {step:05d} | Epoch {self.current_epoch} | Val BPB: {val_bpb:.6f} | Val Loss: {val_loss:.6f}")
+                log.metrics({"step": step, "epoch": self.current_epoch, "val/bpb": val_bpb, "val/loss": val_loss})
+                stop = False
+                if val_bpb < min_bpb:
+                    min_bpb, min_loss, bad_epochs = val_bpb, val_loss, 0
+                else:
+                    bad_epochs += 1
+                    if c.patience >= 0 and bad_epochs >= c.patience:
+                        print0(f"Early stopping: no improvement for {c.patience} epoch(s)")
+                        stop = True
+                if keep > 0 and not stop:
+                    path = ring.save(self.model, self.current_epoch)
+                    print0(f"  Saved checkpoint {path} ({len(ring.paths)}/{keep})")
+                if stop:
+                    break
+                st = window_stage_for_epoch(self.window_schedule, epoch)
+                if st is not None and (st.short_window != self.model.short_window or st.long_window != self.model.long_window):
+                    self.model.set_window_sizes(st.short_window, st.long_window, apply_yarn=True)
+                    self.flops_per_token = self.model.estimate_flops()
+                    print0(f"Updated window stage for epoch {epoch}: short={st.short_window}, long={st.long_window}, "
+                           f"yarn_scale={self.model.rotary.attn_scale:.6f}")
+                self.current_epoch = epoch
+            if c.track == "tiny" and c.max_train_steps > 0 and self.step >= c.max_train_steps:
+                print0(f"Reached max_train_steps={c.max_train_steps}")
+                break
+            if self.step == 1:
+                gc.collect()
+                gc.freeze()
+                gc.disable()
+        gc.enable()
+        # ---------------------------------------------------------------- post-training averaging
+        comm = self.comm if world > 1 else None
+        if c.track in ("limited", "two_hour") and c.logit_avg > 0:
+            paths = ring.paths
+            if c.eval_logit_avg:
+                import glob
+                paths = sorted(glob.glob(os.path.join(c.logit_avg_dir, "epoch_*.pt")))[-c.logit_avg:]
+            if len(paths) >= 2:
+                n = len(paths)
+                print0(f"\n--- Evaluating logit avg ({n} checkpoints: {[os.path.basename(p) for p in paths]}) ---")
+                if self.token_bytes is None:
+                    self.token_bytes = default_token_bytes(self.device, c.model.vocab_size)
+                steps = max(1, c.eval_tokens // (c.device_batch_size * c.model.sequence_len * world))
+                self.model.eval()
+                for label in (("equal", "weighted") if c.logit_avg_mode == "both" else (c.logit_avg_mode,)):
+                    w = recency_weights(n, label)
+                    print0(f"  [{label}] weights: {[f'{x:.3f}' for x in w]}")
+                    bpb, loss = evaluate_prob_avg(self.model, self.build_val_loader, paths, w, steps, self.token_bytes, comm)
+                    print0(f"  [{label}] Val BPB: {bpb:.6f} | Val Loss: {loss:.6f}")
+                    log.metrics({f"logit_avg_{label}/bpb": bpb, f"logit_avg_{label}/loss": loss})
+                    if loss < min_loss:
+                        min_loss, min_bpb = loss, bpb
+                        print0(f"  ** New best! (logit avg {label} weights)")
+        if c.track == "tiny":
+            if self.ema is not None and self.ema.copy_into(self.model):
+                val_bpb, val_loss = self.evaluate(max_iters)
+                print0(f"EMA Val BPB: {val_bpb:.6f} | EMA Val Loss: {val_loss:.6f} | iters: {max_iters}")
+                log.metrics({"step": self.step, "val/ema_bpb": val_bpb, "val/ema_loss": val_loss})
+                if val_bpb < min_bpb:
+                    min_bpb, min_loss = val_bpb, val_loss
+            if len(ring.paths) >= 2:
+                average_checkpoints_into(self.model, ring.paths, recency_weights(len(ring.paths)), comm, self.master)
+                avg_bpb, avg_loss = self.evaluate(max_iters)
+                print0(f"Ckpt avg Val BPB: {avg_bpb:.6f} | Val Loss: {avg_loss:.6f} | iters: {max_iters}")
+                log.metrics({"ckpt_avg/bpb": avg_bpb, "ckpt_avg/loss": avg_loss})
+                if avg_loss < min_loss:
+                    min_loss, min_bpb = avg_loss, avg_bpb
+            if self.master:
+                torch.save({n: p.data.float().cpu() for n, p in self.model.named_parameters()}, os.path.join(log.run_dir, "model.pt"))
+        peak = torch.cuda.max_memory_allocated() / 1024 / 1024 if self.device.type == "cuda" else 0.0
+        final_train = self.smooth_loss / (1 - 0.9 ** self.step) if self.step > 0 else float("inf")
+        print0(f"Peak memory: {peak:.2f} MiB")
+        print0(f"Total training time: {total_time / 60:.2f}m")
+        print0(f"Final train loss: {final_train:.6f}")
+        print0(f"Min val BPB: {min_bpb:.6f}")
+        print0(f"Min val Loss: {min_loss:.6f}")
+        result = {"matrix_lr": c.matrix_lr, "weight_decay": c.weight_decay, "num_epochs": c.num_epochs,
+                  "val_loss": val_loss, "best_val_loss": min_loss, "val_bpb": val_bpb, "best_val_bpb": min_bpb,
+                  "final_train_loss": final_train, "steps": self.step, "training_time_s": total_time,
+                  "peak_memory_mib": peak, "wandb_url": None}
+        log.finish(result)
+        return result
