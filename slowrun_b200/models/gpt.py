@@ -525,5 +525,8 @@ def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_siz
     model.init_weights()
     if device.type == "cuda":
         model.norm_eps = ops.BF16_EPS
+        from ..ops.attention import current_attention, install_default_attention
+        if current_attention() is None:
+            install_default_attention()
     model.finalize(world_size)
     return model

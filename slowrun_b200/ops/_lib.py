@@ -47,12 +47,26 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+_fn_cache = {}
+launch_count = 0     # launcher calls made so far (each launcher enqueues one or more kernels)
+
+
 def fn(name: str, argtypes, restype=c_int):
+    """Returns a callable for the `extern "C"` launcher `name`; every call through it is counted."""
+    w = _fn_cache.get(name)
+    if w is not None:
+        return w
     f = getattr(lib(), name)
-    if f.argtypes is None:
-        f.argtypes = argtypes
-        f.restype = restype
-    return f
+    f.argtypes = argtypes
+    f.restype = restype
+
+    def call(*args, _f=f):
+        global launch_count
+        launch_count += 1
+        return _f(*args)
+
+    _fn_cache[name] = call
+    return call
 
 
 def stream_ptr() -> int:

@@ -57,12 +57,13 @@ def build_param_groups(model, cfg: TrainConfig):
     if model.config.attn_gate_adamw:
         gates = [b.attn.attn_gate.weight for b in model.transformer.h]
         groups.append(dict(A, name="attn_gate", params=gates, lr=lrs["scalar"], betas=(0.9, 0.99), weight_decay=0.0))
-        if model.config.xsa_mode != "off":
-            groups.append(dict(A, name="xsa", params=[model.xsa_alphas], lr=lrs["scalar"], betas=(0.9, 0.95), weight_decay=0.0))
     else:
         iha = _iha_params(model)
         if iha:
             groups.append(dict(A, name="iha", params=iha, lr=cfg.iha_lr, betas=betas, weight_decay=0.0))
+    # learnable XSA strengths (tiny/train.py:653-655); available to every track when xsa_mode is on
+    if model.config.xsa_mode != "off" and hasattr(model, "xsa_alphas"):
+        groups.append(dict(A, name="xsa", params=[model.xsa_alphas], lr=lrs["scalar"], betas=(0.9, 0.95), weight_decay=0.0))
     for shape, ps in muon_shape_groups(model):
         groups.append(dict(kind="muon", name=f"muon{tuple(shape)}", params=ps, lr=lrs["matrix"], momentum=cfg.muon_momentum,
                            ns_steps=cfg.ns_steps, beta2=0.95, weight_decay=wd))

@@ -57,17 +57,19 @@ def newton_schulz_ref(X: torch.Tensor, ns_steps: int) -> torch.Tensor:
 def muon_update_ref(G, M, S, momentum, beta2, ns_steps):
     """Reference math of train.py:603-634 up to the variance-reduced update U (bf16). Updates M and S in place.
     G: [n, r, c] fp32 averaged gradient (consumed), M: momentum, S: second moment ([n,r,1] or [n,1,c])."""
-    M.lerp_(G, 1 - momentum)
-    g = G.lerp_(M, momentum)
-    g = g / g.float().norm(dim=-1, keepdim=True).clamp_min(1e-7)
+    mu = torch.tensor(momentum, dtype=G.dtype)     # the reference forms 1 - mu in the gradient dtype
+    M.lerp_(G, (1 - mu).to(G.device))
+    g = G.lerp_(M, mu.to(G.device))
+    g /= g.float().norm(dim=-1, keepdim=True).clamp_min(1e-7).to(g.dtype)
     X = g.bfloat16()
-    X = X / (X.float().norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6).to(X.dtype)
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6)
     X = newton_schulz_ref(X, ns_steps)
     red_dim = -1 if G.size(-2) >= G.size(-1) else -2
     v_mean = X.float().square().mean(dim=red_dim, keepdim=True)
     red = X.size(red_dim)
     v_norm = (v_mean.sum(dim=(-2, -1), keepdim=True) * red).sqrt()
-    S.lerp_(v_mean.to(S.dtype), 1 - beta2)
+    # the reference casts beta2 to the (bf16) dtype of the orthogonalised update before forming 1 - beta2
+    S.lerp_(v_mean.to(S.dtype), 1 - _bf16(beta2))
     step = S.clamp_min(1e-10).rsqrt()
     v_norm_new = ((v_mean * red) * step.float().square()).sum(dim=(-2, -1), keepdim=True).sqrt()
     final_scale = step * (v_norm / v_norm_new.clamp_min(1e-10))
@@ -302,7 +304,7 @@ class ShardedMuonAdamW:
                 Xo = newton_schulz_cuda(X, ns, st["ws"])
                 rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
                     Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), U.data_ptr(), n_own, r, c,
-                    beta2, _lib.stream_ptr())
+                    _bf16(beta2), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_post")
             else:
                 g_own = G[:n_own].mul(gscale) if gscale != 1.0 else G[:n_own].clone()
