@@ -1,0 +1,321 @@
+// Kernels that exist only because the transformer block is executed as ONE autograd node with a hand-written
+// backward (slowrun_b200/ops/block.py): every gradient buffer is written exactly once, so no slice/concat/zero-fill
+// glue is left to the autograd engine.
+//
+//   qkv_prep fwd/bwd   split the fused [M, 3d] projection, add the gated value residual to v, apply RoPE and the
+//                      per-head RMSNorm to q and k; backward writes one dense dqkv buffer (train.py:296-306).
+//   iha_mix fwd/bwd    Interleaved-head mixing of projection weights W'[h] = sum_m mix[h,m] W[m] on bf16 shadows and
+//                      its gradients (dW += mix^T dW', dmix = dW' W^T). The reference leaves the [H, d*D] x [d*D, H]
+//                      product to a library GEMM (train.py:277-280); with H <= 20 that is a long skinny reduction,
+//                      done here as a streaming kernel plus a shared-memory tree.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = kWarpsPerBlock * 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void st2(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// ---------------------------------------------------------------------------------------------- qkv prep
+// One warp per (token, head); lane l owns elements {2l, 2l+1} and {64+2l, 64+2l+1} of each 128-wide head vector.
+__global__ void qkv_prep_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ ve,
+                                    const float* __restrict__ gate, const __nv_bfloat16* __restrict__ cosb,
+                                    const __nv_bfloat16* __restrict__ sinb, __nv_bfloat16* __restrict__ q_out,
+                                    __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, long tokens, int H,
+                                    int T, float eps) {
+  const long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (wid >= tokens * H) return;
+  const int lane = threadIdx.x & 31;
+  const long tok = wid / H;
+  const int h = (int)(wid - tok * H);
+  const int t = (int)(tok % T);
+  const long d = (long)H * 128;
+  const float2 c = ld2(cosb + (long)t * 64 + 2 * lane);
+  const float2 s = ld2(sinb + (long)t * 64 + 2 * lane);
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* p = qkv + tok * 3 * d + which * d + h * 128;
+    const float2 x1 = ld2(p + 2 * lane), x2 = ld2(p + 64 + 2 * lane);
+    float2 o1, o2;
+    o1.x = x1.x * c.x + x2.x * s.x;
+    o1.y = x1.y * c.y + x2.y * s.y;
+    o2.x = -x1.x * s.x + x2.x * c.x;
+    o2.y = -x1.y * s.y + x2.y * c.y;
+    float ss = o1.x * o1.x + o1.y * o1.y + o2.x * o2.x + o2.y * o2.y;
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+    __nv_bfloat16* o = (which == 0 ? q_out : k_out) + wid * 128;
+    st2(o + 2 * lane, o1.x * r, o1.y * r);
+    st2(o + 64 + 2 * lane, o2.x * r, o2.y * r);
+  }
+  {
+    const __nv_bfloat16* p = qkv + tok * 3 * d + 2 * d + h * 128 + lane * 4;
+    float2 a0 = ld2(p), a1 = ld2(p + 2);
+    if (ve != nullptr) {
+      const float g = gate[wid];
+      const __nv_bfloat16* e = ve + tok * d + h * 128 + lane * 4;
+      const float2 e0 = ld2(e), e1 = ld2(e + 2);
+      a0.x += g * e0.x; a0.y += g * e0.y; a1.x += g * e1.x; a1.y += g * e1.y;
+    }
+    __nv_bfloat16* o = v_out + wid * 128 + lane * 4;
+    st2(o, a0.x, a0.y);
+    st2(o + 2, a1.x, a1.y);
+  }
+}
+
+__global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ ve,
+                                    const float* __restrict__ gate, const __nv_bfloat16* __restrict__ cosb,
+                                    const __nv_bfloat16* __restrict__ sinb, const __nv_bfloat16* __restrict__ dq,
+                                    const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ dv,
+                                    __nv_bfloat16* __restrict__ dqkv, __nv_bfloat16* __restrict__ dve,
+                                    float* __restrict__ dgate, long tokens, int H, int T, float eps) {
+  const long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (wid >= tokens * H) return;
+  const int lane = threadIdx.x & 31;
+  const long tok = wid / H;
+  const int h = (int)(wid - tok * H);
+  const int t = (int)(tok % T);
+  const long d = (long)H * 128;
+  const float2 c = ld2(cosb + (long)t * 64 + 2 * lane);
+  const float2 s = ld2(sinb + (long)t * 64 + 2 * lane);
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* p = qkv + tok * 3 * d + which * d + h * 128;
+    const float2 x1 = ld2(p + 2 * lane), x2 = ld2(p + 64 + 2 * lane);
+    float2 o1, o2;
+    o1.x = x1.x * c.x + x2.x * s.x;
+    o1.y = x1.y * c.y + x2.y * s.y;
+    o2.x = -x1.x * s.x + x2.x * c.x;
+    o2.y = -x1.y * s.y + x2.y * c.y;
+    const __nv_bfloat16* gp = (which == 0 ? dq : dk) + wid * 128;
+    const float2 g1 = ld2(gp + 2 * lane), g2 = ld2(gp + 64 + 2 * lane);
+    float ss = o1.x * o1.x + o1.y * o1.y + o2.x * o2.x + o2.y * o2.y;
+    float dot = o1.x * g1.x + o1.y * g1.y + o2.x * g2.x + o2.y * g2.y;
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+    const float k = r * r * r * dot * (1.f / 128.f);
+    float2 d1, d2;
+    d1.x = r * g1.x - k * o1.x;
+    d1.y = r * g1.y - k * o1.y;
+    d2.x = r * g2.x - k * o2.x;
+    d2.y = r * g2.y - k * o2.y;
+    __nv_bfloat16* o = dqkv + tok * 3 * d + which * d + h * 128;
+    st2(o + 2 * lane, d1.x * c.x - d2.x * s.x, d1.y * c.y - d2.y * s.y);
+    st2(o + 64 + 2 * lane, d1.x * s.x + d2.x * c.x, d1.y * s.y + d2.y * c.y);
+  }
+  {
+    const __nv_bfloat16* gp = dv + wid * 128 + lane * 4;
+    const float2 g0 = ld2(gp), g1 = ld2(gp + 2);
+    __nv_bfloat16* o = dqkv + tok * 3 * d + 2 * d + h * 128 + lane * 4;
+    st2(o, g0.x, g0.y);
+    st2(o + 2, g1.x, g1.y);
+    if (ve != nullptr) {
+      const float g = gate[wid];
+      const __nv_bfloat16* e = ve + tok * d + h * 128 + lane * 4;
+      const float2 e0 = ld2(e), e1 = ld2(e + 2);
+      float dot = g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y;
+      dot = warp_sum(dot);
+      if (lane == 0) dgate[wid] = dot;
+      __nv_bfloat16* de = dve + tok * d + h * 128 + lane * 4;
+      st2(de, g * g0.x, g * g0.y);
+      st2(de + 2, g * g1.x, g * g1.y);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- IHA weight mixing
+// W, out: [P, H, J] bf16 (J = head_dim * d_in); mix: [P, H, H] fp32, used rounded to bf16 as the reference's autocast
+// matmul does. One thread per pair of columns.
+template <int H>
+__global__ void iha_mix_fwd_kernel(const float* __restrict__ mix, const __nv_bfloat16* __restrict__ W,
+                                   __nv_bfloat16* __restrict__ out, long J) {
+  __shared__ float sm[H * H];
+  const int p = blockIdx.y;
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x)
+    sm[i] = __bfloat162float(__float2bfloat16(mix[(long)p * H * H + i]));
+  __syncthreads();
+  const long j = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (j >= J) return;
+  const __nv_bfloat16* w = W + (long)p * H * J + j;
+  float2 x[H];
+#pragma unroll
+  for (int m = 0; m < H; ++m) x[m] = ld2(w + (long)m * J);
+  __nv_bfloat16* o = out + (long)p * H * J + j;
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int m = 0; m < H; ++m) {
+      a += sm[h * H + m] * x[m].x;
+      b += sm[h * H + m] * x[m].y;
+    }
+    st2(o + (long)h * J, a, b);
+  }
+}
+
+// gradW[p, m, j] += sum_h mix[p, h, m] * dWp[p, h, j]      (fp32 accumulate into the gradient arena)
+template <int H>
+__global__ void iha_mix_bwd_w_kernel(const float* __restrict__ mix, const __nv_bfloat16* __restrict__ dWp,
+                                     float* __restrict__ gradW, long J) {
+  __shared__ float sm[H * H];
+  const int p = blockIdx.y;
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x)
+    sm[i] = __bfloat162float(__float2bfloat16(mix[(long)p * H * H + i]));
+  __syncthreads();
+  const long j = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (j >= J) return;
+  const __nv_bfloat16* g = dWp + (long)p * H * J + j;
+  float2 x[H];
+#pragma unroll
+  for (int h = 0; h < H; ++h) x[h] = ld2(g + (long)h * J);
+  float* o = gradW + (long)p * H * J + j;
+#pragma unroll
+  for (int m = 0; m < H; ++m) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+      a += sm[h * H + m] * x[h].x;
+      b += sm[h * H + m] * x[h].y;
+    }
+    float2 cur = *reinterpret_cast<float2*>(o + (long)m * J);
+    cur.x += a;
+    cur.y += b;
+    *reinterpret_cast<float2*>(o + (long)m * J) = cur;
+  }
+}
+
+// dmix[p, h, m] += sum_j dWp[p, h, j] * W[p, m, j].  Each CTA stages `kCols` columns of both operands in shared memory
+// (rows padded by one word against bank conflicts), every thread owns (h, m) pairs, one atomicAdd per pair per CTA.
+constexpr int kCols = 512;
+constexpr int kChunksPerCta = 8;
+template <int H>
+__global__ void iha_mix_bwd_mix_kernel(const __nv_bfloat16* __restrict__ dWp, const __nv_bfloat16* __restrict__ W,
+                                       float* __restrict__ dmix, long J) {
+  constexpr int kStride = kCols + 2;
+  __shared__ __nv_bfloat16 sg[H * kStride];
+  __shared__ __nv_bfloat16 sw[H * kStride];
+  const int p = blockIdx.y;
+  constexpr int kPairs = H * H;
+  constexpr int kPer = (kPairs + kThreads - 1) / kThreads;
+  float acc[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) acc[i] = 0.f;
+  for (int ch = 0; ch < kChunksPerCta; ++ch) {
+    const long j0 = ((long)blockIdx.x * kChunksPerCta + ch) * kCols;
+    if (j0 >= J) break;
+    const int ncols = (int)min((long)kCols, J - j0);
+    for (int i = threadIdx.x; i < H * (kCols / 2); i += kThreads) {
+      const int row = i / (kCols / 2), c2 = (i - row * (kCols / 2)) * 2;
+      __nv_bfloat162 a = __floats2bfloat162_rn(0.f, 0.f), b = a;
+      if (c2 < ncols) {
+        a = *reinterpret_cast<const __nv_bfloat162*>(dWp + ((long)p * H + row) * J + j0 + c2);
+        b = *reinterpret_cast<const __nv_bfloat162*>(W + ((long)p * H + row) * J + j0 + c2);
+      }
+      *reinterpret_cast<__nv_bfloat162*>(sg + row * kStride + c2) = a;
+      *reinterpret_cast<__nv_bfloat162*>(sw + row * kStride + c2) = b;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int pair = threadIdx.x + i * kThreads;
+      if (pair < kPairs) {
+        const int h = pair / H, m = pair - h * H;
+        const __nv_bfloat16* a = sg + h * kStride;
+        const __nv_bfloat16* b = sw + m * kStride;
+        float s = 0.f;
+#pragma unroll 8
+        for (int c = 0; c < kCols; c += 2) {
+          const float2 x = ld2(a + c), y = ld2(b + c);
+          s += x.x * y.x + x.y * y.y;
+        }
+        acc[i] += s;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int pair = threadIdx.x + i * kThreads;
+    if (pair < kPairs) atomicAdd(dmix + (long)p * kPairs + pair, acc[i]);
+  }
+}
+
+inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
+
+template <int H>
+int iha_launch(int which, const float* mix, const void* W, const void* dWp, void* out, float* gradW, float* dmix, int P,
+               long J, cudaStream_t s) {
+  const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(dWp);
+  const dim3 grid((unsigned)((J / 2 + kThreads - 1) / kThreads), P);
+  if (which == 0) {
+    iha_mix_fwd_kernel<H><<<grid, kThreads, 0, s>>>(mix, w, reinterpret_cast<__nv_bfloat16*>(out), J);
+  } else {
+    iha_mix_bwd_w_kernel<H><<<grid, kThreads, 0, s>>>(mix, g, gradW, J);
+    const long chunks = (J + kCols - 1) / kCols;
+    const dim3 grid2((unsigned)((chunks + kChunksPerCta - 1) / kChunksPerCta), P);
+    iha_mix_bwd_mix_kernel<H><<<grid2, kThreads, 0, s>>>(g, w, dmix, J);
+  }
+  return rc();
+}
+
+int iha_dispatch(int which, int H, const float* mix, const void* W, const void* dWp, void* out, float* gradW,
+                 float* dmix, int P, long J, cudaStream_t s) {
+  if (J % 2) return -2;
+  switch (H) {
+    case 2: return iha_launch<2>(which, mix, W, dWp, out, gradW, dmix, P, J, s);
+    case 4: return iha_launch<4>(which, mix, W, dWp, out, gradW, dmix, P, J, s);
+    case 8: return iha_launch<8>(which, mix, W, dWp, out, gradW, dmix, P, J, s);
+    case 14: return iha_launch<14>(which, mix, W, dWp, out, gradW, dmix, P, J, s);
+    case 16: return iha_launch<16>(which, mix, W, dWp, out, gradW, dmix, P, J, s);
+    case 20: return iha_launch<20>(which, mix, W, dWp, out, gradW, dmix, P, J, s);
+    default: return -7;  // unsupported head count: the caller falls back to library matmuls
+  }
+}
+
+}  // namespace
+
+#define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
+#define BFM(p) reinterpret_cast<__nv_bfloat16*>(p)
+
+// qkv: [tokens, 3*H*128]; ve: [tokens, H*128] or null; gate: fp32 [tokens, H] (only read when ve != null)
+extern "C" int sr_qkv_prep_fwd(const void* qkv, const void* ve, const float* gate, const void* cosb, const void* sinb,
+                               void* q, void* k, void* v, long tokens, int H, int T, float eps, cudaStream_t s) {
+  const long n = tokens * H;
+  if (n <= 0) return 0;
+  qkv_prep_fwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BFM(q), BFM(k), BFM(v), tokens, H, T, eps);
+  return rc();
+}
+extern "C" int sr_qkv_prep_bwd(const void* qkv, const void* ve, const float* gate, const void* cosb, const void* sinb,
+                               const void* dq, const void* dk, const void* dv, void* dqkv, void* dve, float* dgate,
+                               long tokens, int H, int T, float eps, cudaStream_t s) {
+  const long n = tokens * H;
+  if (n <= 0) return 0;
+  qkv_prep_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BF(dq), BF(dk), BF(dv), BFM(dqkv), BFM(dve), dgate, tokens, H, T, eps);
+  return rc();
+}
+// out[p] = bf16(mix[p]) @ W[p] for P stacked projections, W viewed as [P, H, J]
+extern "C" int sr_iha_mix_fwd(const float* mix, const void* W, void* out, int P, int H, long J, cudaStream_t s) {
+  return iha_dispatch(0, H, mix, W, nullptr, out, nullptr, nullptr, P, J, s);
+}
+// gradW[p] += bf16(mix[p])^T @ dWp[p] (fp32) and dmix[p] += dWp[p] @ W[p]^T (fp32, atomically accumulated)
+extern "C" int sr_iha_mix_bwd(const float* mix, const void* W, const void* dWp, float* gradW, float* dmix, int P, int H,
+                              long J, cudaStream_t s) {
+  return iha_dispatch(1, H, mix, W, dWp, nullptr, gradW, dmix, P, J, s);
+}

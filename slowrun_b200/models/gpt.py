@@ -19,6 +19,7 @@ from ..config import ModelConfig
 from ..ops import functional as ops
 from ..ops.gemm import gemm
 from ..ops import _lib
+from ..ops.block import block_forward, block_supported
 
 
 def has_ve(layer_idx: int, n_layer: int) -> bool:
@@ -189,7 +190,8 @@ class GPT(nn.Module):
         if self.mtp_weight > 0:
             self.mtp_proj = nn.Linear(2 * c.n_embd, c.n_embd, bias=False)
             self.mtp_block = Block(c, c.n_layer)
-        self.arena = None          # set by finalize() on CUDA
+        self.use_fused_blocks = True   # CUDA: run each block as one autograd node (ops/block.py)
+        self.arena = None          # set by finalize()
         self.norm_eps: Optional[float] = None   # None = torch default for the activation dtype
 
     # ------------------------------------------------------------------ structure helpers
@@ -417,6 +419,10 @@ class GPT(nn.Module):
 
     def _layer(self, i, x, x0, skip, cos_sin, scale):
         j = i - self.encoder_layers
+        block = self.transformer.h[i]
+        if x.is_cuda and self.use_fused_blocks and block_supported(self, block):
+            ve_lin = self.ve_projs[str(i)] if str(i) in self.ve_projs else None
+            return block_forward(self, block, x, x0, skip, i, max(j, 0), True, ve_lin, self.window_sizes[i], scale)
         x = ops.lambda_mix(x, x0, skip, self.resid_lambdas, self.x0_lambdas, self.skip_weights, i, max(j, 0))
         ve = self._ve(i, x0)
         xsa = self.xsa_alphas[i] if self._xsa_enabled(i) else None
@@ -507,7 +513,11 @@ class GPT(nn.Module):
         mT = combined.size(1)
         cs = (self.rotary.cos[:, :mT], self.rotary.sin[:, :mT])
         scale = self.rotary.attn_scale if self.rotary.yarn_active else None
-        mtp_out = ops.rms_norm(self._block_forward(self.mtp_block, combined, None, cs, (-1, -1), scale), self.norm_eps)
+        if combined.is_cuda and self.use_fused_blocks and block_supported(self, self.mtp_block):
+            mtp_x = block_forward(self, self.mtp_block, combined, None, None, 0, 0, False, None, (-1, -1), scale)
+        else:
+            mtp_x = self._block_forward(self.mtp_block, combined, None, cs, (-1, -1), scale)
+        mtp_out = ops.rms_norm(mtp_x, self.norm_eps)
         mtp_loss = ops.lm_head_loss(mtp_out, w, targets[:, 1:], c.logit_cap, c.vocab_size, acc, w_t)
         loss = lm_loss + self.mtp_weight * mtp_loss
         return loss, {"lm_loss": lm_loss, "mtp_loss": mtp_loss}

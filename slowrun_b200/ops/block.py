@@ -1,0 +1,277 @@
+"""The transformer block (with its lambda-mix prologue) as ONE autograd node with a hand-written backward.
+
+Forward and backward are straight-line sequences of the sm_100a kernels: tcgen05 GEMMs for the five projections
+(weight gradients accumulate into the fp32 arenas inside the GEMM epilogue), fused row-wise kernels in between, the
+attention implementation through its explicit fwd/bwd interface. Every gradient tensor is written once, by the
+kernel that produces it; autograd only sees the three activations entering the block (previous residual stream, x0,
+U-Net skip). Semantics are those of the reference block (train.py:282-344, 514-525): value residual gated per head,
+RoPE then QK-norm, per-head sigmoid attention gate, IHA weight mixing, SwiGLU, dropout on both residual branches,
+stochastic depth as a blend with the block input.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import _lib
+from . import functional as ops
+from .attention import current_impl
+from .gemm import gemm
+
+P, I, L, F32, ULL = _lib.c_void_p, _lib.c_int, _lib.ctypes.c_long, _lib.c_float, _lib.ctypes.c_ulonglong
+
+
+def _call(name, argtypes, *args):
+    rc = _lib.fn(name, argtypes)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name}: launcher returned {rc}")
+
+
+def _sp():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _rmsnorm_fwd(x, eps):
+    y = torch.empty_like(x)
+    _call("sr_rmsnorm_fwd", [P, P, L, I, L, F32, P], x.data_ptr(), y.data_ptr(), x.size(0), x.size(1), x.stride(0), eps, _sp())
+    return y
+
+
+def _rmsnorm_bwd(x, dy, dres, eps):
+    dx = torch.empty_like(x)
+    _call("sr_rmsnorm_bwd", [P, P, P, P, L, I, L, F32, P], x.data_ptr(), dy.data_ptr(), _lib.ptr(dres), dx.data_ptr(),
+          x.size(0), x.size(1), x.stride(0), eps, _sp())
+    return dx
+
+
+def _dropout_add_fwd(x_mid, y, p, seed, x_in=None, keep=None):
+    out = torch.empty_like(x_mid)
+    _call("sr_dropout_add_fwd", [P] * 5 + [L, F32, ULL, P], x_mid.data_ptr(), y.data_ptr(), _lib.ptr(x_in), _lib.ptr(keep),
+          out.data_ptr(), x_mid.numel(), p, seed, _sp())
+    return out
+
+
+def _dropout_add_bwd(g, p, seed, keep=None):
+    dy = torch.empty_like(g)
+    dmid = torch.empty_like(g) if keep is not None else None
+    din = torch.empty_like(g) if keep is not None else None
+    _call("sr_dropout_add_bwd", [P] * 5 + [L, F32, ULL, P], g.data_ptr(), _lib.ptr(keep), dy.data_ptr(), _lib.ptr(dmid),
+          _lib.ptr(din), g.numel(), p, seed, _sp())
+    return dy, dmid, din
+
+
+def iha_mix_weights(mixes, w16, H):
+    """W'[p] = bf16(mix[p]) @ W[p].view(H, -1); falls back to a library bmm for head counts without a kernel."""
+    Pn = mixes.size(0)
+    J = w16.numel() // (Pn * H)
+    out = torch.empty_like(w16)
+    rc = _lib.fn("sr_iha_mix_fwd", [P, P, P, I, I, L, P])(mixes.data_ptr(), w16.data_ptr(), out.data_ptr(), Pn, H, J, _sp())
+    if rc == -7:
+        return torch.bmm(mixes.to(torch.bfloat16), w16.view(Pn, H, J)).view(w16.shape)
+    if rc != 0:
+        raise RuntimeError(f"sr_iha_mix_fwd: launcher returned {rc}")
+    return out
+
+
+def iha_mix_backward(mixes, w16, dwp, grad_w, H):
+    """grad_w (fp32) += bf16(mix)^T @ dW'; returns dmix [P, H, H] fp32."""
+    Pn = mixes.size(0)
+    J = w16.numel() // (Pn * H)
+    dmix = torch.zeros_like(mixes)
+    rc = _lib.fn("sr_iha_mix_bwd", [P, P, P, P, P, I, I, L, P])(mixes.data_ptr(), w16.data_ptr(), dwp.data_ptr(),
+                                                               grad_w.data_ptr(), dmix.data_ptr(), Pn, H, J, _sp())
+    if rc == -7:
+        d3 = dwp.view(Pn, H, J)
+        m16 = mixes.to(torch.bfloat16)
+        dmix = torch.bmm(d3, w16.view(Pn, H, J).transpose(1, 2)).float()
+        grad_w.view(Pn, H, J).add_(torch.bmm(m16.transpose(1, 2), d3))
+        return dmix
+    if rc != 0:
+        raise RuntimeError(f"sr_iha_mix_bwd: launcher returned {rc}")
+    return dmix
+
+
+class _BlockFn(Function):
+    @staticmethod
+    def forward(ctx, x_prev, x0, skip, model, block, i, j, do_mix, ve_lin, window, scale, training):
+        B, T, C = x_prev.shape
+        M = B * T
+        attn, mlp = block.attn, block.mlp
+        H, D = attn.n_head, attn.head_dim
+        eps = float(model.norm_eps)
+        impl = current_impl()
+        xp = x_prev.reshape(M, C)
+        xp = xp if xp.is_contiguous() else xp.contiguous()
+        x0_2 = None
+        if x0 is not None:
+            x0_2 = x0.reshape(M, C)
+            x0_2 = x0_2 if x0_2.is_contiguous() else x0_2.contiguous()
+        sk = None
+        if skip is not None:
+            sk = skip.reshape(M, C)
+            sk = sk if sk.is_contiguous() else sk.contiguous()
+        # ---- lambda mix
+        if do_mix:
+            x = torch.empty_like(xp)
+            rl, xl, sw = model.resid_lambdas, model.x0_lambdas, model.skip_weights
+            _call("sr_lambda_mix_fwd", [P] * 7 + [L, P], xp.data_ptr(), x0_2.data_ptr(), _lib.ptr(sk), x.data_ptr(),
+                  rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i, sw.data_ptr() + 4 * j if sk is not None else 0, xp.numel(), _sp())
+        else:
+            x = xp
+        a = _rmsnorm_fwd(x, eps)
+        # ---- projections
+        ve = gemm(x0_2, ve_lin.fused["w16"]) if ve_lin is not None else None
+        fz = attn.fused
+        mixes = None
+        if attn.use_iha:
+            eye = None
+            if not attn.iha_mix_v:
+                eye = torch.eye(H, device=x.device, dtype=torch.float32)
+            mixes = torch.stack([attn.q_mix.data, attn.k_mix.data, attn.v_mix.data if attn.iha_mix_v else eye])
+            w_qkv = iha_mix_weights(mixes, fz["qkv_w16"], H)
+        else:
+            w_qkv = fz["qkv_w16"]
+        qkv = gemm(a, w_qkv)
+        # ---- gates (tiny [M, H] tensors: library ops)
+        agw = attn.attn_gate.weight.data
+        agate = torch.sigmoid((a[:, :attn.attn_gate_channels] @ agw.to(torch.bfloat16).t()).float())
+        ve_gate = None
+        if ve is not None:
+            vgw = attn.ve_gate.weight.data
+            ve_gate = 2 * torch.sigmoid((a[:, :attn.ve_gate_channels] @ vgw.to(torch.bfloat16).t()).float())
+        # ---- split + value residual + RoPE + QK norm
+        cos, sin = model.rotary.cos, model.rotary.sin
+        cos2, sin2 = cos.view(-1, cos.size(-1)), sin.view(-1, sin.size(-1))
+        q = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=x.device)
+        k, v = torch.empty_like(q), torch.empty_like(q)
+        _call("sr_qkv_prep_fwd", [P] * 8 + [L, I, I, F32, P], qkv.data_ptr(), _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(),
+              sin2.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), M, H, T, eps, _sp())
+        y, attn_saved = impl.fwd(q, k, v, window, scale)
+        y2 = torch.empty_like(y)
+        _call("sr_head_gate_fwd", [P] * 4 + [L, I, L, L, L, I, P], y.data_ptr(), 0, agate.data_ptr(), y2.data_ptr(), M, H,
+              H * D, 0, H * D, 1, _sp())
+        o = gemm(y2.view(M, C), fz["proj_w16"])
+        # ---- residual, MLP
+        p_attn = float(attn.dropout) if training else 0.0
+        p_mlp = float(mlp.dropout) if training else 0.0
+        seed1 = ops.next_dropout_seed() if p_attn > 0 else 0
+        seed2 = ops.next_dropout_seed() if p_mlp > 0 else 0
+        x_mid = _dropout_add_fwd(x, o, p_attn, seed1)
+        n = _rmsnorm_fwd(x_mid, eps)
+        mz = mlp.fused
+        gf = gemm(n, mz["gf_w16"])
+        hdim = gf.size(1) // 2
+        hdn = torch.empty((M, hdim), dtype=torch.bfloat16, device=x.device)
+        _call("sr_swiglu_fwd", [P, P, L, I, P], gf.data_ptr(), hdn.data_ptr(), M, hdim, _sp())
+        mo = gemm(hdn, mz["proj_w16"])
+        keep = None
+        if training and block.drop_prob > 0:
+            keep = (torch.rand((), device=x.device) >= block.drop_prob).float()
+            out = _dropout_add_fwd(x_mid, mo, p_mlp, seed2, x_in=x, keep=keep)
+        else:
+            out = _dropout_add_fwd(x_mid, mo, p_mlp, seed2)
+        ctx.save_for_backward(xp, x0_2 if x0_2 is not None else xp.new_empty(0), sk if sk is not None else xp.new_empty(0))
+        ctx.t = (x, a, ve, mixes, w_qkv, qkv, agate, ve_gate, attn_saved, y, y2, x_mid, n, gf, hdn, keep)
+        ctx.meta = (model, block, i, j, do_mix, ve_lin, p_attn, p_mlp, seed1, seed2, eps, impl, (B, T, C, H, D),
+                    x0 is not None, skip is not None)
+        return out.view(B, T, C)
+
+    @staticmethod
+    def backward(ctx, g_out):
+        xp, x0_2, sk = ctx.saved_tensors
+        x, a, ve, mixes, w_qkv, qkv, agate, ve_gate, attn_saved, y, y2, x_mid, n, gf, hdn, keep = ctx.t
+        model, block, i, j, do_mix, ve_lin, p_attn, p_mlp, seed1, seed2, eps, impl, dims, has_x0, has_skip = ctx.meta
+        ctx.t = None
+        B, T, C, H, D = dims
+        M = B * T
+        attn, mlp = block.attn, block.mlp
+        fz, mz = attn.fused, mlp.fused
+        g = g_out.reshape(M, C)
+        g = g if g.is_contiguous() else g.contiguous()
+        # ---- MLP branch
+        dmo, g_mid, g_in = _dropout_add_bwd(g, p_mlp, seed2, keep)
+        if keep is None:
+            g_mid = g
+        dhdn = gemm(dmo, mz["proj_w16"], b_mn=True)
+        gemm(dmo, hdn, out=mz["proj_grad"], cin=mz["proj_grad"], a_mn=True, b_mn=True, beta=1.0)
+        dgf = torch.empty_like(gf)
+        _call("sr_swiglu_bwd", [P, P, P, L, I, P], gf.data_ptr(), dhdn.data_ptr(), dgf.data_ptr(), M, gf.size(1) // 2, _sp())
+        dn = gemm(dgf, mz["gf_w16"], b_mn=True)
+        gemm(dgf, n, out=mz["gf_grad"], cin=mz["gf_grad"], a_mn=True, b_mn=True, beta=1.0)
+        g_mid_tot = _rmsnorm_bwd(x_mid, dn, g_mid, eps)
+        # ---- attention branch
+        do, _, _ = _dropout_add_bwd(g_mid_tot, p_attn, seed1)
+        dy2 = gemm(do, fz["proj_w16"], b_mn=True)
+        gemm(do, y2.view(M, C), out=fz["proj_grad"], cin=fz["proj_grad"], a_mn=True, b_mn=True, beta=1.0)
+        dy = torch.empty_like(y)
+        dagate = torch.empty((M, H), dtype=torch.float32, device=g.device)
+        _call("sr_head_gate_bwd", [P] * 5 + [L, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), agate.data_ptr(), dy.data_ptr(),
+              dagate.data_ptr(), M, H, H * D, H * D, H * D, _sp())
+        dq, dk, dv = impl.bwd(attn_saved, dy)
+        dqkv = torch.empty_like(qkv)
+        dve = torch.empty((M, C), dtype=torch.bfloat16, device=g.device) if ve is not None else None
+        dvegate = torch.empty((M, H), dtype=torch.float32, device=g.device) if ve is not None else None
+        cos, sin = model.rotary.cos, model.rotary.sin
+        cos2, sin2 = cos.view(-1, cos.size(-1)), sin.view(-1, sin.size(-1))
+        _call("sr_qkv_prep_bwd", [P] * 11 + [L, I, I, F32, P], qkv.data_ptr(), _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(),
+              sin2.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dqkv.data_ptr(), _lib.ptr(dve), _lib.ptr(dvegate),
+              M, H, T, eps, _sp())
+        da = gemm(dqkv, w_qkv, b_mn=True)
+        if mixes is not None:
+            dwp = gemm(dqkv, a, a_mn=True, b_mn=True)
+            dmix = iha_mix_backward(mixes, fz["qkv_w16"], dwp, fz["qkv_grad"], H)
+            attn.q_mix.grad.add_(dmix[0])
+            attn.k_mix.grad.add_(dmix[1])
+            if attn.iha_mix_v:
+                attn.v_mix.grad.add_(dmix[2])
+        else:
+            gemm(dqkv, a, out=fz["qkv_grad"], cin=fz["qkv_grad"], a_mn=True, b_mn=True, beta=1.0)
+        # ---- gates (tiny)
+        nc = attn.attn_gate_channels
+        dz = dagate * agate * (1 - agate)
+        a_s = a[:, :max(nc, attn.ve_gate_channels)].float()
+        attn.attn_gate.weight.grad.addmm_(dz.t(), a_s[:, :nc])
+        da[:, :nc] += (dz @ attn.attn_gate.weight.data.to(torch.bfloat16).float()).to(torch.bfloat16)
+        dx0 = None
+        if ve is not None:
+            vc = attn.ve_gate_channels
+            dzv = dvegate * ve_gate * (1 - 0.5 * ve_gate)
+            attn.ve_gate.weight.grad.addmm_(dzv.t(), a_s[:, :vc])
+            da[:, :vc] += (dzv @ attn.ve_gate.weight.data.to(torch.bfloat16).float()).to(torch.bfloat16)
+            gemm(dve, x0_2, out=ve_lin.fused["grad"], cin=ve_lin.fused["grad"], a_mn=True, b_mn=True, beta=1.0)
+        # ---- back through the first norm and the lambda mix
+        if g_in is not None:
+            g_mid_tot.add_(g_in)
+        g_x = _rmsnorm_bwd(x, da, g_mid_tot, eps)
+        if not do_mix:
+            if ve is not None:
+                dx0 = gemm(dve, ve_lin.fused["w16"], b_mn=True)
+            return (g_x.view(B, T, C), dx0.view(B, T, C) if dx0 is not None else None, None) + (None,) * 9
+        dxp = torch.empty_like(g_x)
+        dx0 = torch.empty_like(g_x)
+        dsk = torch.empty_like(g_x) if has_skip else None
+        dscal = torch.zeros(3, dtype=torch.float32, device=g.device)
+        rl, xl, sw = model.resid_lambdas, model.x0_lambdas, model.skip_weights
+        _call("sr_lambda_mix_bwd", [P] * 11 + [L, P], g_x.data_ptr(), xp.data_ptr(), x0_2.data_ptr(), sk.data_ptr() if has_skip else 0,
+              dxp.data_ptr(), dx0.data_ptr(), _lib.ptr(dsk), rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i,
+              sw.data_ptr() + 4 * j if has_skip else 0, dscal.data_ptr(), g_x.numel(), _sp())
+        rl.grad[i] += dscal[0]
+        xl.grad[i] += dscal[1]
+        if has_skip:
+            sw.grad[j] += dscal[2]
+        if ve is not None:
+            gemm(dve, ve_lin.fused["w16"], out=dx0, cin=dx0, b_mn=True, beta=1.0)
+        return (dxp.view(B, T, C), dx0.view(B, T, C), dsk.view(B, T, C) if dsk is not None else None) + (None,) * 9
+
+
+def block_forward(model, block, x_prev, x0, skip, i, j, do_mix, ve_lin, window, scale):
+    """x_out of layer `i` (lambda mix with skip j when do_mix, then the block) through the fused autograd node."""
+    return _BlockFn.apply(x_prev, x0, skip, model, block, i, j, do_mix, ve_lin, window[0], scale, model.training)
+
+
+def block_supported(model, block) -> bool:
+    """The fused node covers the limited / two-hour / unlimited feature set; XSA and the key offset of the tiny track
+    go through the op-by-op path."""
+    a = block.attn
+    return (not a.use_key_offset) and model.config.xsa_mode == "off" and a.head_dim == 128 and a.fused is not None \
+        and a.fused["qkv_w16"] is not None

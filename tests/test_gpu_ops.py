@@ -321,3 +321,61 @@ def test_model_cuda_path_tracks_cpu_oracle(track):
 def test_graft_smoke():
     import __graft_entry__ as g
     g.smoke()
+
+
+def test_fused_block_node_matches_op_by_op_path():
+    """Same CUDA model, block run as one autograd node vs. op by op: loss and every gradient must agree."""
+    from slowrun_b200.config import track_defaults
+    from slowrun_b200.models.gpt import build_model
+    from slowrun_b200.ops import _lib
+    cfg = track_defaults("limited")
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 4, 256, 2, 2, 256
+    m.dropout, m.stoch_depth = 0.0, 0.0
+    model = build_model(m, "cuda", seed=0)
+    torch.manual_seed(1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if any(s in n for s in ("gate", "mix", "lambdas", "skip")):
+                p.add_(0.05 * torch.randn_like(p))
+    model.arena.refresh_shadows()
+    model.set_dupe_layers(2, 3, 1)
+    idx = torch.randint(0, 50257, (2, 256), device="cuda")
+    tgt = torch.randint(0, 50257, (2, 256), device="cuda")
+    res = {}
+    for fused in (True, False):
+        model.use_fused_blocks = fused
+        model.zero_grad_arena()
+        loss, _ = model(idx, tgt)
+        loss.backward()
+        torch.cuda.synchronize(); _lib.check_status()
+        res[fused] = (loss.item(), {n: (model.arena.head_grad if n == "lm_head.weight" else p.grad).clone()
+                                    for n, p in model.named_parameters()})
+    assert abs(res[True][0] - res[False][0]) < 2e-2, (res[True][0], res[False][0])
+    for n in res[True][1]:
+        a, b = res[True][1][n].float(), res[False][1][n].float()
+        if b.abs().max() == 0:
+            assert a.abs().max() == 0, n
+            continue
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+        assert cos > 0.99, (n, cos)
+        assert abs(a.norm().item() / b.norm().item() - 1) < 0.1, (n, a.norm().item(), b.norm().item())
+
+
+def test_fused_block_with_dropout_and_stochastic_depth_runs():
+    from slowrun_b200.config import track_defaults
+    from slowrun_b200.models.gpt import build_model
+    from slowrun_b200.ops import _lib
+    cfg = track_defaults("limited")
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 4, 256, 2, 2, 128
+    m.stoch_depth = 0.5
+    model = build_model(m, "cuda", seed=0)
+    idx = torch.randint(0, 50257, (2, 128), device="cuda")
+    for _ in range(3):
+        loss, _ = model(idx, idx)
+        loss.backward()
+    torch.cuda.synchronize(); _lib.check_status()
+    assert torch.isfinite(loss)
+    for n, p in model.named_parameters():
+        assert torch.isfinite(p.grad.float()).all(), n
