@@ -1,0 +1,264 @@
+// Collectives fused with their consumers, over NVLink peer memory (plain P2P loads; no multimem, no TMA on remote
+// memory). Every rank maps every peer's symmetric buffers; kernels take a small device array of W base pointers.
+//
+//   peer_barrier          all-ranks barrier on symmetric flag words, monotonic epochs, bounded wait -> status word
+//   muon_pre_multi        gradient reduce-scatter fused with the Muon prologue: the owner of a matrix reads that
+//                         matrix's gradient rows from all W ranks, sums and scales them, updates momentum, applies
+//                         Nesterov + row normalisation and writes the bf16 Newton-Schulz input directly
+//                         (reference: reduce_scatter_tensor then muon_step_fused, train.py:671-683, 603-613)
+//   muon_apply_multi      all-gather of the orthogonalised update fused with the cautious-weight-decay apply: every
+//                         rank reads each owner's bf16 update chunk in place and updates its own fp32 replica and
+//                         bf16 shadow (reference: all_gather_into_tensor of fp32 parameters + copy, train.py:742-760)
+//   reduce_multi          out = sum over ranks of src_r[offset : offset+n]  (row-slice reduce-scatter for the AdamW
+//                         parameters, and the one-shot all-reduce of the packed small-parameter gradients)
+//   gather_multi          pull every other rank's slice of a sharded parameter into the local replica
+#include "sm100_common.cuh"
+
+namespace {
+
+using namespace sr;
+
+constexpr int kMaxWorld = 16;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+
+struct PtrTable {
+  const void* p[kMaxWorld];
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+// flags: on every rank an array uint32[W]; slot s of rank d is written only by rank s.
+__global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_t epoch, int* status) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  uint32_t* remote = reinterpret_cast<uint32_t*>(const_cast<void*>(flags.p[t])) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.p[rank]) + t;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(v - epoch) >= 0) break;
+    if ((++it & 255u) == 0u && globaltimer_ns() - t0 > kWaitLimitNs) {
+      report_error(status, SR_ERR_PEER_TIMEOUT, 900, t);
+      break;
+    }
+  }
+  __threadfence_system();
+}
+
+// One warp per row of the owned stack. G_r points at rank r's full gradient arena of this group; `base` is the element
+// offset of the owned chunk inside it.
+__global__ void muon_pre_multi_kernel(PtrTable G, int world, long base, float* __restrict__ Mom,
+                                      __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r,
+                                      int c, float mu, float gscale) {
+  const long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  if (row >= rows_total) return;
+  const int lane = threadIdx.x & 31;
+  float* m = Mom + row * c;
+  __nv_bfloat16* x = X + row * c;
+  const long off = base + row * c;
+  float ss = 0.f;
+  // pass 1 reduces the row over all ranks and updates the momentum. The Nesterov gradient is needed again after the
+  // row norm is known; it is kept per lane (64 floats cover rows up to 8192 columns) so the peers are read only once.
+  constexpr int kCache = 64;
+  float cache[kCache];
+  const bool fits = c <= kCache * 32;
+  int ci = 0;
+  for (int j = lane * 4; j < c; j += 128, ci += 4) {
+    float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < world; ++p) {
+      const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(G.p[p]) + off + j);
+      gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
+    }
+    gv.x *= gscale; gv.y *= gscale; gv.z *= gscale; gv.w *= gscale;
+    float4 mv = *reinterpret_cast<const float4*>(m + j);
+    mv.x += (1.f - mu) * (gv.x - mv.x); mv.y += (1.f - mu) * (gv.y - mv.y);
+    mv.z += (1.f - mu) * (gv.z - mv.z); mv.w += (1.f - mu) * (gv.w - mv.w);
+    *reinterpret_cast<float4*>(m + j) = mv;
+    const float a = gv.x + mu * (mv.x - gv.x), b = gv.y + mu * (mv.y - gv.y);
+    const float cc = gv.z + mu * (mv.z - gv.z), d = gv.w + mu * (mv.w - gv.w);
+    ss += a * a + b * b + cc * cc + d * d;
+    if (fits) {
+      cache[ci] = a; cache[ci + 1] = b; cache[ci + 2] = cc; cache[ci + 3] = d;
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.f / fmaxf(sqrtf(ss), 1e-7f);
+  float xs = 0.f;
+  ci = 0;
+  for (int j = lane * 4; j < c; j += 128, ci += 4) {
+    float a, b, cc, d;
+    if (fits) {
+      a = cache[ci]; b = cache[ci + 1]; cc = cache[ci + 2]; d = cache[ci + 3];
+    } else {
+      float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < world; ++p) {
+        const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(G.p[p]) + off + j);
+        gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
+      }
+      gv.x *= gscale; gv.y *= gscale; gv.z *= gscale; gv.w *= gscale;
+      const float4 mv = *reinterpret_cast<const float4*>(m + j);
+      a = gv.x + mu * (mv.x - gv.x); b = gv.y + mu * (mv.y - gv.y);
+      cc = gv.z + mu * (mv.z - gv.z); d = gv.w + mu * (mv.w - gv.w);
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a * inv, b * inv);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(cc * inv, d * inv);
+    *reinterpret_cast<__nv_bfloat162*>(x + j) = lo;
+    *reinterpret_cast<__nv_bfloat162*>(x + j + 2) = hi;
+    const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
+    xs += l.x * l.x + l.y * l.y + h.x * h.x + h.y * h.y;
+  }
+  xs = warp_sum(xs);
+  if (lane == 0) atomicAdd(sumsq + row / r, xs);
+}
+
+__global__ void fnorm_scale_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__ sumsq, long per_mat,
+                                   long total) {
+  for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 2; i < total; i += (long)gridDim.x * blockDim.x * 2) {
+    const float s = 1.f / (1.02f * sqrtf(sumsq[i / per_mat]) + 1e-6f);
+    const float2 v = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(X + i));
+    *reinterpret_cast<__nv_bfloat162*>(X + i) = __floats2bfloat162_rn(v.x * s, v.y * s);
+  }
+}
+
+// U_r points at rank r's update chunk [chunk_elems]; element i of the stack belongs to rank i / chunk_elems.
+__global__ void muon_apply_multi_kernel(float* __restrict__ P, PtrTable U, long chunk_elems,
+                                        __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total) {
+  for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += (long)gridDim.x * blockDim.x * 4) {
+    const long owner = i / chunk_elems;
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(U.p[owner]) + (i - owner * chunk_elems);
+    float4 p = *reinterpret_cast<float4*>(P + i);
+    const uint2 raw = *reinterpret_cast<const uint2*>(u);
+    const float2 u0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 u1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    p.x -= bf16_round(lr_b * u0.x) + ((u0.x * p.x >= 0.f) ? lrwd_b * p.x : 0.f);
+    p.y -= bf16_round(lr_b * u0.y) + ((u0.y * p.y >= 0.f) ? lrwd_b * p.y : 0.f);
+    p.z -= bf16_round(lr_b * u1.x) + ((u1.x * p.z >= 0.f) ? lrwd_b * p.z : 0.f);
+    p.w -= bf16_round(lr_b * u1.y) + ((u1.y * p.w >= 0.f) ? lrwd_b * p.w : 0.f);
+    *reinterpret_cast<float4*>(P + i) = p;
+    if (shadow != nullptr) {
+      *reinterpret_cast<__nv_bfloat162*>(shadow + i) = __floats2bfloat162_rn(p.x, p.y);
+      *reinterpret_cast<__nv_bfloat162*>(shadow + i + 2) = __floats2bfloat162_rn(p.z, p.w);
+    }
+  }
+}
+
+template <bool BF16>
+__global__ void reduce_multi_kernel(PtrTable src, int world, long offset, float* __restrict__ out, long n) {
+  for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long)gridDim.x * blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i + 3 < n) {
+      for (int p = 0; p < world; ++p) {
+        if (BF16) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(src.p[p]) + offset + i);
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+          acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+        } else {
+          const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[p]) + offset + i);
+          acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+        }
+      }
+      *reinterpret_cast<float4*>(out + i) = acc;
+    } else {
+      for (long j = i; j < n; ++j) {
+        float a = 0.f;
+        for (int p = 0; p < world; ++p)
+          a += BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src.p[p])[offset + j])
+                    : reinterpret_cast<const float*>(src.p[p])[offset + j];
+        out[j] = a;
+      }
+    }
+  }
+}
+
+// bufs[r] = rank r's replica (same layout everywhere); copy slice s (bytes [s*slice, (s+1)*slice)) from rank s for all s != rank
+__global__ void gather_multi_kernel(PtrTable bufs, int world, int rank, long slice_bytes) {
+  const long vecs = slice_bytes / 16;
+  const int s = blockIdx.y;
+  if (s == rank) return;
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(bufs.p[s]) + (long)s * slice_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(const_cast<void*>(bufs.p[rank])) + (long)s * slice_bytes);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+inline int grid_for(long n, int per_block) {
+  long b = (n + per_block - 1) / per_block;
+  const long cap = 148L * 8;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
+
+inline bool fill(PtrTable& t, const unsigned long long* ptrs, int world) {
+  if (world < 1 || world > kMaxWorld) return false;
+  for (int i = 0; i < world; ++i) t.p[i] = reinterpret_cast<const void*>(ptrs[i]);
+  return true;
+}
+
+}  // namespace
+
+// `ptrs` arguments are HOST arrays of `world` device addresses (one per rank, this rank's own included).
+extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, int world, unsigned int epoch, int* status,
+                               cudaStream_t s) {
+  PtrTable t;
+  if (!fill(t, flag_ptrs, world)) return -2;
+  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, epoch, status);
+  return rc();
+}
+
+extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, int world, long base, float* Mom, void* X,
+                                 float* sumsq, int n, int r, int c, float mu, float gscale, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (c % 4) return -2;
+  PtrTable t;
+  if (!fill(t, g_ptrs, world)) return -2;
+  const long rows = (long)n * r;
+  cudaMemsetAsync(sumsq, 0, sizeof(float) * n, s);
+  muon_pre_multi_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(
+      t, world, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
+  const long total = rows * c;
+  fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total);
+  return rc();
+}
+
+extern "C" int sr_muon_apply_multi(float* P, const unsigned long long* u_ptrs, int world, long chunk_elems, void* shadow,
+                                   long total, float lr_b, float lrwd_b, cudaStream_t s) {
+  if (total <= 0) return 0;
+  if (total % 4 || chunk_elems % 4) return -2;
+  PtrTable t;
+  if (!fill(t, u_ptrs, world)) return -2;
+  muon_apply_multi_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
+  return rc();
+}
+
+extern "C" int sr_reduce_multi(const unsigned long long* src_ptrs, int world, long offset, float* out, long n,
+                               int src_bf16, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (offset % 4) return -2;
+  PtrTable t;
+  if (!fill(t, src_ptrs, world)) return -2;
+  if (src_bf16)
+    reduce_multi_kernel<true><<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(t, world, offset, out, n);
+  else
+    reduce_multi_kernel<false><<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(t, world, offset, out, n);
+  return rc();
+}
+
+extern "C" int sr_gather_multi(const unsigned long long* buf_ptrs, int world, int rank, long slice_bytes, cudaStream_t s) {
+  if (slice_bytes <= 0) return 0;
+  if (slice_bytes % 16) return -2;
+  PtrTable t;
+  if (!fill(t, buf_ptrs, world)) return -2;
+  dim3 grid(grid_for(slice_bytes / 16, kThreads) / 2 + 1, world);
+  gather_multi_kernel<<<grid, kThreads, 0, s>>>(t, world, rank, slice_bytes);
+  return rc();
+}

@@ -322,10 +322,10 @@ class GPT(nn.Module):
         return 6 * (nparams - exclude) + attn
 
     # ------------------------------------------------------------------ CUDA preparation
-    def finalize(self, world_size: int = 1):
+    def finalize(self, world_size: int = 1, alloc=None):
         """Move parameters and gradients into stacked arenas (plus bf16 shadows and fused operand views on CUDA)."""
         from ..optim.arena import ParamArena
-        self.arena = ParamArena(self, world_size)
+        self.arena = ParamArena(self, world_size, alloc)
         return self
 
     def zero_grad_arena(self):
@@ -523,7 +523,7 @@ class GPT(nn.Module):
         return loss, {"lm_loss": lm_loss, "mtp_loss": mtp_loss}
 
 
-def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_size: int = 1) -> GPT:
+def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_size: int = 1, alloc=None) -> GPT:
     """Construct on `device`, initialise with the reference's RNG call order, and lay out the arenas."""
     device = torch.device(device)
     if seed is not None:
@@ -538,5 +538,5 @@ def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_siz
         from ..ops.attention import current_attention, install_default_attention
         if current_attention() is None:
             install_default_attention()
-    model.finalize(world_size)
+    model.finalize(world_size, alloc)
     return model

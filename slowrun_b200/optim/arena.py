@@ -22,7 +22,7 @@ SMALL_NUMEL = 1024
 
 
 class MuonGroupArena:
-    def __init__(self, shape, params: List[torch.nn.Parameter], world_size: int, make_shadow: bool):
+    def __init__(self, shape, params: List[torch.nn.Parameter], world_size: int, make_shadow: bool, zeros=None):
         self.shape = tuple(shape)
         self.params = params
         n = len(params)
@@ -32,7 +32,7 @@ class MuonGroupArena:
         self.chunk = (n + world_size - 1) // world_size
         self.n_pad = self.chunk * world_size
         self.P = torch.empty((n, r, c), dtype=torch.float32, device=dev)
-        self.G = torch.zeros((self.n_pad, r, c), dtype=torch.float32, device=dev)
+        self.G = (zeros or (lambda sh, dt: torch.zeros(sh, dtype=dt, device=dev)))((self.n_pad, r, c), torch.float32)
         self.W16 = torch.empty((n, r, c), dtype=torch.bfloat16, device=dev) if make_shadow else None
         for i, p in enumerate(params):
             self.P[i].copy_(p.data)
@@ -49,25 +49,40 @@ class MuonGroupArena:
 
 
 class ParamArena:
-    def __init__(self, model, world_size: int = 1):
+    def __init__(self, model, world_size: int = 1, alloc=None):
+        """`alloc(shape, dtype)` (optional) returns zero-filled peer-mapped memory; everything another rank has to read
+        (gradients, the sharded AdamW parameters) is then placed there."""
         self.model = model
         self.world_size = world_size
         dev = model.get_device()
         cuda = dev.type == "cuda"
+        self.symmetric = alloc is not None
+
+        def zeros(shape, dtype):
+            if alloc is not None:
+                return alloc(tuple(shape), dtype)
+            return torch.zeros(tuple(shape), dtype=dtype, device=dev)
+
+        def repoint(p):
+            if alloc is not None:
+                buf = alloc(tuple(p.shape), p.dtype)
+                buf.copy_(p.data)
+                p.data = buf
         self.groups: Dict[tuple, MuonGroupArena] = {}
         for shape, ps in muon_shape_groups(model):
             big = cuda and shape[0] % 8 == 0 and shape[1] % 8 == 0 and shape[1] >= 64 and shape[0] >= 64
-            self.groups[tuple(shape)] = MuonGroupArena(shape, ps, world_size, make_shadow=big)
+            self.groups[tuple(shape)] = MuonGroupArena(shape, ps, world_size, make_shadow=big, zeros=zeros)
         # lm head
         head = model.lm_head.weight
         self.head_w16 = None
+        repoint(head)
         if head.dtype == torch.float32:
-            head.grad = torch.zeros_like(head)
+            head.grad = zeros(head.shape, torch.float32)
             self.head_grad = head.grad
             if cuda:
                 self.head_w16 = head.data.to(torch.bfloat16)
         else:
-            self.head_grad = torch.zeros(head.shape, dtype=torch.float32, device=dev)
+            self.head_grad = zeros(head.shape, torch.float32)
         # everything else keeps an ordinary, persistently allocated .grad; small ones share one flat buffer
         muon_ids = {id(p) for g in self.groups.values() for p in g.params}
         rest = [p for p in model.parameters() if id(p) not in muon_ids and p is not head]
@@ -75,7 +90,7 @@ class ParamArena:
         self.small_params = small
         total = sum(p.numel() for p in small)
         self.small_P = torch.empty(total, dtype=torch.float32, device=dev)
-        self.small_grads = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.small_grads = zeros((max(total, 4),), torch.float32)[:total] if total > 0 else torch.zeros(0, device=dev)
         self.small_offsets = {}
         off = 0
         for p in small:
@@ -87,7 +102,8 @@ class ParamArena:
             off += n
         self.other_params = [p for p in rest if not (p.numel() < SMALL_NUMEL and p.dtype == torch.float32)]
         for p in self.other_params:
-            p.grad = torch.zeros_like(p)
+            repoint(p)
+            p.grad = zeros(p.shape, p.dtype)
         if cuda:
             self._wire_fused_views()
 

@@ -142,6 +142,7 @@ class ShardedMuonAdamW:
         self.device = dev
         self.state = {}
         self.step_count = 0
+        self.fused = bool(getattr(comm, "fused", False)) and self.world > 1 and self.cuda and self.arena.symmetric
         if self.arena.world_size != self.world:
             raise ValueError(f"arena was laid out for world size {self.arena.world_size}, comm has {self.world}")
         self._init_state()
@@ -156,9 +157,11 @@ class ShardedMuonAdamW:
                 st = dict(arena=ga,
                           momentum=torch.zeros((ga.chunk, r, c), dtype=torch.float32, device=dev),
                           second=torch.zeros((ga.chunk, r, 1) if r >= c else (ga.chunk, 1, c), dtype=torch.float32, device=dev),
-                          grad_chunk=torch.empty((ga.chunk, r, c), dtype=torch.float32, device=dev) if W > 1 else None,
-                          U=torch.zeros((ga.chunk, r, c), dtype=torch.bfloat16, device=dev),
-                          U_all=torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev) if W > 1 else None)
+                          grad_chunk=torch.empty((ga.chunk, r, c), dtype=torch.float32, device=dev) if (W > 1 and not self.fused) else None,
+                          U=(self.comm.alloc((ga.chunk, r, c), torch.bfloat16) if (self.fused and ga.W16 is not None)
+                             else torch.zeros((ga.chunk, r, c), dtype=torch.bfloat16, device=dev)),
+                          U_all=torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev)
+                          if (W > 1 and not (self.fused and ga.W16 is not None)) else None)
                 if self.cuda and ga.W16 is not None:
                     st["X"] = torch.empty((ga.chunk, r, c), dtype=torch.bfloat16, device=dev)
                     st["ws"] = _NSWorkspace(ga.chunk, r, c, dev)
@@ -187,6 +190,8 @@ class ShardedMuonAdamW:
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self):
+        if self.fused:
+            return self._step_fused()
         self.step_count += 1
         W, rank, comm = self.world, self.rank, self.comm
         gscale = 1.0 / W
@@ -222,6 +227,113 @@ class ShardedMuonAdamW:
         for item in pending:
             item()
 
+    # ------------------------------------------------------------------ fused peer-memory step
+    @torch.no_grad()
+    def _step_fused(self):
+        """Same update as `step()`, with every collective replaced by a kernel that reads the peers' symmetric buffers
+        and consumes the data in the same pass (csrc/comm_fused.cu). Two device-side barriers bracket the work:
+        A = every rank's gradients are final; B = every owner's update chunk / parameter slice is final."""
+        import ctypes
+        self.step_count += 1
+        W, rank, comm, arena = self.world, self.rank, self.comm, self.arena
+        gscale = 1.0 / W
+        head = self.model.lm_head.weight
+        cvp = ctypes.c_void_p
+        comm.device_barrier()                                                                      # A
+        small_sum = None
+        if arena.small_grads.numel() > 0:
+            if "small_sum" not in self.state:
+                self.state["small_sum"] = torch.empty(arena.small_grads.numel(), dtype=torch.float32, device=self.device)
+            small_sum = self.state["small_sum"]
+            comm.reduce_from_peers(arena.small_grads, 0, small_sum)
+        gathers, applies = [], []
+        for g in self.param_groups:
+            if g["kind"] == "muon":
+                st = self.state[g["name"]]
+                ga = st["arena"]
+                r, c = ga.shape
+                n_own = self.num_owned(ga)
+                mu, beta2, ns = float(g["momentum"]), float(g["beta2"]), int(g["ns_steps"])
+                base = rank * ga.chunk * r * c
+                if n_own > 0:
+                    if "X" in st:
+                        X = st["X"][:n_own]
+                        sc = st["scratch"]
+                        rc = _lib.fn("sr_muon_pre_multi", [cvp, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
+                            ctypes.cast(comm.peer_ptrs(ga.G), cvp), W, base, st["momentum"].data_ptr(), X.data_ptr(),
+                            st["sumsq"].data_ptr(), n_own, r, c, mu, gscale, _lib.stream_ptr())
+                        _lib.check_rc(rc, "sr_muon_pre_multi")
+                        Xo = newton_schulz_cuda(X, ns, st["ws"])
+                        rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
+                            Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), st["U"].data_ptr(),
+                            n_own, r, c, _bf16(beta2), _lib.stream_ptr())
+                        _lib.check_rc(rc, "sr_muon_post")
+                    else:
+                        tmp = torch.empty((n_own, r, c), dtype=torch.float32, device=self.device)
+                        comm.reduce_from_peers(ga.G, base, tmp)
+                        tmp.mul_(gscale)
+                        st["U"][:n_own].copy_(muon_update_ref(tmp, st["momentum"][:n_own], st["second"][:n_own], mu, beta2, ns))
+                applies.append((g, st, ga))
+            else:
+                smalls = [p for p in g["params"] if self.state[id(p)]["small"]]
+                if smalls:
+                    self._adamw_small(g, smalls, small_sum, gscale)
+                for p in g["params"]:
+                    st = self.state[id(p)]
+                    if st["small"]:
+                        continue
+                    grad = self._grad_of(p)
+                    if st["sharded"]:
+                        rows = st["rows"]
+                        per_row = p.numel() // p.shape[0]
+                        if "gslice32" not in st:
+                            st["gslice32"] = torch.empty((rows,) + tuple(p.shape[1:]), dtype=torch.float32, device=self.device)
+                        comm.reduce_from_peers(grad, rank * rows * per_row, st["gslice32"])
+                        self._adamw_launch(p.data[rank * rows:(rank + 1) * rows], st["gslice32"], st["m"], st["v"], None, g, gscale)
+                        gathers.append(p)
+                    else:
+                        if "gfull32" not in st:
+                            st["gfull32"] = torch.empty(p.shape, dtype=torch.float32, device=self.device)
+                        comm.reduce_from_peers(grad, 0, st["gfull32"])
+                        shadow = arena.head_w16 if (p is head and arena.head_w16 is not None) else None
+                        self._adamw_launch(p.data, st["gfull32"], st["m"], st["v"], shadow, g, gscale)
+        comm.device_barrier()                                                                      # B
+        for g, st, ga in applies:
+            r, c = ga.shape
+            lr_eff = float(g["lr"]) * max(1.0, r / c) ** 0.5
+            wd = float(g["weight_decay"])
+            if ga.W16 is not None:
+                lr_b = _bf16(lr_eff)
+                rc = _lib.fn("sr_muon_apply_multi", [cvp, cvp, c_int, c_long, cvp, c_long, c_float, c_float, cvp])(
+                    ga.P.data_ptr(), ctypes.cast(comm.peer_ptrs(st["U"]), cvp), W, ga.chunk * r * c, ga.W16.data_ptr(),
+                    ga.P.numel(), lr_b, _bf16(lr_b * _bf16(wd)), _lib.stream_ptr())
+                _lib.check_rc(rc, "sr_muon_apply_multi")
+            else:
+                comm.all_gather(st["U_all"], st["U"], async_op=False)
+                muon_apply_ref(ga.P, st["U_all"][:ga.n], lr_eff, wd)
+        for p in gathers:
+            comm.gather_slices(p.data)
+            if p is head and arena.head_w16 is not None:
+                arena.head_w16.copy_(p.data)
+
+    def _adamw_small(self, grp, smalls, grads_flat, gscale):
+        """One launch per run of parameters that are adjacent in the flat small-parameter buffer."""
+        arena = self.arena
+        segs = sorted(arena.small_offsets[id(p)] for p in smalls)
+        merged = []
+        for off, n in segs:
+            if merged and merged[-1][0] + merged[-1][1] == off:
+                merged[-1][1] += n
+            else:
+                merged.append([off, n])
+        if "small_m" not in self.state:
+            self.state["small_m"] = torch.zeros_like(arena.small_P)
+            self.state["small_v"] = torch.zeros_like(arena.small_P)
+        for off, n in merged:
+            sl = slice(off, off + n)
+            self._adamw_launch(arena.small_P[sl], grads_flat[sl], self.state["small_m"][sl], self.state["small_v"][sl],
+                               None, grp, gscale)
+
     # ------------------------------------------------------------------ AdamW
     def _adamw_launch(self, p_t, g_t, m_t, v_t, shadow, grp, gscale):
         lr, wd = float(grp["lr"]), float(grp["weight_decay"])
@@ -245,21 +357,7 @@ class ShardedMuonAdamW:
         head = self.model.lm_head.weight
         smalls = [p for p in grp["params"] if self.state[id(p)]["small"]]
         if smalls:
-            # merge parameters that are adjacent in the flat small-parameter buffer into one launch
-            segs = sorted(arena.small_offsets[id(p)] for p in smalls)
-            merged = []
-            for off, n in segs:
-                if merged and merged[-1][0] + merged[-1][1] == off:
-                    merged[-1][1] += n
-                else:
-                    merged.append([off, n])
-            if "small_m" not in self.state:
-                self.state["small_m"] = torch.zeros_like(arena.small_P)
-                self.state["small_v"] = torch.zeros_like(arena.small_P)
-            for off, n in merged:
-                sl = slice(off, off + n)
-                self._adamw_launch(arena.small_P[sl], arena.small_grads[sl], self.state["small_m"][sl],
-                                   self.state["small_v"][sl], None, grp, gscale)
+            self._adamw_small(grp, smalls, arena.small_grads, gscale)
         for p in grp["params"]:
             st = self.state[id(p)]
             if st["small"]:

@@ -1,0 +1,97 @@
+"""Peer-memory collectives: the fused counterpart of `TorchComm` for single-node multi-GPU jobs.
+
+Buffers that other ranks must read (gradient arenas, update chunks, sharded AdamW parameters, flag words) are
+allocated through `torch.distributed._symmetric_memory`, which maps every rank's allocation into every other rank's
+address space over NVLink. The kernels in `csrc/comm_fused.cu` then read peers directly with plain loads, fused
+with the arithmetic that consumes the data (see `ShardedMuonAdamW._step_fused`). NCCL stays available through the
+inherited `TorchComm` methods for everything that is not on the hot path (epoch sync, evaluation sums, broadcasts).
+
+The reference has no such layer: all of its gradient traffic is NCCL reduce_scatter / all_gather / all_reduce calls
+(train.py:656-760).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from .comm import TorchComm
+
+ULL = ctypes.c_ulonglong
+
+
+class FusedComm(TorchComm):
+    name = "fused-p2p"
+    fused = True
+
+    def __init__(self, group=None):
+        super().__init__(group)
+        if not self.active:
+            raise RuntimeError("FusedComm needs an initialised multi-rank process group")
+        if not torch.cuda.is_available():
+            raise RuntimeError("FusedComm needs CUDA")
+        import torch.distributed._symmetric_memory as symm
+        self._symm = symm
+        self._pg = group if group is not None else dist.group.WORLD
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._allocs = []          # (base address, bytes, handle)
+        self._ptr_cache = {}
+        self.epoch = 0
+        self.flags = self.alloc((64,), torch.int32)
+        self.flag_ptrs = self.peer_ptrs(self.flags)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------ symmetric allocation
+    def alloc(self, shape, dtype) -> torch.Tensor:
+        """Zero-filled tensor mapped by every rank (collective call: all ranks must allocate in the same order)."""
+        t = self._symm.empty(tuple(shape), dtype=dtype, device=self.device)
+        t.zero_()
+        hdl = self._symm.rendezvous(t, self._pg)
+        self._allocs.append((t.data_ptr(), t.numel() * t.element_size(), hdl))
+        return t
+
+    def peer_ptrs(self, t: torch.Tensor):
+        """ctypes array with the address of `t` (or of a view into an allocated tensor) on every rank."""
+        key = (t.data_ptr(), t.numel())
+        arr = self._ptr_cache.get(key)
+        if arr is not None:
+            return arr
+        a = t.data_ptr()
+        for base, nbytes, hdl in self._allocs:
+            if base <= a < base + max(nbytes, 1):
+                ptrs = list(hdl.buffer_ptrs)
+                mine = ptrs[hdl.rank]
+                off = a - mine
+                if off < 0:
+                    raise RuntimeError("symmetric allocation does not start at the handle's buffer pointer")
+                arr = (ULL * self.world)(*[int(p) + off for p in ptrs])
+                self._ptr_cache[key] = arr
+                return arr
+        raise KeyError("tensor was not allocated through FusedComm.alloc")
+
+    # ------------------------------------------------------------------ device-side barrier
+    def device_barrier(self):
+        """All ranks' preceding work on the current stream is complete and visible before any rank proceeds."""
+        self.epoch += 1
+        rc = _lib.fn("sr_peer_barrier", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p])(
+            ctypes.cast(self.flag_ptrs, ctypes.c_void_p), self.rank, self.world, self.epoch,
+            _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_peer_barrier")
+
+    # ------------------------------------------------------------------ fused primitives
+    def reduce_from_peers(self, src: torch.Tensor, offset: int, out: torch.Tensor):
+        """out[i] = sum_r src_r[offset + i], fp32 result; src is a symmetric fp32 or bf16 tensor."""
+        rc = _lib.fn("sr_reduce_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_long, ctypes.c_int, ctypes.c_void_p])(
+            ctypes.cast(self.peer_ptrs(src), ctypes.c_void_p), self.world, offset, out.data_ptr(), out.numel(),
+            int(src.dtype == torch.bfloat16), _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_reduce_multi")
+
+    def gather_slices(self, buf: torch.Tensor):
+        """Every rank owns slice `rank` of `buf` along dim 0; pull the other ranks' slices from their replicas."""
+        slice_bytes = buf.numel() * buf.element_size() // self.world
+        rc = _lib.fn("sr_gather_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_long, ctypes.c_void_p])(
+            ctypes.cast(self.peer_ptrs(buf), ctypes.c_void_p), self.world, self.rank, slice_bytes, _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_gather_multi")

@@ -55,8 +55,9 @@ class Trainer:
         self.quiet = quiet
         c = cfg
         seed = c.seed if c.track == "unlimited" else 42
-        self.model = build_model(c.model, self.device, seed=seed, world_size=info.world_size)
         self.comm = make_comm(c, info)
+        self.model = build_model(c.model, self.device, seed=seed, world_size=info.world_size,
+                                 alloc=self.comm.alloc if getattr(self.comm, "fused", False) else None)
         self.param_groups = build_param_groups(self.model, c)
         self.optimizer = ShardedMuonAdamW(self.model, self.param_groups, self.comm)
         train_path = c.input_bin or os.path.join(c.data_dir, "fineweb_train.pt")
