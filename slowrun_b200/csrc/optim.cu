@@ -295,3 +295,69 @@ extern "C" int sr_cast_f32_to_bf16(const float* src, void* dst, long n, cudaStre
   cast_f32_to_bf16_kernel<<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), n);
   return rc();
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of sr_muon_post (declared in no_alloc.h; no counterpart in the reference).
+//
+// sr_muon_post needs two fp32 work arrays of n*len elements (per-row or per-column mean squares and the resulting
+// scale factors) that its caller has to allocate on the device. Some callers cannot do that: a step that runs inside a
+// host framework whose caching allocator must not be re-entered (an allocator hook, a gradient-ready callback fired
+// from another library's thread), or a process whose device memory is fully handed out up front and that has no
+// cudaMalloc budget left. For them the work arrays live in the file-scope device array below, which every GPU that
+// loads this library keeps resident until the process exits (2 * kNoAllocMaxElems * 4 bytes = 2 MiB).
+//
+// Rules of use:
+//  * n * max(r, c) (row mode: n * r; column mode: n * c) must not exceed sr_muon_post_noalloc_max_elems(); larger
+//    problems are refused with SR_NOALLOC_TOO_LARGE and nothing is launched.
+//  * The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with that device
+//    current) and remembers it; make that first call outside of any stream capture.
+//  * All calls share the one array and it keeps whatever the last call left in it. What has to start at zero (the
+//    column sums) is cleared on the caller's stream before use. Two calls whose kernels overlap on the GPU (different
+//    streams, no ordering between them) race on the array: order them.
+//  * No cudaMalloc, cudaFree or allocating library routine is called on any path of this function.
+constexpr long kNoAllocMaxElems = 1L << 18;
+static __device__ __align__(256) float g_noalloc_scratch[2 * kNoAllocMaxElems];
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+
+enum { SR_NOALLOC_TOO_LARGE = -8, SR_NOALLOC_NO_SYMBOL = -9, SR_NOALLOC_BAD_DEVICE = -10 };
+
+extern "C" long sr_muon_post_noalloc_max_elems() { return kNoAllocMaxElems; }
+
+extern "C" int sr_muon_post_noalloc(const void* X, float* S, void* U, int n, int r, int c, float beta2,
+                                    cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (c % 4) return -2;
+  const int row_mode = r >= c;
+  const int len = row_mode ? r : c;
+  if ((long)n * len > kNoAllocMaxElems) return SR_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return SR_NOALLOC_BAD_DEVICE;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // In host code the array's name is only a stand-in; the kernels need its device address on THIS device.
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return SR_NOALLOC_NO_SYMBOL;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* vmean = g_noalloc_ptr[dev];
+  float* fs = vmean + kNoAllocMaxElems;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(X);
+  if (row_mode) {
+    const long rows = (long)n * r;
+    muon_rowstat_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(x, vmean, rows, c);
+  } else {
+    if (cudaMemsetAsync(vmean, 0, sizeof(float) * (long)n * c, s) != cudaSuccess) return -5;
+    int slices = r / 128;
+    if (slices < 1) slices = 1;
+    if (slices > 32) slices = 32;
+    dim3 grid((c / 2 + 127) / 128, n, slices);
+    muon_colstat_kernel<<<grid, 128, 0, s>>>(x, vmean, n, r, c);
+  }
+  const int n_red = row_mode ? c : r;
+  muon_finalize_kernel<<<n, kThreads, 0, s>>>(vmean, S, fs, len, n_red, beta2);
+  const long total = (long)n * r * c;
+  muon_scale_update_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(x, fs, reinterpret_cast<__nv_bfloat16*>(U), r, c, row_mode, total);
+  return rc();
+}
