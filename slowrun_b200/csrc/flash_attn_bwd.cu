@@ -1,0 +1,346 @@
+// Flash attention backward for sm_100a (same problem as flash_attn_fwd.cu): dQ, dK, dV from dO, Q, K, V, O, LSE.
+//
+// One CTA per (batch*head, 128-key tile j): K_j and V_j stay in shared memory, the CTA walks the query tiles i that can
+// see them. Per query tile, five tcgen05 products with fp32 accumulators in TMEM:
+//     S  = Q_i K_j^T            dP = dO_i V_j^T                     (both operands K-major)
+//     dV += P^T dO_i            dK += dS^T Q_i                      (both operands MN-major views of row-major tiles)
+//     dQ_i = dS K_j                                                 (A K-major, B MN-major)
+// with P = exp(scale*S - lse) and dS = P * (dP - delta) * scale formed by the compute warps (thread = query row) and
+// written as bf16 into 128B-swizzled shared-memory tiles; the same dS tile is read K-major for dQ and MN-major for dK.
+// dV/dK accumulate in TMEM across the query loop; dQ tiles are added into an fp32 global accumulator with vector
+// reductions and converted to bf16 by a second kernel. delta = rowsum(dO * O) comes from a small pre-pass.
+// Warp roles (192 threads): warp 0 TMA, warp 1 MMA issuer + TMEM owner, warps 2..5 compute / epilogue.
+#include "sm100_common.cuh"
+
+namespace sr_attn {
+int encode_bthd(CUtensorMap* map, const void* ptr, int B, int T, int H, long ld_t, int rows);
+}
+
+namespace {
+
+using namespace sr;
+
+constexpr int BQ = 128, BKV = 128, D = 128;
+constexpr int kThreads = 192;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;
+constexpr uint32_t kHalfBytes = 128 * 128;
+constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;   // K, V, Q, dO, P, dS
+
+struct BwdParams {
+  const float* lse;      // [B, H, T]
+  const float* delta;    // [B, H, T]
+  float* dq_acc;         // [B, T, H, D] fp32
+  __nv_bfloat16* dk;     // [B, T, H, D]
+  __nv_bfloat16* dv;
+  int B, T, H, window;
+  float scale, scale_log2;
+  int* status;
+};
+
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (b, t, h)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                  float* __restrict__ delta, int B, int T, int H) {
+  const long wid = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (wid >= (long)B * T * H) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 a = *reinterpret_cast<const uint2*>(dO + wid * D + lane * 4);
+  const uint2 o = *reinterpret_cast<const uint2*>(O + wid * D + lane * 4);
+  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  const float2 o0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o.x));
+  const float2 o1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o.y));
+  float s = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) {
+    const long bt = wid / H;
+    const int h = (int)(wid - bt * H);
+    const long b = bt / T;
+    const int t = (int)(bt - b * T);
+    delta[(b * H + h) * T + t] = s;
+  }
+}
+
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long n4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(acc)[i];
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+    reinterpret_cast<uint2*>(dq)[i] = o;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                 const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTileBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes;
+  uint8_t* sdO = smem + 3 * kTileBytes;
+  uint8_t* sP = smem + 4 * kTileBytes;
+  uint8_t* sdS = smem + 5 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint64_t* kv_full = bars;          // 1
+  uint64_t* qdo_full = bars + 1;     // 1
+  uint64_t* qdo_empty = bars + 2;    // 1  (tcgen05.commit after the products that read Q_i / dO_i)
+  uint64_t* sdp_full = bars + 3;     // 1  S and dP ready
+  uint64_t* pds_full = bars + 4;     // 128 arrivals: P and dS written
+  uint64_t* dq_full = bars + 5;      // 1  dQ tile ready (also: dV/dK products of this tile issued and done)
+  uint64_t* dq_read = bars + 6;      // 128 arrivals: dQ tile consumed, S columns free
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh - b * p.H;
+  const int k0 = j * BKV;
+  const int n_qt = (p.T + BQ - 1) / BQ;
+  const int i_lo = j;   // BQ == BKV: the diagonal tile
+  int i_hi = n_qt - 1;
+  if (p.window >= 0) i_hi = min(i_hi, (min(k0 + BKV - 1, p.T - 1) + p.window) / BQ);
+  const int n_q = i_hi - i_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+  const uint32_t tdQ = tS;   // the S columns are reused for the dQ tile once S has been consumed
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
+      tma_load_4d(sK, &map_k, kv_full, 0, h, k0, b);
+      tma_load_4d(sK + kHalfBytes, &map_k, kv_full, 64, h, k0, b);
+      tma_load_4d(sV, &map_v, kv_full, 0, h, k0, b);
+      tma_load_4d(sV + kHalfBytes, &map_v, kv_full, 64, h, k0, b);
+      for (int it = 0; it < n_q; ++it) {
+        if (!mbar_wait(qdo_empty, (it & 1u) ^ 1u, abort_flag, p.status, 2100)) break;
+        const int q0 = (i_lo + it) * BQ;
+        mbar_arrive_expect_tx(qdo_full, 2 * kTileBytes);
+        tma_load_4d(sQ, &map_q, qdo_full, 0, h, q0, b);
+        tma_load_4d(sQ + kHalfBytes, &map_q, qdo_full, 64, h, q0, b);
+        tma_load_4d(sdO, &map_do, qdo_full, 0, h, q0, b);
+        tma_load_4d(sdO + kHalfBytes, &map_do, qdo_full, 64, h, q0, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t id_kk = make_idesc(1, 1, 0, 0, 128, 128);   // K-major x K-major
+      const uint32_t id_mm = make_idesc(1, 1, 1, 1, 128, 128);   // MN-major x MN-major
+      const uint32_t id_km = make_idesc(1, 1, 0, 1, 128, 128);   // K-major x MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
+                     adS = smem_u32(sdS);
+      auto kmaj = [&](uint32_t base, int k) { return make_smem_desc_sw128(base + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024); };
+      auto mnmaj = [&](uint32_t base, int k) { return make_smem_desc_sw128(base + k * 2048, kHalfBytes, 1024); };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 2200);
+      for (int it = 0; it < n_q && ok; ++it) {
+        const uint32_t ph = it & 1u;
+        ok = mbar_wait(qdo_full, ph, abort_flag, p.status, 2201);
+        if (!ok) break;
+        if (it > 0) {   // the previous dQ tile still lives in the S columns until the compute warps have read it
+          ok = mbar_wait(dq_read, (it - 1) & 1u, abort_flag, p.status, 2202);
+          if (!ok) break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tS, kmaj(aQ, k), kmaj(aK, k), id_kk, k != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, kmaj(adO, k), kmaj(aV, k), id_kk, k != 0 ? 1u : 0u);
+        tc_commit(sdp_full);
+        ok = mbar_wait(pds_full, ph, abort_flag, p.status, 2203);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdV, mnmaj(aP, k), mnmaj(adO, k), id_mm, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdK, mnmaj(adS, k), mnmaj(aQ, k), id_mm, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ss(tdQ, kmaj(adS, k), mnmaj(aK, k), id_km, k != 0 ? 1u : 0u);
+        tc_commit(dq_full);
+        tc_commit(qdo_empty);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float log2e = 1.4426950408889634f;
+    bool ok = true;
+    for (int it = 0; it < n_q; ++it) {
+      const uint32_t ph = it & 1u;
+      const int q0 = (i_lo + it) * BQ;
+      const int qg = q0 + r;
+      const bool row_ok = qg < p.T;
+      const size_t stat = ((size_t)b * p.H + h) * p.T + (row_ok ? qg : 0);
+      const float lse2 = row_ok ? p.lse[stat] * log2e : 0.f;
+      const float dlt = row_ok ? p.delta[stat] : 0.f;
+      const int k_hi = min(qg, p.T - 1);
+      const int k_lo = (p.window < 0) ? 0 : max(0, qg - p.window);
+      ok = mbar_wait(sdp_full, ph, abort_flag, p.status, 2300);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32(tS + lane_addr + ch * 32, s);
+        tmem_ld_32x32(tdP + lane_addr + ch * 32, dp);
+        tc_wait_ld();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kg = k0 + ch * 32 + jj + e;
+            const bool vis = row_ok && kg <= k_hi && kg >= k_lo;
+            const float pr = vis ? exp2f(__uint_as_float(s[jj + e]) * p.scale_log2 - lse2) : 0.f;
+            pv[e] = pr;
+            dv[e] = pr * (__uint_as_float(dp[jj + e]) - dlt) * p.scale;
+          }
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
+          const __nv_bfloat162 db = __floats2bfloat162_rn(dv[0], dv[1]);
+          pp[jj / 2] = *reinterpret_cast<const uint32_t*>(&pb);
+          dd[jj / 2] = *reinterpret_cast<const uint32_t*>(&db);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t off = sw128_offset(r, ch * 32 + c * 8, kHalfBytes);
+          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
+          *reinterpret_cast<uint4*>(sdS + off) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      // dQ tile -> fp32 accumulator in global memory
+      ok = mbar_wait(dq_full, ph, abort_flag, p.status, 2301);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float* dst = p.dq_acc + (((size_t)b * p.T + (row_ok ? qg : 0)) * p.H + h) * D;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32(tdQ + lane_addr + ch * 32, v);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + ch * 32 + jj),
+                         "f"(__uint_as_float(v[jj])), "f"(__uint_as_float(v[jj + 1])), "f"(__uint_as_float(v[jj + 2])),
+                         "f"(__uint_as_float(v[jj + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_read);
+    }
+    // ---- dK / dV epilogue: the last dq_full commit covers every product issued before it
+    if (ok && n_q > 0) {
+      tc_fence_after();
+      const int kg = k0 + r;
+      const bool row_ok = kg < p.T;
+      const size_t base = (((size_t)b * p.T + (row_ok ? kg : 0)) * p.H + h) * D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t t = (which == 0 ? tdV : tdK) + lane_addr;
+        __nv_bfloat16* dstp = (which == 0 ? p.dv : p.dk) + base;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t v[32];
+          tmem_ld_32x32(t + ch * 32, v);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 8) {
+              uint4 o;
+              __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                hh[e] = __floats2bfloat162_rn(__uint_as_float(v[jj + 2 * e]), __uint_as_float(v[jj + 2 * e + 1]));
+              *reinterpret_cast<uint4*>(dstp + ch * 32 + jj) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+// All tensors contiguous (B, T, H, 128) bf16 except lse/delta fp32 (B, H, T) and dq_acc fp32 (B, T, H, 128), which must
+// be zero on entry. window < 0 = full causal.
+extern "C" int sr_flash_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
+                                 const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int T,
+                                 int H, int window, float scale, int* status, cudaStream_t stream) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return -4;
+    configured = true;
+  }
+  const long ld = (long)H * D;
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  if ((rc = sr_attn::encode_bthd(&mq, q, B, T, H, ld, 128))) return rc;
+  if ((rc = sr_attn::encode_bthd(&mk, k, B, T, H, ld, 128))) return rc - 10;
+  if ((rc = sr_attn::encode_bthd(&mv, v, B, T, H, ld, 128))) return rc - 20;
+  if ((rc = sr_attn::encode_bthd(&mdo, dO, B, T, H, ld, 128))) return rc - 30;
+  const long rows = (long)B * T * H;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dO),
+                                                                     reinterpret_cast<const __nv_bfloat16*>(out), delta, B, T, H);
+  BwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.B = B; p.T = T; p.H = H;
+  p.window = (window < 0 || window >= T) ? -1 : window;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((T + BKV - 1) / BKV, B * H);
+  flash_bwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
+  const long n4 = rows * D / 4;
+  long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  attn_dq_convert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n4);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

@@ -1,0 +1,367 @@
+// Flash attention forward for sm_100a: causal with a left sliding window, head_dim 128, bf16, (B, T, H, D) layout.
+//
+// One CTA per (batch*head, 128-query tile). Warp roles (192 threads):
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles (128 keys) through a 2-stage ring
+//   warp 1      MMA issuer + TMEM owner:  S_j = Q K_j^T   (SS, both operands K-major, accumulator in TMEM)
+//                                          O  += P_j V_j   (SS, P from shared memory, V_j as an MN-major operand)
+//   warps 2..5  softmax: thread i owns query row i (TMEM lane i), so row max / row sum need no shuffles. They read
+//               S_j from TMEM, apply scale + mask, keep running (m, l), rescale O in TMEM when the max moved,
+//               write P_j (bf16) into shared memory in the 128B-swizzled K-major layout, and at the end write
+//               O / l and the log-sum-exp.
+// S is double buffered in TMEM so S_{j+1} is computed while the softmax of tile j runs.
+// Keys visible to query i: max(0, i - window) <= k <= i  (window < 0 means unlimited), the convention of
+// flash_attn's window_size=(window, 0) that the reference uses (train.py:211-213, 432-438).
+#include "sm100_common.cuh"
+
+namespace {
+
+using namespace sr;
+
+constexpr int BQ = 128, BKV = 128, D = 128;
+constexpr int kThreads = 192;
+constexpr uint32_t kTileBytes = BQ * D * 2;        // 32 KB
+constexpr uint32_t kHalfBytes = BQ * 128;          // one 64-column half: 128 rows x 128 B
+constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;   // Q, K[2], V[2], P
+
+struct FwdParams {
+  __nv_bfloat16* out;   // [B, T, H, D]
+  float* lse;           // [B, H, T]
+  int B, T, H;
+  int window;           // < 0: unlimited
+  float scale_log2;     // softmax scale * log2(e)
+  int* status;
+};
+
+__device__ __forceinline__ void kv_range(int q0, int T, int window, int& j_lo, int& j_hi) {
+  const int q_last = min(q0 + BQ - 1, T - 1);
+  j_hi = q_last / BKV;
+  j_lo = (window < 0) ? 0 : max(0, q0 - window) / BKV;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + kTileBytes;          // 2 stages
+  uint8_t* sV = smem + 3 * kTileBytes;      // 2 stages
+  uint8_t* sP = smem + 5 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // 2
+  uint64_t* v_full = bars + 3;        // 2
+  uint64_t* kv_empty = bars + 5;      // 2
+  uint64_t* s_full = bars + 7;        // 2
+  uint64_t* p_full = bars + 9;        // 1 (count 128)
+  uint64_t* pv_done = bars + 10;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.T + BQ - 1) / BQ;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);   // heavy (late) tiles first
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh - b * p.H;
+  const int q0 = qt * BQ;
+  int j_lo, j_hi;
+  kv_range(q0, p.T, p.window, j_lo, j_hi);
+  const int n_kv = j_hi - j_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;          // two buffers of 128 columns
+  const uint32_t tmem_O = tmem_base + 256;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_arrive_expect_tx(q_full, kTileBytes);
+      tma_load_4d(sQ, &map_q, q_full, 0, h, q0, b);
+      tma_load_4d(sQ + kHalfBytes, &map_q, q_full, 64, h, q0, b);
+      for (int it = 0; it < n_kv; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1u;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, 1100)) break;
+        const int k0 = (j_lo + it) * BKV;
+        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+        tma_load_4d(sK + st * kTileBytes, &map_k, &k_full[st], 0, h, k0, b);
+        tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, &k_full[st], 64, h, k0, b);
+        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+        tma_load_4d(sV + st * kTileBytes, &map_v, &v_full[st], 0, h, k0, b);
+        tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, &v_full[st], 64, h, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_s = make_idesc(1, 1, 0, 0, BQ, BKV);   // Q (K-major) x K_j (K-major)
+      const uint32_t idesc_o = make_idesc(1, 1, 0, 1, BQ, D);     // P (K-major) x V_j (MN-major)
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 1200);
+      auto issue_s = [&](int it) {
+        const int st = it & 1;
+        const uint32_t aK = smem_u32(sK + st * kTileBytes);
+        const uint32_t d = tmem_S + static_cast<uint32_t>((it & 1) * 128);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t koff = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_f16_ss(d, make_smem_desc_sw128(aQ + koff, 16, 1024), make_smem_desc_sw128(aK + koff, 16, 1024), idesc_s,
+                      k != 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[it & 1]);
+      };
+      if (ok) {
+        ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, 1201);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+        }
+      }
+      for (int it = 0; it < n_kv && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1u;
+        if (it + 1 < n_kv) {
+          ok = mbar_wait(&k_full[(it + 1) & 1], ((it + 1) >> 1) & 1u, abort_flag, p.status, 1202);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(it + 1);
+        }
+        ok = mbar_wait(p_full, it & 1u, abort_flag, p.status, 1203);
+        if (!ok) break;
+        ok = mbar_wait(&v_full[st], ph, abort_flag, p.status, 1204);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + st * kTileBytes);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          // A = P: K-major over keys; B = V_j: [key rows x d], d contiguous -> MN-major, 64-column groups kHalfBytes apart
+          const uint64_t adesc = make_smem_desc_sw128(aP + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(aV + k * (16 * 128), kHalfBytes, 1024);
+          umma_f16_ss(tmem_O, adesc, bdesc, idesc_o, (it | k) != 0 ? 1u : 0u);
+        }
+        tc_commit(pv_done);
+        tc_commit(&kv_empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int q = warp & 3;
+    const int r = q * 32 + lane;               // row inside the tile == TMEM lane
+    const int qg = q0 + r;                     // global query index
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_kv; ++it) {
+      ok = mbar_wait(&s_full[it & 1], (it >> 1) & 1u, abort_flag, p.status, 1300);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tS = tmem_S + lane_addr + static_cast<uint32_t>((it & 1) * 128);
+      const int k0 = (j_lo + it) * BKV;
+      const int k_hi = min(qg, p.T - 1);                              // last visible key
+      const int k_lo = (p.window < 0) ? 0 : max(0, qg - p.window);    // first visible key
+      const bool need_mask = (k0 + BKV - 1 > k_hi) || (k0 < k_lo);
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + ch * 32, v);
+        tc_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kg = k0 + ch * 32 + j;
+            if (kg <= k_hi && kg >= k_lo) mx = fmaxf(mx, __uint_as_float(v[j]));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+        }
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+      // pass 2: probabilities, packed to bf16
+      uint32_t pk[64];
+      float rs = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + ch * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float e0 = exp2f(__uint_as_float(v[j]) * p.scale_log2 - m_use);
+          float e1 = exp2f(__uint_as_float(v[j + 1]) * p.scale_log2 - m_use);
+          if (need_mask) {
+            const int kg = k0 + ch * 32 + j;
+            if (!(kg <= k_hi && kg >= k_lo)) e0 = 0.f;
+            if (!(kg + 1 <= k_hi && kg + 1 >= k_lo)) e1 = 0.f;
+          }
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
+          const float2 back = __bfloat1622float2(pb);
+          rs += back.x + back.y;
+          pk[ch * 16 + j / 2] = *reinterpret_cast<const uint32_t*>(&pb);
+        }
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      // O and the P buffer are free once the previous P V product has completed
+      if (it > 0) {
+        ok = mbar_wait(pv_done, (it - 1) & 1u, abort_flag, p.status, 1301);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (!__all_sync(0xffffffffu, alpha == 1.f)) {
+          const uint32_t tO = tmem_O + lane_addr;
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t v[32];
+            tmem_ld_32x32(tO + ch * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+            tmem_st_32x32(tO + ch * 32, v);
+          }
+          tc_wait_st();
+        }
+      }
+      // P row -> shared memory (K-major, 128B swizzle): 16 chunks of 8 keys
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const uint32_t off = sw128_offset(r, c * 8, kHalfBytes);
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok) {
+      ok = mbar_wait(pv_done, (n_kv - 1) & 1u, abort_flag, p.status, 1302);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      const uint32_t tO = tmem_O + lane_addr;
+      const bool row_ok = qg < p.T;
+      __nv_bfloat16* orow = p.out + (((size_t)b * p.T + (row_ok ? qg : 0)) * p.H + h) * D;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32(tO + ch * 32, v);
+        tc_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 t;
+            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              hh[e] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]) * inv, __uint_as_float(v[j + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(orow + ch * 32 + j) = t;
+          }
+        }
+      }
+      if (row_ok) p.lse[((size_t)b * p.H + h) * p.T + qg] = (l > 0.f) ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+namespace sr_attn {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// (B, T, H, 128) bf16 tensor with row stride `ld_t` elements between tokens (the head h slice starts at h*128);
+// box = 64 columns x `rows` tokens of one head, 128B swizzle, zero fill past T.
+int encode_bthd(CUtensorMap* map, const void* ptr, int B, int T, int H, long ld_t, int rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld_t % 8) != 0) return -2;
+  cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[3] = {128 * 2, (cuuint64_t)ld_t * 2, (cuuint64_t)ld_t * 2 * (cuuint64_t)T};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+}  // namespace sr_attn
+
+// q, k, v: (B, T, H, 128) bf16 with token stride ld_* elements (contiguous tensors: H*128); out contiguous;
+// lse: fp32 (B, H, T), natural log of sum exp(scale * s). window < 0 = full causal.
+extern "C" int sr_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int T, int H,
+                                 long ld_q, long ld_k, long ld_v, int window, float scale, int* status,
+                                 cudaStream_t stream) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return -4;
+    configured = true;
+  }
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = sr_attn::encode_bthd(&mq, q, B, T, H, ld_q, BQ))) return rc;
+  if ((rc = sr_attn::encode_bthd(&mk, k, B, T, H, ld_k, BKV))) return rc - 10;
+  if ((rc = sr_attn::encode_bthd(&mv, v, B, T, H, ld_v, BKV))) return rc - 20;
+  FwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.B = B; p.T = T; p.H = H;
+  p.window = (window < 0 || window >= T) ? -1 : window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((T + BQ - 1) / BQ, B * H);
+  flash_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

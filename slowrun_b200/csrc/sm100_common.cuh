@@ -230,3 +230,26 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 }  // namespace sr
+
+// ---------------------------------------------------------------- additions used by the attention kernels
+namespace sr {
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Byte offset of element (row, col) of a bf16 tile stored as 64-column halves of [rows x 128 B] with the 128-byte
+// swizzle (the layout TMA writes and the UMMA descriptors above read). `half_bytes` = rows * 128.
+__device__ __forceinline__ uint32_t sw128_offset(int row, int col, uint32_t half_bytes) {
+  const int half = col >> 6;
+  const int c = col & 63;
+  const int chunk = (c >> 3) ^ (row & 7);
+  return half * half_bytes + row * 128 + chunk * 16 + (c & 7) * 2;
+}
+
+}  // namespace sr

@@ -1,2 +1,2 @@
-from .loader import TokenLoader
+from .loader import TokenLoader, EnsembleTokenLoader
 from .synthetic import write_synthetic_corpus, zipf_tokens

@@ -114,3 +114,67 @@ class TokenLoader:
         if self._stream is not None and self.pos < self.num_steps:
             self._next = self._issue()
         return x, y, epoch
+
+
+class EnsembleTokenLoader(TokenLoader):
+    """Loader of the unlimited track: per-model seed, step interleaving over data-parallel ranks, and a held-out
+    "fitness" slice carved from the front of the training file at document granularity
+    (unlimited/train.py:765-964). Ordering per epoch e of a model with seed s: documents permuted (cumulatively)
+    with seed s*1009 + e + 1000, windows permuted with seed s*1009 + e + 2000, the step list truncated to a multiple
+    of the data-parallel size and rank r takes steps r, r + world, ...
+    """
+
+    def __init__(self, filepath, B, T, device="cuda", seed=0, rank=0, world_size=1, fitness_tokens=0,
+                 fitness_only=False, prefetch=True):
+        self.seed = int(seed)
+        self.fitness_tokens = int(fitness_tokens)
+        self.fitness_only = fitness_only
+        self._carved = False
+        super().__init__(filepath, B, T, device=device, doc_shuffle=True, rank=rank, world_size=world_size,
+                         prefetch=prefetch)
+
+    def _carve(self):
+        if self._carved:
+            return
+        self._carved = True
+        if self.fitness_tokens <= 0:
+            self.fitness_docs = []
+            return
+        n, cut = 0, 0
+        for cut, d in enumerate(self.doc_tokens):
+            if n >= self.fitness_tokens:
+                break
+            n += len(d)
+        else:
+            cut = len(self.doc_tokens)
+        self.fitness_docs = self.doc_tokens[:cut]
+        self.doc_tokens = self.doc_tokens[cut:]
+
+    def _build_batches(self):
+        self._carve()
+        if self.fitness_only:
+            tokens = torch.cat(self.fitness_docs) if self.fitness_docs else torch.zeros(0, dtype=torch.long)
+            num_seqs = len(tokens) // self.seq_size
+            all_seqs = tokens[:num_seqs * self.seq_size].view(num_seqs, self.seq_size)
+        else:
+            g = torch.Generator()
+            g.manual_seed(self.seed * 1009 + self.epoch + 1000)
+            perm = torch.randperm(len(self.doc_tokens), generator=g)
+            self.doc_tokens = [self.doc_tokens[i] for i in perm.tolist()]
+            tokens = torch.cat(self.doc_tokens)
+            num_seqs = len(tokens) // self.seq_size
+            all_seqs = tokens[:num_seqs * self.seq_size].view(num_seqs, self.seq_size)
+            g.manual_seed(self.seed * 1009 + self.epoch + 2000)
+            all_seqs = all_seqs[torch.randperm(num_seqs, generator=g)]
+        steps_total = len(all_seqs) // self.B
+        steps_total = (steps_total // self.world_size) * self.world_size
+        usable = steps_total * self.B
+        all_seqs = all_seqs[:usable].view(steps_total, self.B, self.seq_size)
+        self._set_rank_data(all_seqs[self.rank::self.world_size])
+        self.num_steps = steps_total // self.world_size
+        self.total_tokens = usable * self.T
+        self.pos = 0
+
+    def _next_epoch(self):
+        self.epoch += 1
+        self._build_batches()

@@ -489,21 +489,9 @@ class GPT(nn.Module):
         x = self._run_network_once(x, x_emb, cos_sin, scale)
         return ops.rms_norm(x, self.norm_eps)
 
-    def forward(self, idx, targets=None, loss_reduction="mean", num_iterations=None, mtp_weights=None):
+    def _mtp_loss(self, x, targets, w, acc, w_t):
+        """Extra-block multi-token prediction (train.py:569-579): predict targets[t+1] from (x[t], embed(targets[t]))."""
         c = self.config
-        x = self.trunk(idx, num_iterations)
-        w, acc, w_t = self._head_weight()
-        if targets is None:
-            return ops.lm_head_logits(x, w, c.logit_cap, c.vocab_size, w_t)
-        if c.fused_mtp and self.training and mtp_weights is not None:
-            # tiny: one head scored against shifted targets over the whole padded vocabulary (tiny/train.py:682-696)
-            return ops.lm_head_loss(x, w, targets, c.logit_cap, self.padded_vocab, acc, w_t, weights=mtp_weights)
-        if loss_reduction != "mean":
-            return ops.lm_head_rows(x, w, targets, c.logit_cap, c.vocab_size, w_t).view(targets.shape)
-        lm_loss = ops.lm_head_loss(x, w, targets, c.logit_cap, c.vocab_size, acc, w_t)
-        if self.mtp_weight <= 0 or c.fused_mtp:
-            return (lm_loss, {"lm_loss": lm_loss}) if not c.fused_mtp else lm_loss
-        # extra-block MTP (train.py:569-579)
         mtp_emb = self._embed(targets[:, :-1].clamp(min=0))
         cat = torch.cat([x[:, :-1], mtp_emb], dim=-1)
         if cat.is_cuda:
@@ -518,9 +506,36 @@ class GPT(nn.Module):
         else:
             mtp_x = self._block_forward(self.mtp_block, combined, None, cs, (-1, -1), scale)
         mtp_out = ops.rms_norm(mtp_x, self.norm_eps)
-        mtp_loss = ops.lm_head_loss(mtp_out, w, targets[:, 1:], c.logit_cap, c.vocab_size, acc, w_t)
-        loss = lm_loss + self.mtp_weight * mtp_loss
-        return loss, {"lm_loss": lm_loss, "mtp_loss": mtp_loss}
+        return ops.lm_head_loss(mtp_out, w, targets[:, 1:], c.logit_cap, c.vocab_size, acc, w_t)
+
+    def forward(self, idx, targets=None, loss_reduction="mean", num_iterations=None, mtp_weights=None, distill=False,
+                label_smoothing=0.0):
+        c = self.config
+        x = self.trunk(idx, num_iterations)
+        w, acc, w_t = self._head_weight()
+        if targets is None:
+            return ops.lm_head_logits(x, w, c.logit_cap, c.vocab_size, w_t)
+        if distill or label_smoothing > 0:
+            # unlimited track: logits are needed outside (KL to a teacher) or the loss is label-smoothed
+            logits = ops.lm_head_logits_grad(x, w, c.logit_cap, c.vocab_size, acc, w_t)
+            mtp_loss = self._mtp_loss(x, targets, w, acc, w_t) if self.mtp_weight > 0 else None
+            if distill:
+                return logits, mtp_loss
+            loss = F.cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1), ignore_index=-1,
+                                   label_smoothing=label_smoothing)
+            return (loss + self.mtp_weight * mtp_loss if mtp_loss is not None else loss), {"lm_loss": loss}
+        if c.fused_mtp and self.training and mtp_weights is not None:
+            # tiny: one head scored against shifted targets over the whole padded vocabulary (tiny/train.py:682-696)
+            return ops.lm_head_loss(x, w, targets, c.logit_cap, self.padded_vocab, acc, w_t, weights=mtp_weights)
+        if loss_reduction != "mean":
+            return ops.lm_head_rows(x, w, targets, c.logit_cap, c.vocab_size, w_t).view(targets.shape)
+        lm_loss = ops.lm_head_loss(x, w, targets, c.logit_cap, c.vocab_size, acc, w_t)
+        if c.fused_mtp:
+            return lm_loss
+        if self.mtp_weight <= 0:
+            return lm_loss, {"lm_loss": lm_loss}
+        mtp_loss = self._mtp_loss(x, targets, w, acc, w_t)
+        return lm_loss + self.mtp_weight * mtp_loss, {"lm_loss": lm_loss, "mtp_loss": mtp_loss}
 
 
 def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_size: int = 1, alloc=None) -> GPT:

@@ -496,6 +496,12 @@ def lm_head_rows(x, w, targets, cap, vocab, w_t=False):
     return softcap_ce_ref(logits.reshape(-1, logits.size(-1)), targets.reshape(-1), cap, vocab, None, "none")
 
 
+def lm_head_logits_grad(x, w, cap, vocab, grad_acc=None, w_t=False):
+    """Differentiable soft-capped fp32 logits (distillation / label-smoothing paths, unlimited/train.py:603-634)."""
+    logits = linear(x, w, grad_acc, w_t)[..., :vocab].float()
+    return cap * torch.tanh(logits / cap) if cap > 0 else logits
+
+
 def lm_head_logits(x, w, cap, vocab, w_t=False):
     """Soft-capped fp32 logits [..., vocab] (train.py:559-562)."""
     if x.is_cuda:

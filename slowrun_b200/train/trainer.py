@@ -209,7 +209,7 @@ class Trainer:
             print0(f"step {step:05d} ({100 * step / target_steps:.2f}%) | loss: {debiased:.6f} | dt: {dt * 1000:.2f}ms | "
                    f"tok/sec: {tok_s:,} | bf16_mfu: {mfu:.2f}%{it_s}{tag}{eta}")
             log.metrics({"step": step, "train/loss": debiased, "train/mfu": mfu, "train/tok_per_sec": tok_s,
-                         **{f"train/{k}": float(v) for k, v in out["metrics"].items()}})
+                         **{f"train/{k}": float(v.detach()) for k, v in out["metrics"].items()}})
             epoch = self.sync_epoch(out["epoch"])
             if epoch != self.current_epoch:
                 val_bpb, val_loss = self.evaluate(max_iters)

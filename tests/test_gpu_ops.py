@@ -379,3 +379,56 @@ def test_fused_block_with_dropout_and_stochastic_depth_runs():
     assert torch.isfinite(loss)
     for n, p in model.named_parameters():
         assert torch.isfinite(p.grad.float()).all(), n
+
+
+@pytest.mark.parametrize("B,T,H,window", [(1, 128, 1, -1), (2, 384, 3, -1), (1, 2048, 2, 1024), (2, 2047, 2, -1),
+                                           (1, 1000, 2, 256), (1, 640, 1, 100)])
+def test_native_flash_attention_forward(B, T, H, window):
+    from slowrun_b200.ops.flash_attention import native_available, native_fwd
+    from slowrun_b200.ops.functional import attention_ref
+    if not native_available():
+        pytest.skip("native attention not built")
+    q, k, v = _bf(B, T, H, 128, seed=21), _bf(B, T, H, 128, seed=22), _bf(B, T, H, 128, seed=23)
+    out, lse, sc, w = native_fwd(q, k, v, window, None)
+    _status_ok()
+    ref = attention_ref(q.float(), k.float(), v.float(), window, None)
+    _close(out, ref, 3e-2, 3e-2)
+    # log-sum-exp of the scaled scores
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * (128 ** -0.5)
+    i = torch.arange(T, device="cuda").unsqueeze(1)
+    j = torch.arange(T, device="cuda").unsqueeze(0)
+    mask = (j <= i) & ((i - j) <= (window if window >= 0 else T))
+    s = s.masked_fill(~mask, float("-inf"))
+    assert torch.allclose(lse, torch.logsumexp(s, dim=-1), rtol=1e-3, atol=1e-2)
+
+
+def test_native_flash_attention_on_strided_qkv_view():
+    from slowrun_b200.ops.flash_attention import native_available, native_fwd
+    from slowrun_b200.ops.functional import attention_ref
+    if not native_available():
+        pytest.skip("native attention not built")
+    B, T, H = 2, 256, 2
+    qkv = _bf(B, T, 3, H, 128, seed=24)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    out, *_ = native_fwd(q, k, v, 64, 0.1)
+    _status_ok()
+    _close(out, attention_ref(q.float(), k.float(), v.float(), 64, 0.1), 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("B,T,H,window", [(1, 128, 1, -1), (2, 384, 2, -1), (1, 1024, 2, 256), (1, 2047, 1, -1), (1, 700, 2, 100)])
+def test_native_flash_attention_backward(B, T, H, window):
+    from slowrun_b200.ops.flash_attention import native_available, native_fwd, native_bwd, _has
+    from slowrun_b200.ops.functional import attention_ref
+    if not (native_available() and _has("sr_flash_attn_bwd")):
+        pytest.skip("native attention backward not built")
+    q, k, v = _bf(B, T, H, 128, seed=31), _bf(B, T, H, 128, seed=32), _bf(B, T, H, 128, seed=33)
+    dy = _bf(B, T, H, 128, seed=34)
+    out, lse, sc, w = native_fwd(q, k, v, window, None)
+    dq, dk, dv = native_bwd(dy, q, k, v, out, lse, sc, w)
+    _status_ok()
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, window, None)
+    ref.backward(dy.float())
+    _close(dq, qf.grad, 4e-2, 4e-2)
+    _close(dk, kf.grad, 4e-2, 4e-2)
+    _close(dv, vf.grad, 4e-2, 4e-2)

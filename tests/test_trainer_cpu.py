@@ -1,0 +1,105 @@
+"""End-to-end CPU runs of the training drivers on a tiny model and a tiny synthetic corpus: the loop, schedules,
+epoch handling, checkpoint ring, averaging passes, tiny-track recurrence/MTP/EMA and the unlimited chain."""
+import json
+import os
+
+import pytest
+import torch
+
+from slowrun_b200.config import track_defaults, config_from_args
+from slowrun_b200.data.synthetic import write_synthetic_corpus
+from slowrun_b200.parallel.comm import DistInfo
+
+
+@pytest.fixture(scope="module")
+def corpus(tmp_path_factory):
+    d = tmp_path_factory.mktemp("corpus")
+    return write_synthetic_corpus(str(d), train_tokens=24_000, val_tokens=8_000)
+
+
+def _shrink(cfg, corpus, tmp_path):
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 2, 64, 2, 2, 64
+    cfg.device_batch_size = 4
+    cfg.total_batch_size = 4 * 64 * 2
+    cfg.eval_tokens = 4 * 64 * 2
+    cfg.input_bin, cfg.input_val_bin = corpus
+    cfg.runs_dir = str(tmp_path / "runs")
+    cfg.logit_avg_dir = str(tmp_path / "ckpts")
+    cfg.run_name = "t"
+    return cfg
+
+
+def _info():
+    return DistInfo(False, 0, 0, 1, torch.device("cpu"))
+
+
+def test_limited_track_runs_epochs_checkpoints_and_logit_average(corpus, tmp_path):
+    from slowrun_b200.train.trainer import Trainer
+    cfg = _shrink(track_defaults("limited"), corpus, tmp_path)
+    cfg.num_epochs, cfg.swa_last_epochs, cfg.logit_avg, cfg.dupe_start_epoch = 3, 2, 2, 2
+    cfg.dupe_layers_start, cfg.dupe_layers_end = 1, 2
+    tr = Trainer(cfg, _info(), quiet=True)
+    res = tr.fit()
+    assert tr.dupe_active and tr.current_epoch > 3
+    assert res["steps"] > 0 and res["best_val_loss"] < 11.0
+    assert len(os.listdir(cfg.logit_avg_dir)) == 2
+    ck = torch.load(os.path.join(cfg.logit_avg_dir, sorted(os.listdir(cfg.logit_avg_dir))[-1]), weights_only=True)
+    assert set(ck) == {n for n, _ in tr.model.named_parameters()} and all(v.dtype == torch.float32 for v in ck.values())
+    assert json.load(open(os.path.join(cfg.runs_dir, "t", "result.json")))["steps"] == res["steps"]
+
+
+def test_two_hour_window_schedule_applies_yarn(corpus, tmp_path):
+    from slowrun_b200.train.trainer import Trainer
+    cfg = _shrink(track_defaults("two_hour"), corpus, tmp_path)
+    cfg.num_epochs, cfg.swa_last_epochs, cfg.logit_avg, cfg.dupe_start_epoch = 2, 0, 0, 99
+    cfg.window_schedule = "1-1:16,32;2-2:32,64"
+    tr = Trainer(cfg, _info(), quiet=True)
+    assert tr.model.long_window == 32
+    s0 = tr.model.rotary.attn_scale
+    tr.fit()
+    assert tr.model.long_window == 64 and tr.model.rotary.yarn_active and tr.model.rotary.attn_scale > s0
+
+
+def test_tiny_track_recurrence_mtp_ema_and_weight_average(corpus, tmp_path):
+    from slowrun_b200.train.trainer import Trainer
+    cfg = _shrink(track_defaults("tiny"), corpus, tmp_path)
+    cfg.num_epochs, cfg.swa_last_epochs, cfg.update_ema_every, cfg.max_train_steps = 3, 2, 2, 0
+    tr = Trainer(cfg, _info(), quiet=True)
+    assert tr.sched.num_recurrences(0) == 1 and tr.sched.num_recurrences(tr.sched.N) == 2
+    assert tr.sched.mtp_weights(0) == [1.0, 0.5, 0.25] and tr.sched.mtp_weights(tr.sched.N)[1:] == [0.0, 0.0]
+    res = tr.fit()
+    assert tr.ema.updates > 0 and res["best_val_loss"] < 11.0
+    assert os.path.exists(os.path.join(cfg.runs_dir, "t", "model.pt"))
+
+
+def test_reference_flag_spellings_are_accepted():
+    cfg = config_from_args("limited", ["--n_embd", "2560", "--n_head", "20", "--device-batch-size", "2", "--no-iha",
+                                       "--output_json", "x.json", "--dupe-loops", "3", "--logit-avg-mode", "equal"])
+    assert cfg.model.n_embd == 2560 and cfg.model.n_head == 20 and not cfg.model.use_iha and cfg.save_result == "x.json"
+    t = config_from_args("tiny", ["--xsa-mode", "first6", "--wd-mid", "0.2", "--mtp-predict", "2"])
+    assert t.model.xsa_mode == "first6" and t.wd_mid == 0.2 and t.mtp_predict == 2
+    u = config_from_args("unlimited", ["--num-models", "4", "--k-sweep", "2", "4", "--run", "r1", "--distill-alpha", "0.3"])
+    assert u.num_models == 4 and list(u.k_sweep) == [2, 4] and u.run_name == "r1" and u.distill_alpha == 0.3
+    h = config_from_args("two_hour", [])
+    assert h.num_epochs == 22 and h.window_schedule.startswith("1-6:256,768")
+
+
+def test_unlimited_chain_distills_selects_and_resumes(corpus, tmp_path):
+    from slowrun_b200.train.unlimited import UnlimitedTrainer
+    cfg = _shrink(track_defaults("unlimited"), corpus, tmp_path)
+    cfg.num_models, cfg.epochs_per_cycle, cfg.distill_after_cycles = 3, 0.1, 1
+    cfg.bs_floor = cfg.total_batch_size
+    cfg.fitness_tokens, cfg.pgt_steps, cfg.k_sweep, cfg.grad_opt_steps = 2000, 2, (2, 3), 30
+    cfg.checkpoint_base, cfg.run_name = str(tmp_path / "ck"), "u"
+    cfg.dupe_layers_start, cfg.dupe_layers_end, cfg.dupe_loops = 1, 2, 1
+    tr = UnlimitedTrainer(cfg, _info())
+    out = tr.run()
+    assert len(out["models"]) == 3 and set(out["ensemble"]) == {2, 3}
+    assert all(os.path.exists(os.path.join(cfg.checkpoint_base, "u", f"model_{i}.pt")) for i in range(3))
+    assert out["ensemble"][3]["val_loss"] < 11.0
+    assert abs(sum(out["selection"][2]["weights"]) - 1.0) < 1e-5
+    # resume: a fresh trainer picks up after the last finished cycle and goes straight to selection
+    cfg.resume = "u"
+    tr2 = UnlimitedTrainer(cfg, _info())
+    assert tr2.try_resume() and tr2.cycle == 3 and len(tr2.results) == 3
