@@ -151,6 +151,7 @@ class TrainConfig:
     # framework switches (no counterpart in the reference)
     comm: str = "auto"                # auto | fused | nccl : gradient/param collectives
     wire_dtype: str = "bf16"          # bf16 | fp32 : gradient reduce-scatter wire format
+    cuda_graphs: bool = True          # replay each micro-batch's forward+backward as one captured CUDA graph
     max_steps: int = -1               # stop after this many optimizer steps (benchmarks/tests)
     eval_tokens: int = EVAL_TOKENS
     log_jsonl: str = ""
@@ -292,6 +293,7 @@ def build_parser(track: str) -> argparse.ArgumentParser:
     # framework switches
     a("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"])
     a("--wire-dtype", type=str, default="bf16", choices=["bf16", "fp32"])
+    a("--no-cuda-graphs", action="store_false", dest="cuda_graphs")
     a("--max-steps", type=int, default=-1)
     a("--eval-tokens", type=int, default=EVAL_TOKENS)
     a("--log-jsonl", type=str, default="")

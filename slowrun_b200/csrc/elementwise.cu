@@ -8,7 +8,9 @@
 //   gated_add fwd/bwd          v += gate[b,t,h] * ve (value residual, train.py:299-303)
 //   head_scale fwd/bwd         y *= gate[b,t,h] (attention gate, train.py:308-309)
 //   swiglu fwd/bwd             silu(g) * f on a fused [M, 2h] GEMM output (train.py:322-323)
-//   dropout_add fwd/bwd        out = x_in + keep*(x_mid + dropout(y) - x_in) (train.py:333-344)
+//   dropout_add fwd/bwd        out = x_in + keep*(x_mid + dropout(y) - x_in) (train.py:333-344); the mask is a hash of
+//                              (per-call salt, device-resident step counter, element index), so a captured CUDA graph
+//                              draws a fresh mask on every replay
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -371,7 +373,9 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gf, const __
 // out = x_in + keep*(x_mid + drop(y) - x_in); with x_in == nullptr: out = x_mid + drop(y)
 __global__ void dropout_add_fwd_kernel(const __nv_bfloat16* __restrict__ x_mid, const __nv_bfloat16* __restrict__ y,
                                        const __nv_bfloat16* __restrict__ x_in, const float* __restrict__ keep_p,
-                                       __nv_bfloat16* __restrict__ out, long n8, float p, uint64_t seed) {
+                                       __nv_bfloat16* __restrict__ out, long n8, float p, uint64_t salt,
+                                       const unsigned long long* __restrict__ seed_ptr) {
+  const uint64_t seed = salt + (seed_ptr ? (*seed_ptr) * 0x9E3779B97F4A7C15ull : 0ull);
   const float keep = (x_in != nullptr) ? *keep_p : 1.f;
   const float scale = 1.f / (1.f - p);
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
@@ -397,7 +401,9 @@ __global__ void dropout_add_fwd_kernel(const __nv_bfloat16* __restrict__ x_mid, 
 // dy = keep * mask/(1-p) * g ; (optional) dmid = keep*g ; (optional) din = (1-keep)*g
 __global__ void dropout_add_bwd_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ keep_p,
                                        __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dmid,
-                                       __nv_bfloat16* __restrict__ din, long n8, float p, uint64_t seed) {
+                                       __nv_bfloat16* __restrict__ din, long n8, float p, uint64_t salt,
+                                       const unsigned long long* __restrict__ seed_ptr) {
+  const uint64_t seed = salt + (seed_ptr ? (*seed_ptr) * 0x9E3779B97F4A7C15ull : 0ull);
   const float keep = (keep_p != nullptr) ? *keep_p : 1.f;
   const float scale = 1.f / (1.f - p);
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
@@ -513,15 +519,16 @@ extern "C" int sr_swiglu_bwd(const void* gf, const void* dout, void* dgf, long M
   return rc();
 }
 extern "C" int sr_dropout_add_fwd(const void* x_mid, const void* y, const void* x_in, const float* keep, void* out,
-                                  long n, float p, unsigned long long seed, cudaStream_t s) {
+                                  long n, float p, unsigned long long seed, const unsigned long long* seed_ptr,
+                                  cudaStream_t s) {
   if (n % 8) return -2;
-  dropout_add_fwd_kernel<<<grid_for(n / 8, kThreads), kThreads, 0, s>>>(BF(x_mid), BF(y), BF(x_in), keep, BFM(out), n / 8, p, seed);
+  dropout_add_fwd_kernel<<<grid_for(n / 8, kThreads), kThreads, 0, s>>>(BF(x_mid), BF(y), BF(x_in), keep, BFM(out), n / 8, p, seed, seed_ptr);
   return rc();
 }
 extern "C" int sr_dropout_add_bwd(const void* g, const float* keep, void* dy, void* dmid, void* din, long n, float p,
-                                  unsigned long long seed, cudaStream_t s) {
+                                  unsigned long long seed, const unsigned long long* seed_ptr, cudaStream_t s) {
   if (n % 8) return -2;
-  dropout_add_bwd_kernel<<<grid_for(n / 8, kThreads), kThreads, 0, s>>>(BF(g), keep, BFM(dy), BFM(dmid), BFM(din), n / 8, p, seed);
+  dropout_add_bwd_kernel<<<grid_for(n / 8, kThreads), kThreads, 0, s>>>(BF(g), keep, BFM(dy), BFM(dmid), BFM(din), n / 8, p, seed, seed_ptr);
   return rc();
 }
 extern "C" int sr_acc_bf16_into_f32(float* acc, const void* g, long n, cudaStream_t s) {

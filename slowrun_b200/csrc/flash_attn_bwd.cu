@@ -9,7 +9,8 @@
 // written as bf16 into 128B-swizzled shared-memory tiles; the same dS tile is read K-major for dQ and MN-major for dK.
 // dV/dK accumulate in TMEM across the query loop; dQ tiles are added into an fp32 global accumulator with vector
 // reductions and converted to bf16 by a second kernel. delta = rowsum(dO * O) comes from a small pre-pass.
-// Warp roles (192 threads): warp 0 TMA, warp 1 MMA issuer + TMEM owner, warps 2..5 compute / epilogue.
+// Warp roles (320 threads): warp 0 TMA, warp 1 MMA issuer + TMEM owner, warps 2..9 compute / epilogue; every row of a
+// tile is shared by two threads (columns 0..63 and 64..127) so each scheduler has two compute warps to interleave.
 #include "sm100_common.cuh"
 
 namespace sr_attn {
@@ -21,10 +22,10 @@ namespace {
 using namespace sr;
 
 constexpr int BQ = 128, BKV = 128, D = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 compute (two threads per row, 64 columns each)
 constexpr uint32_t kTileBytes = 128 * 128 * 2;
 constexpr uint32_t kHalfBytes = 128 * 128;
-constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;   // K, V, Q, dO, P, dS
+constexpr int kSmemBytes = 6 * kTileBytes + 256;   // K, V, Q, dO, P, dS
 
 struct BwdParams {
   const float* lse;      // [B, H, T]
@@ -75,8 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                  const BwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = smem + kTileBytes;
   uint8_t* sQ = smem + 2 * kTileBytes;
@@ -88,9 +88,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* qdo_full = bars + 1;     // 1
   uint64_t* qdo_empty = bars + 2;    // 1  (tcgen05.commit after the products that read Q_i / dO_i)
   uint64_t* sdp_full = bars + 3;     // 1  S and dP ready
-  uint64_t* pds_full = bars + 4;     // 128 arrivals: P and dS written
+  uint64_t* pds_full = bars + 4;     // 256 arrivals: P and dS written
   uint64_t* dq_full = bars + 5;      // 1  dQ tile ready (also: dV/dK products of this tile issued and done)
-  uint64_t* dq_read = bars + 6;      // 128 arrivals: dQ tile consumed, S columns free
+  uint64_t* dq_read = bars + 6;      // 256 arrivals: dQ tile consumed, S columns free
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -110,10 +110,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     mbar_init(qdo_full, 1);
     mbar_init(qdo_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 128);
+    mbar_init(dq_read, 256);
     *abort_flag = 0;
+    if ((smem_u32(smem) & 1023u) != 0u) report_error(p.status, SR_ERR_BAD_ARG, 2000, 0);   // swizzle needs 1 KB alignment
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
@@ -189,7 +190,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ compute warps
-    const int q = warp & 3;
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    const int chalf = (warp - 2) >> 2;      // which 64 columns of the row this thread handles
     const int r = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float log2e = 1.4426950408889634f;
@@ -209,7 +211,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {
         uint32_t s[32], dp[32];
         tmem_ld_32x32(tS + lane_addr + ch * 32, s);
         tmem_ld_32x32(tdP + lane_addr + ch * 32, dp);
@@ -248,7 +250,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_fence_after();
       float* dst = p.dq_acc + (((size_t)b * p.T + (row_ok ? qg : 0)) * p.H + h) * D;
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {
         uint32_t v[32];
         tmem_ld_32x32(tdQ + lane_addr + ch * 32, v);
         tc_wait_ld();
@@ -275,7 +277,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t t = (which == 0 ? tdV : tdK) + lane_addr;
         __nv_bfloat16* dstp = (which == 0 ? p.dv : p.dk) + base;
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {
           uint32_t v[32];
           tmem_ld_32x32(t + ch * 32, v);
           tc_wait_ld();

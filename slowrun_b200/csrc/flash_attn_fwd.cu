@@ -17,11 +17,20 @@ namespace {
 
 using namespace sr;
 
-constexpr int BQ = 128, BKV = 128, D = 128;
+constexpr int BQ = 128, D = 128;
 constexpr int kThreads = 192;
-constexpr uint32_t kTileBytes = BQ * D * 2;        // 32 KB
-constexpr uint32_t kHalfBytes = BQ * 128;          // one 64-column half: 128 rows x 128 B
-constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;   // Q, K[2], V[2], P
+constexpr uint32_t kQBytes = BQ * D * 2;           // 32 KB
+constexpr uint32_t kQHalf = BQ * 128;              // one 64-column half of a 128-row tile: 128 rows x 128 B
+
+// BKV = keys per tile. 128: one CTA per SM; 64: two CTAs per SM (their softmax and MMA phases overlap).
+template <int BKV>
+struct FwdCfg {
+  static constexpr uint32_t kKVBytes = BKV * D * 2;       // K or V tile
+  static constexpr uint32_t kKVHalf = BKV * 128;          // 64 d-columns of a K/V tile
+  static constexpr uint32_t kPBytes = BQ * BKV * 2;
+  static constexpr uint32_t kTmemCols = (BKV == 128) ? 512 : 256;   // 2 S buffers + O
+  static constexpr int kSmemBytes = kQBytes + 4 * kKVBytes + kPBytes + 256;
+};
 
 struct FwdParams {
   __nv_bfloat16* out;   // [B, T, H, D]
@@ -32,22 +41,25 @@ struct FwdParams {
   int* status;
 };
 
+template <int BKV>
 __device__ __forceinline__ void kv_range(int q0, int T, int window, int& j_lo, int& j_hi) {
   const int q_last = min(q0 + BQ - 1, T - 1);
   j_hi = q_last / BKV;
   j_lo = (window < 0) ? 0 : max(0, q0 - window) / BKV;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BKV>
+__global__ void __launch_bounds__(kThreads, (BKV == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using C_ = FwdCfg<BKV>;
+  constexpr uint32_t kKVBytes = C_::kKVBytes, kKVHalf = C_::kKVHalf;
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
-  uint8_t* sK = smem + kTileBytes;          // 2 stages
-  uint8_t* sV = smem + 3 * kTileBytes;      // 2 stages
-  uint8_t* sP = smem + 5 * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint8_t* sK = smem + kQBytes;                       // 2 stages
+  uint8_t* sV = sK + 2 * kKVBytes;                    // 2 stages
+  uint8_t* sP = sV + 2 * kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C_::kPBytes);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // 2
   uint64_t* v_full = bars + 3;        // 2
@@ -65,7 +77,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const int b = bh / p.H, h = bh - b * p.H;
   const int q0 = qt * BQ;
   int j_lo, j_hi;
-  kv_range(q0, p.T, p.window, j_lo, j_hi);
+  kv_range<BKV>(q0, p.T, p.window, j_lo, j_hi);
   const int n_kv = j_hi - j_lo + 1;
 
   if (threadIdx.x == 0) {
@@ -79,39 +91,40 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     mbar_init(p_full, 128);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
+    if ((smem_u32(smem) & 1023u) != 0u) report_error(p.status, SR_ERR_BAD_ARG, 1000, 0);   // swizzle needs 1 KB alignment
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, C_::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S = tmem_base;          // two buffers of 128 columns
-  const uint32_t tmem_O = tmem_base + 256;
+  const uint32_t tmem_S = tmem_base;          // two buffers of BKV columns
+  const uint32_t tmem_O = tmem_base + 2 * BKV;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      mbar_arrive_expect_tx(q_full, kTileBytes);
+      mbar_arrive_expect_tx(q_full, kQBytes);
       tma_load_4d(sQ, &map_q, q_full, 0, h, q0, b);
-      tma_load_4d(sQ + kHalfBytes, &map_q, q_full, 64, h, q0, b);
+      tma_load_4d(sQ + kQHalf, &map_q, q_full, 64, h, q0, b);
       for (int it = 0; it < n_kv; ++it) {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1u;
         if (!mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, p.status, 1100)) break;
         const int k0 = (j_lo + it) * BKV;
-        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &map_k, &k_full[st], 0, h, k0, b);
-        tma_load_4d(sK + st * kTileBytes + kHalfBytes, &map_k, &k_full[st], 64, h, k0, b);
-        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
-        tma_load_4d(sV + st * kTileBytes, &map_v, &v_full[st], 0, h, k0, b);
-        tma_load_4d(sV + st * kTileBytes + kHalfBytes, &map_v, &v_full[st], 64, h, k0, b);
+        mbar_arrive_expect_tx(&k_full[st], kKVBytes);
+        tma_load_4d(sK + st * kKVBytes, &map_k, &k_full[st], 0, h, k0, b);
+        tma_load_4d(sK + st * kKVBytes + kKVHalf, &map_k, &k_full[st], 64, h, k0, b);
+        mbar_arrive_expect_tx(&v_full[st], kKVBytes);
+        tma_load_4d(sV + st * kKVBytes, &map_v, &v_full[st], 0, h, k0, b);
+        tma_load_4d(sV + st * kKVBytes + kKVHalf, &map_v, &v_full[st], 64, h, k0, b);
       }
     }
   } else if (warp == 1) {
@@ -123,12 +136,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 1200);
       auto issue_s = [&](int it) {
         const int st = it & 1;
-        const uint32_t aK = smem_u32(sK + st * kTileBytes);
-        const uint32_t d = tmem_S + static_cast<uint32_t>((it & 1) * 128);
+        const uint32_t aK = smem_u32(sK + st * kKVBytes);
+        const uint32_t d = tmem_S + static_cast<uint32_t>((it & 1) * BKV);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t koff = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_f16_ss(d, make_smem_desc_sw128(aQ + koff, 16, 1024), make_smem_desc_sw128(aK + koff, 16, 1024), idesc_s,
+          const uint32_t qoff = (k >> 2) * kQHalf + (k & 3) * 32;
+          const uint32_t koff = (k >> 2) * kKVHalf + (k & 3) * 32;
+          umma_f16_ss(d, make_smem_desc_sw128(aQ + qoff, 16, 1024), make_smem_desc_sw128(aK + koff, 16, 1024), idesc_s,
                       k != 0 ? 1u : 0u);
         }
         tc_commit(&s_full[it & 1]);
@@ -154,12 +168,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         ok = mbar_wait(&v_full[st], ph, abort_flag, p.status, 1204);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + st * kTileBytes);
+        const uint32_t aV = smem_u32(sV + st * kKVBytes);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          // A = P: K-major over keys; B = V_j: [key rows x d], d contiguous -> MN-major, 64-column groups kHalfBytes apart
-          const uint64_t adesc = make_smem_desc_sw128(aP + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(aV + k * (16 * 128), kHalfBytes, 1024);
+          // A = P: K-major over keys (64-key halves of 128 rows); B = V_j: [key rows x d], d contiguous -> MN-major,
+          // its two 64-column groups kKVHalf apart
+          const uint64_t adesc = make_smem_desc_sw128(aP + (k >> 2) * kQHalf + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(aV + k * (16 * 128), kKVHalf, 1024);
           umma_f16_ss(tmem_O, adesc, bdesc, idesc_o, (it | k) != 0 ? 1u : 0u);
         }
         tc_commit(pv_done);
@@ -179,7 +194,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tmem_S + lane_addr + static_cast<uint32_t>((it & 1) * 128);
+      const uint32_t tS = tmem_S + lane_addr + static_cast<uint32_t>((it & 1) * BKV);
       const int k0 = (j_lo + it) * BKV;
       const int k_hi = min(qg, p.T - 1);                              // last visible key
       const int k_lo = (p.window < 0) ? 0 : max(0, qg - p.window);    // first visible key
@@ -187,7 +202,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // pass 1: row max
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < BKV / 32; ++ch) {
         uint32_t v[32];
         tmem_ld_32x32(tS + ch * 32, v);
         tc_wait_ld();
@@ -206,10 +221,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
       // pass 2: probabilities, packed to bf16
-      uint32_t pk[64];
+      uint32_t pk[BKV / 2];
       float rs = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < BKV / 32; ++ch) {
         uint32_t v[32];
         tmem_ld_32x32(tS + ch * 32, v);
         tc_wait_ld();
@@ -252,8 +267,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       // P row -> shared memory (K-major, 128B swizzle): 16 chunks of 8 keys
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const uint32_t off = sw128_offset(r, c * 8, kHalfBytes);
+      for (int c = 0; c < BKV / 8; ++c) {
+        const uint32_t off = sw128_offset(r, c * 8, kQHalf);
         *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
       }
       fence_proxy_async_smem();
@@ -295,7 +310,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, C_::kTmemCols);
   }
 }
 
@@ -339,21 +354,32 @@ int encode_bthd(CUtensorMap* map, const void* ptr, int B, int T, int H, long ld_
 
 // q, k, v: (B, T, H, 128) bf16 with token stride ld_* elements (contiguous tensors: H*128); out contiguous;
 // lse: fp32 (B, H, T), natural log of sum exp(scale * s). window < 0 = full causal.
-extern "C" int sr_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int T, int H,
-                                 long ld_q, long ld_k, long ld_v, int window, float scale, int* status,
-                                 cudaStream_t stream) {
-  if (B <= 0 || T <= 0 || H <= 0) return 0;
+template <int BKV>
+int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdParams& p, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_kernel<BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<BKV>::kSmemBytes) !=
+        cudaSuccess)
       return -4;
     configured = true;
   }
+  dim3 grid((p.T + BQ - 1) / BQ, p.B * p.H);
+  flash_fwd_kernel<BKV><<<grid, kThreads, FwdCfg<BKV>::kSmemBytes, stream>>>(mq, mk, mv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// q, k, v: (B, T, H, 128) bf16 with token stride ld_* elements (contiguous tensors: H*128); out contiguous;
+// lse: fp32 (B, H, T), natural log of sum exp(scale * s). window < 0 = full causal. bkv: 64 or 128 keys per tile.
+extern "C" int sr_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int T, int H,
+                                 long ld_q, long ld_k, long ld_v, int window, float scale, int bkv, int* status,
+                                 cudaStream_t stream) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  if (bkv != 64 && bkv != 128) return -2;
   CUtensorMap mq, mk, mv;
   int rc;
   if ((rc = sr_attn::encode_bthd(&mq, q, B, T, H, ld_q, BQ))) return rc;
-  if ((rc = sr_attn::encode_bthd(&mk, k, B, T, H, ld_k, BKV))) return rc - 10;
-  if ((rc = sr_attn::encode_bthd(&mv, v, B, T, H, ld_v, BKV))) return rc - 20;
+  if ((rc = sr_attn::encode_bthd(&mk, k, B, T, H, ld_k, bkv))) return rc - 10;
+  if ((rc = sr_attn::encode_bthd(&mv, v, B, T, H, ld_v, bkv))) return rc - 20;
   FwdParams p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.lse = lse;
@@ -361,7 +387,5 @@ extern "C" int sr_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   p.window = (window < 0 || window >= T) ? -1 : window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  dim3 grid((T + BQ - 1) / BQ, B * H);
-  flash_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return bkv == 64 ? launch_fwd<64>(mq, mk, mv, p, stream) : launch_fwd<128>(mq, mk, mv, p, stream);
 }

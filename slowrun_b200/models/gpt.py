@@ -471,6 +471,8 @@ class GPT(nn.Module):
         B, T = idx.size()
         cos_sin = (self.rotary.cos[:, :T], self.rotary.sin[:, :T])
         scale = self.rotary.attn_scale if self.rotary.yarn_active else None
+        if self.training and idx.is_cuda:
+            ops.advance_dropout_state(idx.device)
         x = self._embed(idx)
         x_emb = x
         if c.num_iterations > 1 or num_iterations is not None:

@@ -46,8 +46,8 @@ def _rmsnorm_bwd(x, dy, dres, eps):
 
 def _dropout_add_fwd(x_mid, y, p, seed, x_in=None, keep=None):
     out = torch.empty_like(x_mid)
-    _call("sr_dropout_add_fwd", [P] * 5 + [L, F32, ULL, P], x_mid.data_ptr(), y.data_ptr(), _lib.ptr(x_in), _lib.ptr(keep),
-          out.data_ptr(), x_mid.numel(), p, seed, _sp())
+    _call("sr_dropout_add_fwd", [P] * 5 + [L, F32, ULL, P, P], x_mid.data_ptr(), y.data_ptr(), _lib.ptr(x_in), _lib.ptr(keep),
+          out.data_ptr(), x_mid.numel(), p, seed, ops.dropout_state(x_mid.device).data_ptr(), _sp())
     return out
 
 
@@ -55,8 +55,8 @@ def _dropout_add_bwd(g, p, seed, keep=None):
     dy = torch.empty_like(g)
     dmid = torch.empty_like(g) if keep is not None else None
     din = torch.empty_like(g) if keep is not None else None
-    _call("sr_dropout_add_bwd", [P] * 5 + [L, F32, ULL, P], g.data_ptr(), _lib.ptr(keep), dy.data_ptr(), _lib.ptr(dmid),
-          _lib.ptr(din), g.numel(), p, seed, _sp())
+    _call("sr_dropout_add_bwd", [P] * 5 + [L, F32, ULL, P, P], g.data_ptr(), _lib.ptr(keep), dy.data_ptr(), _lib.ptr(dmid),
+          _lib.ptr(din), g.numel(), p, seed, ops.dropout_state(g.device).data_ptr(), _sp())
     return dy, dmid, din
 
 

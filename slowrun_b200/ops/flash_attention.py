@@ -28,7 +28,10 @@ def native_available() -> bool:
     return _has("sr_flash_attn_fwd")
 
 
-def native_fwd(q, k, v, window, scale):
+DEFAULT_BKV = int(os.environ.get("SLOWRUN_ATTN_BKV", "64"))
+
+
+def native_fwd(q, k, v, window, scale, bkv=None):
     """q, k, v: (B, T, H, 128) bf16, last two dims dense (token stride may be larger). Returns (out, lse[B,H,T])."""
     B, T, H, D = q.shape
     assert D == 128 and q.dtype == torch.bfloat16
@@ -38,9 +41,9 @@ def native_fwd(q, k, v, window, scale):
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     w = -1 if (window is None or window < 0 or window >= T) else int(window)
     sc = float(scale) if scale is not None else D ** -0.5
-    rc = _lib.fn("sr_flash_attn_fwd", [P] * 5 + [I, I, I, L, L, L, I, F32, P, P])(
+    rc = _lib.fn("sr_flash_attn_fwd", [P] * 5 + [I, I, I, L, L, L, I, F32, I, P, P])(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, q.stride(1), k.stride(1),
-        v.stride(1), w, sc, _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
+        v.stride(1), w, sc, int(bkv or DEFAULT_BKV), _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "sr_flash_attn_fwd")
     return out, lse, sc, w
 

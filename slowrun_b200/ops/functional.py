@@ -351,12 +351,30 @@ def dropout_add_ref(x_mid, y, p, training, x_in=None, keep=None):
     return out
 
 
-_seed_state = {"gen": None}
+_dropout = {"salt": 0, "state": {}}
 
 
 def next_dropout_seed() -> int:
-    """Host-side counter-free seed drawn from torch's default CPU generator (so `torch.manual_seed` governs it)."""
-    return int(torch.randint(0, 2 ** 62, (1,)).item())
+    """Per-call-site salt: a host counter. It is baked into a captured graph; what changes between replays is the
+    device-resident step counter (`dropout_state`) that every mask also hashes."""
+    _dropout["salt"] += 1
+    return _dropout["salt"] * 0x9E3779B1
+
+
+def dropout_state(device) -> torch.Tensor:
+    """int64[1] on `device`, initialised from torch's CPU generator (so torch.manual_seed governs the masks)."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    st = _dropout["state"].get(key)
+    if st is None:
+        st = torch.randint(0, 2 ** 40, (1,), dtype=torch.int64).to(dev)
+        _dropout["state"][key] = st
+    return st
+
+
+def advance_dropout_state(device):
+    """Call once per forward pass (inside the captured region when CUDA graphs are used)."""
+    dropout_state(device).add_(1)
 
 
 class _DropoutAddFn(Function):
@@ -365,9 +383,9 @@ class _DropoutAddFn(Function):
         x_mid, y = _c(x_mid), _c(y)
         x_in = _c(x_in) if x_in is not None else None
         out = torch.empty_like(x_mid)
-        _call("sr_dropout_add_fwd", [c_void_p] * 5 + [c_long, c_float, c_ull, c_void_p],
+        _call("sr_dropout_add_fwd", [c_void_p] * 5 + [c_long, c_float, c_ull, c_void_p, c_void_p],
               x_mid.data_ptr(), y.data_ptr(), _lib.ptr(x_in), _lib.ptr(keep), out.data_ptr(), x_mid.numel(), p, seed,
-              _lib.stream_ptr())
+              dropout_state(x_mid.device).data_ptr(), _lib.stream_ptr())
         ctx.p, ctx.seed = p, seed
         ctx.has_in = x_in is not None
         ctx.save_for_backward(keep if keep is not None else x_mid.new_empty(0))
@@ -381,9 +399,9 @@ class _DropoutAddFn(Function):
         dy = torch.empty_like(g)
         dmid = torch.empty_like(g) if has_in else None
         din = torch.empty_like(g) if has_in else None
-        _call("sr_dropout_add_bwd", [c_void_p] * 5 + [c_long, c_float, c_ull, c_void_p],
+        _call("sr_dropout_add_bwd", [c_void_p] * 5 + [c_long, c_float, c_ull, c_void_p, c_void_p],
               g.data_ptr(), keep.data_ptr() if has_in else 0, dy.data_ptr(), _lib.ptr(dmid), _lib.ptr(din), g.numel(),
-              ctx.p, ctx.seed, _lib.stream_ptr())
+              ctx.p, ctx.seed, dropout_state(g.device).data_ptr(), _lib.stream_ptr())
         return (dmid if has_in else g), dy, None, None, din, None
 
 

@@ -88,6 +88,11 @@ class Trainer:
         self.model.train()
         self.h2d_bytes_per_step = self.train_loader.h2d_bytes_per_batch * self.grad_accum
         self.d2h_bytes_per_step = 4
+        # CUDA graphs of one micro-batch (forward + backward), keyed by everything that changes the kernel sequence
+        self._graphs = {}
+        self._graph_key = None
+        self._eager_micro = 0
+        self.use_graphs = bool(c.cuda_graphs) and self.device.type == "cuda"
 
     # ------------------------------------------------------------------ one optimizer step
     def _maybe_switch_structure(self):
@@ -112,13 +117,28 @@ class Trainer:
         metrics = {}
         loss_t = None
         epoch = self._pending_epoch
+        key = (self.dupe_active, n_iter, tuple(model.window_sizes), model.rotary.attn_scale, self.grad_accum)
+        if key != self._graph_key:
+            self._graph_key, self._eager_micro = key, 0
         for _ in range(self.grad_accum):
-            if tiny:
-                loss = model(self.x, self.y, num_iterations=n_iter, mtp_weights=mtp_w)
+            graph = self._graphs.get(key) if self.use_graphs else None
+            if graph is None and self.use_graphs and self._eager_micro >= 3:
+                graph = self._capture(key, tiny, n_iter, mtp_w)
+            if graph is not None:
+                graph["x"].copy_(self.x)
+                graph["y"].copy_(self.y)
+                if mtp_w is not None:
+                    graph["mtp_w"].copy_(mtp_w)
+                graph["g"].replay()
+                loss_t, metrics = graph["loss"], graph["metrics"]
             else:
-                loss, metrics = model(self.x, self.y)
-            loss_t = loss.detach()
-            (loss / self.grad_accum).backward()
+                if tiny:
+                    loss = model(self.x, self.y, num_iterations=n_iter, mtp_weights=mtp_w)
+                else:
+                    loss, metrics = model(self.x, self.y)
+                loss_t = loss.detach()
+                (loss / self.grad_accum).backward()
+                self._eager_micro += 1
             self.x, self.y, epoch = next(self.train_loader)
         self._pending_epoch = epoch
         self.sched.apply(self.param_groups, self.step)
@@ -133,6 +153,36 @@ class Trainer:
             if self.device.type == "cuda":
                 _lib.check_status(self.device)
         return out
+
+    def _capture(self, key, tiny, n_iter, mtp_w):
+        """Capture forward+backward of one micro-batch into a CUDA graph (static input buffers, gradients accumulate
+        in place into the arenas). Returns None and disables graphs if the capture is refused."""
+        model = self.model
+        sx, sy = torch.empty_like(self.x), torch.empty_like(self.y)
+        sx.copy_(self.x)
+        sy.copy_(self.y)
+        sw = mtp_w.clone() if mtp_w is not None else None
+        g = torch.cuda.CUDAGraph()
+        try:
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                if tiny:
+                    loss = model(sx, sy, num_iterations=n_iter, mtp_weights=sw)
+                    metrics = {}
+                else:
+                    loss, metrics = model(sx, sy)
+                (loss / self.grad_accum).backward()
+                loss_d = loss.detach()
+                metrics = {k: v.detach() for k, v in metrics.items()}
+        except Exception as e:  # noqa: BLE001
+            print0(f"[graphs] capture refused ({type(e).__name__}: {e}); continuing without CUDA graphs")
+            self.use_graphs = False
+            torch.cuda.synchronize()
+            return None
+        # the capture pass itself does not execute kernels: replay once so this micro-batch is accounted for
+        entry = {"g": g, "x": sx, "y": sy, "mtp_w": sw, "loss": loss_d, "metrics": metrics}
+        self._graphs[key] = entry
+        return entry
 
     # ------------------------------------------------------------------ evaluation helpers
     def build_val_loader(self):
