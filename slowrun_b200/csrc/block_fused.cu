@@ -199,29 +199,43 @@ __global__ void iha_mix_bwd_w_kernel(const float* __restrict__ mix, const __nv_b
 }
 
 // dmix[p, h, m] += sum_j dWp[p, h, j] * W[p, m, j].  Each CTA stages `kCols` columns of both operands in shared memory
-// (rows padded by one word against bank conflicts), every thread owns (h, m) pairs, one atomicAdd per pair per CTA.
+// (rows padded by one word against bank conflicts). The H x H result is cut into 4 x 4 register blocks; a thread owns
+// one block for one slice of the staged columns, so every shared-memory word it loads feeds four multiply-adds.
+// Slices are combined with shared-memory atomics, CTAs with one global atomicAdd per entry.
 constexpr int kCols = 512;
 constexpr int kChunksPerCta = 8;
 template <int H>
-__global__ void iha_mix_bwd_mix_kernel(const __nv_bfloat16* __restrict__ dWp, const __nv_bfloat16* __restrict__ W,
-                                       float* __restrict__ dmix, long J) {
+__global__ void __launch_bounds__(kThreads)
+iha_mix_bwd_mix_kernel(const __nv_bfloat16* __restrict__ dWp, const __nv_bfloat16* __restrict__ W,
+                       float* __restrict__ dmix, long J) {
   constexpr int kStride = kCols + 2;
-  __shared__ __nv_bfloat16 sg[H * kStride];
-  __shared__ __nv_bfloat16 sw[H * kStride];
+  constexpr int HB = (H + 3) / 4;                 // 4-row blocks per side
+  constexpr int HP = HB * 4;                      // padded head count (extra rows are zero)
+  constexpr int kBlocks = HB * HB;
+  constexpr int kSlices = kThreads / kBlocks > 0 ? kThreads / kBlocks : 1;
+  constexpr int kSliceCols = (kCols / 2 + kSlices - 1) / kSlices;   // bf16 pairs per slice
+  __shared__ __nv_bfloat16 sg[HP * kStride];
+  __shared__ __nv_bfloat16 sw[HP * kStride];
+  __shared__ float sacc[HP * HP];
   const int p = blockIdx.y;
-  constexpr int kPairs = H * H;
-  constexpr int kPer = (kPairs + kThreads - 1) / kThreads;
-  float acc[kPer];
+  for (int i = threadIdx.x; i < HP * HP; i += kThreads) sacc[i] = 0.f;
+  const int blk = threadIdx.x % kBlocks, slice = threadIdx.x / kBlocks;
+  const int bh = (blk / HB) * 4, bm = (blk % HB) * 4;
+  const bool active = slice < kSlices;
+  float acc[4][4];
 #pragma unroll
-  for (int i = 0; i < kPer; ++i) acc[i] = 0.f;
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
   for (int ch = 0; ch < kChunksPerCta; ++ch) {
     const long j0 = ((long)blockIdx.x * kChunksPerCta + ch) * kCols;
     if (j0 >= J) break;
     const int ncols = (int)min((long)kCols, J - j0);
-    for (int i = threadIdx.x; i < H * (kCols / 2); i += kThreads) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < HP * (kCols / 2); i += kThreads) {
       const int row = i / (kCols / 2), c2 = (i - row * (kCols / 2)) * 2;
       __nv_bfloat162 a = __floats2bfloat162_rn(0.f, 0.f), b = a;
-      if (c2 < ncols) {
+      if (row < H && c2 < ncols) {
         a = *reinterpret_cast<const __nv_bfloat162*>(dWp + ((long)p * H + row) * J + j0 + c2);
         b = *reinterpret_cast<const __nv_bfloat162*>(W + ((long)p * H + row) * J + j0 + c2);
       }
@@ -229,28 +243,32 @@ __global__ void iha_mix_bwd_mix_kernel(const __nv_bfloat16* __restrict__ dWp, co
       *reinterpret_cast<__nv_bfloat162*>(sw + row * kStride + c2) = b;
     }
     __syncthreads();
+    if (active) {
+      const int c_lo = slice * kSliceCols, c_hi = min(kCols / 2, c_lo + kSliceCols);
+      for (int c = c_lo; c < c_hi; ++c) {
+        float2 g[4], w[4];
 #pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-      const int pair = threadIdx.x + i * kThreads;
-      if (pair < kPairs) {
-        const int h = pair / H, m = pair - h * H;
-        const __nv_bfloat16* a = sg + h * kStride;
-        const __nv_bfloat16* b = sw + m * kStride;
-        float s = 0.f;
-#pragma unroll 8
-        for (int c = 0; c < kCols; c += 2) {
-          const float2 x = ld2(a + c), y = ld2(b + c);
-          s += x.x * y.x + x.y * y.y;
+        for (int a = 0; a < 4; ++a) {
+          g[a] = ld2(sg + (bh + a) * kStride + 2 * c);
+          w[a] = ld2(sw + (bm + a) * kStride + 2 * c);
         }
-        acc[i] += s;
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) acc[a][b] += g[a].x * w[b].x + g[a].y * w[b].y;
       }
     }
-    __syncthreads();
   }
+  if (active) {
 #pragma unroll
-  for (int i = 0; i < kPer; ++i) {
-    const int pair = threadIdx.x + i * kThreads;
-    if (pair < kPairs) atomicAdd(dmix + (long)p * kPairs + pair, acc[i]);
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) atomicAdd(&sacc[(bh + a) * HP + bm + b], acc[a][b]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H * H; i += kThreads) {
+    const int h = i / H, m = i - h * H;
+    atomicAdd(dmix + (long)p * H * H + i, sacc[h * HP + m]);
   }
 }
 

@@ -55,6 +55,14 @@ class Trainer:
         self.quiet = quiet
         c = cfg
         seed = c.seed if c.track == "unlimited" else 42
+        self.stream = None
+        if self.device.type == "cuda" and c.cuda_graphs:
+            # Everything runs on one non-default stream from the first forward on: autograd's per-parameter
+            # gradient accumulators remember the stream they were created on, and a CUDA-graph capture must not touch
+            # the default stream.
+            self.stream = torch.cuda.Stream(device=self.device)
+            self.stream.wait_stream(torch.cuda.current_stream(self.device))
+            torch.cuda.set_stream(self.stream)
         self.comm = make_comm(c, info)
         self.model = build_model(c.model, self.device, seed=seed, world_size=info.world_size,
                                  alloc=self.comm.alloc if getattr(self.comm, "fused", False) else None)
@@ -130,6 +138,7 @@ class Trainer:
                 if mtp_w is not None:
                     graph["mtp_w"].copy_(mtp_w)
                 graph["g"].replay()
+                _lib.launch_count += graph["launches"]      # kernels replayed from the graph
                 loss_t, metrics = graph["loss"], graph["metrics"]
             else:
                 if tiny:
@@ -163,9 +172,10 @@ class Trainer:
         sy.copy_(self.y)
         sw = mtp_w.clone() if mtp_w is not None else None
         g = torch.cuda.CUDAGraph()
+        launches0 = _lib.launch_count
         try:
             torch.cuda.synchronize()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, stream=self.stream):
                 if tiny:
                     loss = model(sx, sy, num_iterations=n_iter, mtp_weights=sw)
                     metrics = {}
@@ -180,7 +190,9 @@ class Trainer:
             torch.cuda.synchronize()
             return None
         # the capture pass itself does not execute kernels: replay once so this micro-batch is accounted for
-        entry = {"g": g, "x": sx, "y": sy, "mtp_w": sw, "loss": loss_d, "metrics": metrics}
+        entry = {"g": g, "x": sx, "y": sy, "mtp_w": sw, "loss": loss_d, "metrics": metrics,
+                 "launches": _lib.launch_count - launches0}
+        _lib.launch_count = launches0
         self._graphs[key] = entry
         return entry
 

@@ -462,3 +462,23 @@ def test_cuda_graph_micro_step_matches_eager(tmp_path):
     num = sum((finals[True][1][n] - finals[False][1][n]).pow(2).sum() for n in finals[True][1])
     den = sum(finals[False][1][n].pow(2).sum() for n in finals[False][1])
     assert (num / den).sqrt().item() < 2e-2
+
+
+@pytest.mark.parametrize("H,J", [(20, 128 * 2560), (14, 128 * 1792), (8, 4096 + 66), (2, 1000)])
+def test_iha_mixing_kernels(H, J):
+    from slowrun_b200.ops.block import iha_mix_weights, iha_mix_backward
+    P = 3
+    mixes = (torch.eye(H, device="cuda").expand(P, H, H) + 0.1 * torch.randn(P, H, H, device="cuda")).contiguous()
+    w = _bf(P * H, J, scale=0.05, seed=41)
+    out = iha_mix_weights(mixes, w, H)
+    ref = torch.bmm(mixes.bfloat16().float(), w.view(P, H, J).float())
+    _status_ok()
+    _close(out.view(P, H, J), ref)
+    dwp = _bf(P * H, J, scale=0.01, seed=42)
+    gw = torch.randn(P * H, J, device="cuda")
+    gw_ref = gw.view(P, H, J) + torch.bmm(mixes.bfloat16().float().transpose(1, 2), dwp.view(P, H, J).float())
+    dmix = iha_mix_backward(mixes, w, dwp, gw, H)
+    _status_ok()
+    dmix_ref = torch.bmm(dwp.view(P, H, J).float(), w.view(P, H, J).float().transpose(1, 2))
+    assert torch.allclose(gw.view(P, H, J), gw_ref, rtol=1e-3, atol=1e-3)
+    assert torch.allclose(dmix, dmix_ref, rtol=2e-3, atol=2e-3 * dmix_ref.abs().max().item())
