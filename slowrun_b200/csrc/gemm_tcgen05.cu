@@ -27,11 +27,14 @@ constexpr int kNumThreads = 192;
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  // BN = 160 exists for N = 2560-like widths, where 128x256 tiles leave a third of the last wave idle.
+  static constexpr int kBNLoad = ((BN + 63) / 64) * 64;   // columns staged per k-block (MN-major boxes are 64 wide)
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 160 ? 5 : 6);
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBBytes = kBNLoad * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kTmemCols = (BN == 128) ? 256 : 512;   // two accumulators, power of two
+  static constexpr int kAccStride = (BN == 128) ? 128 : 256;  // column offset of the second accumulator
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
@@ -48,6 +51,9 @@ struct GemmParams {
   float alpha, beta;
   const float* alpha_ptr;  // optional device scalar multiplied into alpha
   int sym;
+  int splitk;              // fp32 accumulate-into output: CTAs own equal shares of (tile, k-block) units and add their
+                           // partial tiles with vector reductions, so the last wave is never partly idle
+
   int* status;
 };
 
@@ -85,6 +91,49 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     }
   }
 }
+
+// Work items of one CTA. Full waves of tiles are strided over the grid (concurrent CTAs work on neighbouring tiles, which
+// keeps their operand panels in L2). In splitk mode the tiles of the last, partial wave are cut along K instead: every
+// CTA gets an equal share of their (tile, k-block) units and adds its partial tile with reductions.
+struct WorkIter {
+  int num_kb, stride, full_tiles;
+  int t;                // cursor over the strided full-wave tiles
+  long long u, u_end;   // cursor / end over the tail units
+  __device__ __forceinline__ void init(const GemmParams& p, int nkb) {
+    num_kb = nkb;
+    stride = gridDim.x;
+    t = blockIdx.x;
+    if (p.splitk) {
+      full_tiles = (p.num_tiles / stride) * stride;
+      const long long units = (long long)(p.num_tiles - full_tiles) * nkb;
+      u = units * blockIdx.x / stride;
+      u_end = units * (blockIdx.x + 1) / stride;
+    } else {
+      full_tiles = p.num_tiles;
+      u = u_end = 0;
+    }
+  }
+  // partial = true: the item covers only part of K (or shares its tile with other CTAs) and must be added atomically
+  __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1, bool& partial) {
+    if (t < full_tiles) {
+      tile = t;
+      kb0 = 0;
+      kb1 = num_kb;
+      partial = false;
+      t += stride;
+      return true;
+    }
+    if (u >= u_end) return false;
+    const int tt = (int)(u / num_kb);
+    tile = full_tiles + tt;
+    kb0 = (int)(u - (long long)tt * num_kb);
+    const long long len = min((long long)(num_kb - kb0), u_end - u);
+    kb1 = kb0 + (int)len;
+    partial = true;
+    u += len;
+    return true;
+  }
+};
 
 __device__ __forceinline__ bool sym_tile_skipped(int r, int c, int bn) {
   // the tile that would own element (r, c): mi = r / BM, nj = c / bn; skipped iff it lies below the diagonal band
@@ -140,16 +189,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      WorkIter wi;
+      wi.init(p, num_kb);
+      int tile, kb0, kb1;
+      bool partial;
+      while (ok && wi.next(tile, kb0, kb1, partial)) {
         int b, mi, nj;
         tile_coords<BN>(p, tile, b, mi, nj);
         const int m0 = mi * BM, n0 = nj * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
           if (!ok) break;
           uint8_t* sa = smem + stage * C_::kStageBytes;
           uint8_t* sb = sa + C_::kABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], C_::kStageBytes);
+          mbar_arrive_expect_tx(&full_bar[stage], C_::kABytes + (p.b_mn ? C_::kBBytes : BN * BK * 2));
           const int k0 = kb * BK;
           if (!p.a_mn) {
             tma_load_3d(sa, &map_a, &full_bar[stage], k0, m0, b);
@@ -161,7 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tma_load_3d(sb, &map_b, &full_bar[stage], k0, n0, b);
           } else {
 #pragma unroll
-            for (int g = 0; g < BN / 64; ++g) tma_load_3d(sb + g * (BK * 128), &map_b, &full_bar[stage], n0 + g * 64, k0, b);
+            for (int g = 0; g < C_::kBNLoad / 64; ++g) tma_load_3d(sb + g * (BK * 128), &map_b, &full_bar[stage], n0 + g * 64, k0, b);
           }
           if (++stage == C_::kStages) {
             stage = 0;
@@ -181,14 +234,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local) {
+      WorkIter wi;
+      wi.init(p, num_kb);
+      int tile, kb0, kb1;
+      bool partial;
+      for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
         ok = mbar_wait(&tempty_bar[buf], acc_phase ^ 1u, abort_flag, p.status, 200);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * C_::kAccStride);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201);
           if (!ok) break;
           tc_fence_after();
@@ -198,7 +255,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t bdesc = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16_ss(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(tmem_d, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == C_::kStages) {
@@ -214,7 +271,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local) {
+    WorkIter wi;
+    wi.init(p, num_kb);
+    int tile, kb0, kb1;
+    bool partial;
+    for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
       int b, mi, nj;
       tile_coords<BN>(p, tile, b, mi, nj);
       const int buf = local & 1;
@@ -226,7 +287,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       const int r = mi * BM + q * 32 + lane;
       const bool row_ok = r < p.M;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * C_::kAccStride);
       uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C) + (size_t)b * p.strideC * (p.c_fp32 ? 4 : 2);
       const uint8_t* cinbase =
           p.Cin ? reinterpret_cast<const uint8_t*>(p.Cin) + (size_t)b * p.strideCin * (p.cin_fp32 ? 4 : 2) : nullptr;
@@ -241,6 +302,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = alpha * __uint_as_float(v[j]);
           const bool full = (c0 + 32 <= p.N);
+          if (partial) {
+            // partial tile of an accumulate-into fp32 output: add it with 16-byte reductions
+            float* dst = reinterpret_cast<float*>(cbase) + (size_t)r * p.ldc + c0;
+            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(f[j]), "f"(f[j + 1]),
+                             "f"(f[j + 2]), "f"(f[j + 3])
+                             : "memory");
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < p.N) atomicAdd(dst + j, f[j]);
+            }
+            continue;
+          }
           if (cinbase) {
             if (p.cin_fp32) {
               const float* src = reinterpret_cast<const float*>(cinbase) + (size_t)r * p.ldcin + c0;
@@ -392,7 +468,13 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int max_
   p.num_tiles = per_batch * p.batch;
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (p.num_tiles < grid) grid = p.num_tiles;
+  if (p.splitk) {
+    const long long units = (long long)p.num_tiles * ((p.K + BK - 1) / BK);
+    if (units < grid) grid = (int)units;
+    if (p.num_tiles % grid == 0) p.splitk = 0;   // no partial wave: nothing to balance
+  } else if (p.num_tiles < grid) {
+    grid = p.num_tiles;
+  }
   if (grid <= 0) return 0;
   gemm_bf16_kernel<BN><<<grid, kNumThreads, Cfg<BN>::kSmemBytes, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -420,6 +502,10 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   p.C = C; p.ldc = ldc; p.strideC = strideC; p.c_fp32 = c_fp32;
   p.Cin = Cin; p.ldcin = ldcin; p.strideCin = strideCin; p.cin_fp32 = cin_fp32;
   p.alpha = alpha; p.beta = beta; p.alpha_ptr = alpha_ptr; p.sym = sym; p.status = status;
+  // accumulate-into fp32 output (weight gradients): balance the k-loop over all SMs instead of whole tiles
+  p.splitk = (c_fp32 && Cin == C && beta == 1.0f && !sym && ldcin == ldc && strideCin == strideC) ? 1 : 0;
+  if (bn < 0) { p.splitk = 0; bn = -bn; }   // negative bn: caller forces the plain tile schedule
+  if (bn == 0 && p.splitk) bn = 256;
   if (bn == 0) {
     // prefer the 256-wide tile unless it leaves most of a wave idle
     const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256) * batch;
@@ -430,15 +516,25 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
     const long long waves128 = (t128 + sms - 1) / sms;
     const double eff128 = (double)t128 / (double)(waves128 * sms);
     bn = (eff256 + 0.08 >= eff128 && N > 128) ? 256 : 128;
+    // 160-wide tiles when N is a multiple of 160 and they fill the waves better than both
+    if (N % 160 == 0 && !b_mn) {
+      const long long t160 = (long long)((M + 127) / 128) * (N / 160) * batch;
+      const long long waves160 = (t160 + sms - 1) / sms;
+      const double eff160 = (double)t160 / (double)(waves160 * sms);
+      const double best = bn == 256 ? eff256 : eff128 * 0.92;
+      if (eff160 * 0.97 > best + 0.03) bn = 160;
+    }
   }
   CUtensorMap ma, mb;
   int rc;
   if (!a_mn) rc = encode_bf16_map(&ma, A, K, M, batch, lda, strideA, BK, BM);
   else       rc = encode_bf16_map(&ma, A, M, K, batch, lda, strideA, 64, BK);
   if (rc) return rc;
+  if (bn != 128 && bn != 160 && bn != 256) return -7;
   if (!b_mn) rc = encode_bf16_map(&mb, B, K, N, batch, ldb, strideB, BK, bn);
   else       rc = encode_bf16_map(&mb, B, N, K, batch, ldb, strideB, 64, BK);
   if (rc) return rc - 10;
   if (bn == 256) return launch<256>(ma, mb, p, max_ctas, stream);
+  if (bn == 160) return launch<160>(ma, mb, p, max_ctas, stream);
   return launch<128>(ma, mb, p, max_ctas, stream);
 }
