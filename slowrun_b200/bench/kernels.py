@@ -1,0 +1,124 @@
+"""Kernel micro-benchmarks (CUDA-event timed, warm-up, L2 flushed between iterations) and the small fixed workloads
+that the ncu captures under profiles/ are taken on.
+
+    python -m slowrun_b200.bench.kernels gemm --m 8192 --n 7680 --k 2560 [--a-mn] [--b-mn] [--acc] [--iters 20]
+    python -m slowrun_b200.bench.kernels attn --b 4 --t 2048 --h 20 --window 1024 [--bwd]
+    python -m slowrun_b200.bench.kernels ce --m 8192 --v 50304
+    python -m slowrun_b200.bench.kernels ns --n 4 --r 2560 --c 2560
+Prints one JSON line per run with the achieved rate and its fraction of the measured peaks in MEASURED_PEAKS.json
+(fallback 6.65 TB/s, 1590 TFLOP/s when the file is absent).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, 1590.0, "fallback"
+
+
+def timed(fn, iters, flush=True):
+    scratch = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.zero_()          # 160 MB write: evicts the 126 MB L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "ce", "ns"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=7680)
+    ap.add_argument("--k", type=int, default=2560)
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--acc", action="store_true", help="fp32 accumulate-into output (weight-gradient form)")
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--b", type=int, default=4)
+    ap.add_argument("--t", type=int, default=2048)
+    ap.add_argument("--h", type=int, default=20)
+    ap.add_argument("--window", type=int, default=-1)
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--v", type=int, default=50304)
+    ap.add_argument("--r", type=int, default=2560)
+    ap.add_argument("--c", type=int, default=2560)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+    sys.path.insert(0, ROOT)
+    from slowrun_b200.ops import _lib
+    from slowrun_b200.ops.gemm import gemm
+    hbm, tf, src = peaks()
+    out = {"what": a.what, "peaks": src}
+    if a.what == "gemm":
+        A = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device="cuda").bfloat16() * 0.1
+        B = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device="cuda").bfloat16() * 0.1
+        C = torch.zeros(a.m, a.n, device="cuda", dtype=torch.float32 if a.acc else torch.bfloat16)
+        if a.acc:
+            fn = lambda: gemm(A, B, out=C, cin=C, a_mn=a.a_mn, b_mn=a.b_mn, beta=1.0, bn=a.bn)
+        else:
+            fn = lambda: gemm(A, B, out=C, a_mn=a.a_mn, b_mn=a.b_mn, bn=a.bn)
+        ms = timed(fn, a.iters, not a.no_flush)
+        fl = 2.0 * a.m * a.n * a.k
+        out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tf)
+    elif a.what == "attn":
+        from slowrun_b200.ops.flash_attention import native_bwd, native_fwd
+        q, k, v = (torch.randn(a.b, a.t, a.h, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        keys = sum(min(i, a.window if a.window >= 0 else i) + 1 for i in range(a.t))
+        fl = 4.0 * a.b * a.h * keys * 128
+        o, lse, sc, w = native_fwd(q, k, v, a.window, None)
+        if a.bwd:
+            dy = torch.randn_like(o)
+            ms = timed(lambda: native_bwd(dy, q, k, v, o, lse, sc, w), a.iters, not a.no_flush)
+            fl *= 2.5
+        else:
+            ms = timed(lambda: native_fwd(q, k, v, a.window, None), a.iters, not a.no_flush)
+        out.update(shape=[a.b, a.t, a.h, 128], window=a.window, bwd=a.bwd, ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tf)
+    elif a.what == "ce":
+        from slowrun_b200.ops import functional as ops
+        logits = torch.randn(a.m, a.v, device="cuda").bfloat16()
+        tgt = torch.randint(0, a.v - 64, (a.m,), device="cuda")
+        loss = torch.empty(a.m, device="cuda")
+        scale = torch.full((), 1.0 / a.m, device="cuda")
+        fn = lambda: ops._call("sr_softcap_ce", ops._CE_ARGS, logits.data_ptr(), tgt.data_ptr(), loss.data_ptr(), 0, 1,
+                               scale.data_ptr(), a.m, a.v, a.v - 47, a.v, 10.0, 1, _lib.stream_ptr())
+        ms = timed(fn, a.iters, not a.no_flush)
+        byts = a.m * a.v * 2 * 2.0      # one read from HBM, one write (second read is served by L2)
+        out.update(shape=[a.m, a.v], ms=ms, gbs=byts / ms / 1e6, frac_of_peak=byts / ms / 1e6 / hbm)
+    else:
+        from slowrun_b200.optim.muon_adamw import _NSWorkspace, newton_schulz_cuda
+        X = (torch.randn(a.n, a.r, a.c, device="cuda") / (a.r * a.c) ** 0.5).bfloat16()
+        ws = _NSWorkspace(a.n, a.r, a.c, "cuda")
+        ms = timed(lambda: newton_schulz_cuda(X.clone(), 5, ws), a.iters, not a.no_flush)
+        g, o = min(a.r, a.c), max(a.r, a.c)
+        fl = 5 * a.n * (4.0 * g * g * o + 2.0 * g ** 3)      # full (non-symmetric) cost, the reference's bmm count
+        out.update(shape=[a.n, a.r, a.c], ms=ms, tflops_equiv=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tf)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
