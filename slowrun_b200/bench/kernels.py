@@ -66,10 +66,13 @@ def main():
     ap.add_argument("--c", type=int, default=2560)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--no-pair", action="store_true", help="GEMMs on the single-CTA kernel only")
     a = ap.parse_args()
     sys.path.insert(0, ROOT)
     from slowrun_b200.ops import _lib
-    from slowrun_b200.ops.gemm import gemm
+    from slowrun_b200.ops.gemm import gemm, set_pair_mode
+    if a.no_pair:
+        set_pair_mode(False)
     hbm, tf, src = peaks()
     out = {"what": a.what, "peaks": src}
     if a.what == "gemm":

@@ -14,16 +14,9 @@
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2..5 = epilogue.
 // The reference does these products with cuBLAS through torch (train.py:286-323 F.linear, train.py:614-621 bmm).
-#include "sm100_common.cuh"
+#include "gemm_common.cuh"
 
 namespace {
-
-using namespace sr;
-
-constexpr int BM = 128;
-constexpr int BK = 64;  // 64 bf16 = 128 B = one swizzle row
-constexpr int UMMA_K = 16;
-constexpr int kNumThreads = 192;
 
 template <int BN>
 struct Cfg {
@@ -37,109 +30,6 @@ struct Cfg {
   static constexpr int kAccStride = (BN == 128) ? 128 : 256;  // column offset of the second accumulator
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
-
-struct GemmParams {
-  int M, N, K, batch;
-  int tiles_m, tiles_n, num_tiles;
-  int a_mn, b_mn;
-  void* C;
-  long long ldc, strideC;
-  int c_fp32;
-  const void* Cin;
-  long long ldcin, strideCin;
-  int cin_fp32;
-  float alpha, beta;
-  const float* alpha_ptr;  // optional device scalar multiplied into alpha
-  int sym;
-  int splitk;              // fp32 accumulate-into output: CTAs own equal shares of (tile, k-block) units and add their
-                           // partial tiles with vector reductions, so the last wave is never partly idle
-
-  int* status;
-};
-
-// Tile index -> (batch, mi, nj). In sym mode rows only hold the tiles that touch the upper triangle.
-template <int BN>
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& b, int& mi, int& nj) {
-  if (!p.sym) {
-    const int per_batch = p.tiles_m * p.tiles_n;
-    b = tile / per_batch;
-    int t = tile - b * per_batch;
-    // groups of 8 M-tiles share their B tiles in L2
-    constexpr int G = 8;
-    const int group_sz = G * p.tiles_n;
-    const int g = t / group_sz;
-    const int first_m = g * G;
-    const int gm = min(G, p.tiles_m - first_m);
-    const int tt = t - g * group_sz;
-    mi = first_m + tt % gm;
-    nj = tt / gm;
-  } else {
-    int per_batch = 0;
-    for (int r = 0; r < p.tiles_m; ++r) per_batch += p.tiles_n - (r * BM) / BN;
-    b = tile / per_batch;
-    int t = tile - b * per_batch;
-    mi = 0;
-    while (true) {
-      const int first = (mi * BM) / BN;
-      const int cnt = p.tiles_n - first;
-      if (t < cnt) {
-        nj = first + t;
-        break;
-      }
-      t -= cnt;
-      ++mi;
-    }
-  }
-}
-
-// Work items of one CTA. Full waves of tiles are strided over the grid (concurrent CTAs work on neighbouring tiles, which
-// keeps their operand panels in L2). In splitk mode the tiles of the last, partial wave are cut along K instead: every
-// CTA gets an equal share of their (tile, k-block) units and adds its partial tile with reductions.
-struct WorkIter {
-  int num_kb, stride, full_tiles;
-  int t;                // cursor over the strided full-wave tiles
-  long long u, u_end;   // cursor / end over the tail units
-  __device__ __forceinline__ void init(const GemmParams& p, int nkb) {
-    num_kb = nkb;
-    stride = gridDim.x;
-    t = blockIdx.x;
-    if (p.splitk) {
-      full_tiles = (p.num_tiles / stride) * stride;
-      const long long units = (long long)(p.num_tiles - full_tiles) * nkb;
-      u = units * blockIdx.x / stride;
-      u_end = units * (blockIdx.x + 1) / stride;
-    } else {
-      full_tiles = p.num_tiles;
-      u = u_end = 0;
-    }
-  }
-  // partial = true: the item covers only part of K (or shares its tile with other CTAs) and must be added atomically
-  __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1, bool& partial) {
-    if (t < full_tiles) {
-      tile = t;
-      kb0 = 0;
-      kb1 = num_kb;
-      partial = false;
-      t += stride;
-      return true;
-    }
-    if (u >= u_end) return false;
-    const int tt = (int)(u / num_kb);
-    tile = full_tiles + tt;
-    kb0 = (int)(u - (long long)tt * num_kb);
-    const long long len = min((long long)(num_kb - kb0), u_end - u);
-    kb1 = kb0 + (int)len;
-    partial = true;
-    u += len;
-    return true;
-  }
-};
-
-__device__ __forceinline__ bool sym_tile_skipped(int r, int c, int bn) {
-  // the tile that would own element (r, c): mi = r / BM, nj = c / bn; skipped iff it lies below the diagonal band
-  const int mi = r / BM, nj = c / bn;
-  return nj * bn + bn <= mi * BM;
-}
 
 template <int BN>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -190,7 +80,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p, num_kb);
+      wi.init(p, num_kb, blockIdx.x, gridDim.x);
       int tile, kb0, kb1;
       bool partial;
       while (ok && wi.next(tile, kb0, kb1, partial)) {
@@ -235,7 +125,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int local = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p, num_kb);
+      wi.init(p, num_kb, blockIdx.x, gridDim.x);
       int tile, kb0, kb1;
       bool partial;
       for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
@@ -272,7 +162,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int local = 0;
     bool ok = true;
     WorkIter wi;
-    wi.init(p, num_kb);
+    wi.init(p, num_kb, blockIdx.x, gridDim.x);
     int tile, kb0, kb1;
     bool partial;
     for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
@@ -301,93 +191,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = alpha * __uint_as_float(v[j]);
-          const bool full = (c0 + 32 <= p.N);
-          if (partial) {
-            // partial tile of an accumulate-into fp32 output: add it with 16-byte reductions
-            float* dst = reinterpret_cast<float*>(cbase) + (size_t)r * p.ldc + c0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(f[j]), "f"(f[j + 1]),
-                             "f"(f[j + 2]), "f"(f[j + 3])
-                             : "memory");
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < p.N) atomicAdd(dst + j, f[j]);
-            }
-            continue;
-          }
-          if (cinbase) {
-            if (p.cin_fp32) {
-              const float* src = reinterpret_cast<const float*>(cinbase) + (size_t)r * p.ldcin + c0;
-              if (full && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                  const float4 t = *reinterpret_cast<const float4*>(src + j);
-                  f[j] += p.beta * t.x; f[j + 1] += p.beta * t.y; f[j + 2] += p.beta * t.z; f[j + 3] += p.beta * t.w;
-                }
-              } else {
-                for (int j = 0; j < 32; ++j)
-                  if (c0 + j < p.N) f[j] += p.beta * src[j];
-              }
-            } else {
-              const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cinbase) + (size_t)r * p.ldcin + c0;
-              if (full && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  const uint4 t = *reinterpret_cast<const uint4*>(src + j);
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 ff = __bfloat1622float2(h[e]);
-                    f[j + 2 * e] += p.beta * ff.x;
-                    f[j + 2 * e + 1] += p.beta * ff.y;
-                  }
-                }
-              } else {
-                for (int j = 0; j < 32; ++j)
-                  if (c0 + j < p.N) f[j] += p.beta * __bfloat162float(src[j]);
-              }
-            }
-          }
-          if (p.c_fp32) {
-            float* dst = reinterpret_cast<float*>(cbase) + (size_t)r * p.ldc + c0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < p.N) dst[j] = f[j];
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cbase) + (size_t)r * p.ldc + c0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 t;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[j + 2 * e], f[j + 2 * e + 1]);
-                *reinterpret_cast<uint4*>(dst + j) = t;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < p.N) dst[j] = __float2bfloat16(f[j]);
-            }
-          }
-          if (p.sym) {
-            // mirrored store for the tiles that were not computed; lanes hold consecutive rows, so each
-            // store instruction writes 32 consecutive elements of one output row.
-            for (int j = 0; j < 32; ++j) {
-              const int c = c0 + j;
-              if (c < p.N && c > r && sym_tile_skipped(c, r, BN)) {
-                if (p.c_fp32)
-                  reinterpret_cast<float*>(cbase)[(size_t)c * p.ldc + r] = f[j];
-                else
-                  reinterpret_cast<__nv_bfloat16*>(cbase)[(size_t)c * p.ldc + r] = __float2bfloat16(f[j]);
-              }
-            }
-          }
+          epilogue_store<BN>(p, f, r, c0, partial, cbase, cinbase);
         }
       }
       tc_fence_before();
@@ -402,50 +206,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, C_::kTmemCols);
   }
-}
-
-// ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// 3-D bf16 tensor map {inner, rows, batch}, 128B swizzle, zero fill outside the tensor.
-int encode_bf16_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t ld,
-                    uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return -1;
-  if ((ld % 8) != 0 || (reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return -2;
-  if (batch > 1 && (batch_stride % 8) != 0) return -2;
-  cuuint64_t dims[3] = {inner, rows, batch};
-  cuuint64_t strides[2] = {ld * 2, (batch > 1 ? batch_stride : rows * ld) * 2};
-  cuuint32_t box[3] = {box_inner, box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
-}
-
-int num_sms() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
 }
 
 template <int BN>
@@ -482,6 +242,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int max_
 
 }  // namespace
 
+extern "C" int sr_gemm_bf16_pair(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
+                                 long long lda, long long ldb, long long ldc, long long ldcin, long long strideA,
+                                 long long strideB, long long strideC, long long strideCin, int a_mn, int b_mn,
+                                 int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr, int splitk,
+                                 int bn, int max_ctas, int* status, cudaStream_t stream);
+
+static int g_pair_mode = 1;
+// 1 (default): eligible problems run on the CTA-pair kernel (gemm_tcgen05_pair.cu); 0: single-CTA kernel only.
+extern "C" void sr_gemm_set_pair_mode(int on) { g_pair_mode = on; }
+
 // out[b] = alpha * op(A[b]) op(B[b])^T + beta * Cin[b]; see the file header.
 //   a_mn / b_mn : 0 = operand stored [rows, K] (K contiguous), 1 = stored [K, rows] (rows contiguous)
 //   lda / ldb   : leading dimension (elements) of the stored 2-D array; stride* : per-batch element stride
@@ -505,32 +275,38 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   // accumulate-into fp32 output (weight gradients): balance the k-loop over all SMs instead of whole tiles
   p.splitk = (c_fp32 && Cin == C && beta == 1.0f && !sym && ldcin == ldc && strideCin == strideC) ? 1 : 0;
   if (bn < 0) { p.splitk = 0; bn = -bn; }   // negative bn: caller forces the plain tile schedule
+  // CTA pairs (256-row tiles over 74 pairs) for everything but symmetric outputs and single-tile-high problems
+  const bool use_pair = g_pair_mode && !sym && M > BM;
+  const int rows = use_pair ? 2 * BM : BM;
+  const int workers = use_pair ? num_sms() / 2 : num_sms();
   if (bn == 0 && p.splitk) bn = 256;
   if (bn == 0) {
     // prefer the 256-wide tile unless it leaves most of a wave idle
-    const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256) * batch;
-    const int sms = num_sms();
-    const long long waves256 = (t256 + sms - 1) / sms;
-    const double eff256 = (double)t256 / (double)(waves256 * sms);
-    const long long t128 = (long long)((M + 127) / 128) * ((N + 127) / 128) * batch;
-    const long long waves128 = (t128 + sms - 1) / sms;
-    const double eff128 = (double)t128 / (double)(waves128 * sms);
+    const long long tm = (M + rows - 1) / rows;
+    auto eff = [&](long long tiles) {
+      const long long waves = (tiles + workers - 1) / workers;
+      return (double)tiles / (double)(waves * workers);
+    };
+    const double eff256 = eff(tm * ((N + 255) / 256) * batch);
+    const double eff128 = eff(tm * ((N + 127) / 128) * batch);
     bn = (eff256 + 0.08 >= eff128 && N > 128) ? 256 : 128;
     // 160-wide tiles when N is a multiple of 160 and they fill the waves better than both
     if (N % 160 == 0 && !b_mn) {
-      const long long t160 = (long long)((M + 127) / 128) * (N / 160) * batch;
-      const long long waves160 = (t160 + sms - 1) / sms;
-      const double eff160 = (double)t160 / (double)(waves160 * sms);
+      const double eff160 = eff(tm * (N / 160) * batch);
       const double best = bn == 256 ? eff256 : eff128 * 0.92;
       if (eff160 * 0.97 > best + 0.03) bn = 160;
     }
   }
+  if (bn != 128 && bn != 160 && bn != 256) return -7;
+  if (use_pair && !(bn == 160 && b_mn))
+    return sr_gemm_bf16_pair(A, B, C, Cin, M, N, K, batch, lda, ldb, ldc, ldcin, strideA, strideB, strideC, strideCin,
+                             a_mn, b_mn, c_fp32, cin_fp32, alpha, beta, alpha_ptr, p.splitk, bn, max_ctas, status,
+                             stream);
   CUtensorMap ma, mb;
   int rc;
   if (!a_mn) rc = encode_bf16_map(&ma, A, K, M, batch, lda, strideA, BK, BM);
   else       rc = encode_bf16_map(&ma, A, M, K, batch, lda, strideA, 64, BK);
   if (rc) return rc;
-  if (bn != 128 && bn != 160 && bn != 256) return -7;
   if (!b_mn) rc = encode_bf16_map(&mb, B, K, N, batch, ldb, strideB, BK, bn);
   else       rc = encode_bf16_map(&mb, B, N, K, batch, ldb, strideB, 64, BK);
   if (rc) return rc - 10;

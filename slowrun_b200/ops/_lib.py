@@ -44,6 +44,8 @@ def lib() -> ctypes.CDLL:
                 from ..csrc import build as _build
                 _build.build()
             _lib = ctypes.CDLL(_SO)
+            if os.environ.get("SR_GEMM_PAIR", "1") == "0":
+                _lib.sr_gemm_set_pair_mode(0)
     return _lib
 
 

@@ -114,3 +114,12 @@ def mm_nn(x, w, **kw):
 def mm_tn(x, y, **kw):
     """x[K,M].T @ y[K,N]"""
     return gemm(x, y, a_mn=True, b_mn=True, **kw)
+
+
+def set_pair_mode(on: bool) -> None:
+    """Route eligible products to the CTA-pair kernel (`csrc/gemm_tcgen05_pair.cu`, the default) or keep every
+    product on the single-CTA kernel. `SR_GEMM_PAIR=0` in the environment selects the latter at import."""
+    f = _lib.lib().sr_gemm_set_pair_mode
+    f.argtypes = [_lib.c_int]
+    f.restype = None
+    f(1 if on else 0)
