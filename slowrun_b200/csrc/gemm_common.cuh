@@ -26,6 +26,7 @@ struct GemmParams {
   float alpha, beta;
   const float* alpha_ptr;  // optional device scalar multiplied into alpha
   int sym;
+  int tail_split;          // >1: the tiles of the last, partial wave are cut into this many column slices (pair kernel)
   int splitk;              // fp32 accumulate-into output: CTAs own equal shares of (tile, k-block) units and add their
                            // partial tiles with vector reductions, so the last wave is never partly idle
 
@@ -74,11 +75,27 @@ struct WorkIter {
   int num_kb, stride, full_tiles;
   int t;                // cursor over the strided full-wave tiles
   long long u, u_end;   // cursor / end over the tail units
+  int split, v, v_end;  // column-sliced tail (tail_split mode): slices per tile, cursor and end over the slices
+  int n_off, n_w;       // column slice of the current item within its tile (set by next())
+  int bn_full;
   // worker / nworkers: this CTA (or CTA pair) and how many of them share the problem
-  __device__ __forceinline__ void init(const GemmParams& p, int nkb, int worker, int nworkers) {
+  __device__ __forceinline__ void init(const GemmParams& p, int nkb, int worker, int nworkers, int bn) {
     num_kb = nkb;
     stride = nworkers;
     t = worker;
+    n_off = 0;
+    n_w = bn;
+    bn_full = bn;
+    split = 1;
+    v = v_end = 0;
+    if (!p.splitk && p.tail_split > 1) {
+      split = p.tail_split;
+      full_tiles = (p.num_tiles / stride) * stride;
+      v = worker;
+      v_end = (p.num_tiles - full_tiles) * split;
+      u = u_end = 0;
+      return;
+    }
     if (p.splitk) {
       full_tiles = (p.num_tiles / stride) * stride;
       const long long units = (long long)(p.num_tiles - full_tiles) * nkb;
@@ -97,6 +114,17 @@ struct WorkIter {
       kb1 = num_kb;
       partial = false;
       t += stride;
+      return true;
+    }
+    if (split > 1) {
+      if (v >= v_end) return false;
+      tile = full_tiles + v / split;
+      n_w = bn_full / split;
+      n_off = (v % split) * n_w;
+      kb0 = 0;
+      kb1 = num_kb;
+      partial = false;
+      v += stride;
       return true;
     }
     if (u >= u_end) return false;

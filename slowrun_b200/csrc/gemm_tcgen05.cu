@@ -80,7 +80,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p, num_kb, blockIdx.x, gridDim.x);
+      wi.init(p, num_kb, blockIdx.x, gridDim.x, BN);
       int tile, kb0, kb1;
       bool partial;
       while (ok && wi.next(tile, kb0, kb1, partial)) {
@@ -125,7 +125,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int local = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p, num_kb, blockIdx.x, gridDim.x);
+      wi.init(p, num_kb, blockIdx.x, gridDim.x, BN);
       int tile, kb0, kb1;
       bool partial;
       for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
@@ -162,7 +162,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int local = 0;
     bool ok = true;
     WorkIter wi;
-    wi.init(p, num_kb, blockIdx.x, gridDim.x);
+    wi.init(p, num_kb, blockIdx.x, gridDim.x, BN);
     int tile, kb0, kb1;
     bool partial;
     for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
@@ -283,16 +283,18 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   if (bn == 0) {
     // prefer the 256-wide tile unless it leaves most of a wave idle
     const long long tm = (M + rows - 1) / rows;
-    auto eff = [&](long long tiles) {
-      const long long waves = (tiles + workers - 1) / workers;
-      return (double)tiles / (double)(waves * workers);
+    // tiles / (waves * workers); the pair kernel halves a last wave that at most half of the pairs would join
+    auto eff = [&](long long tiles, bool splittable) {
+      const long long full = tiles / workers, rem = tiles % workers;
+      const double waves = (double)full + (rem == 0 ? 0.0 : (splittable && 2 * rem <= workers ? 0.5 : 1.0));
+      return (double)tiles / (waves * workers);
     };
-    const double eff256 = eff(tm * ((N + 255) / 256) * batch);
-    const double eff128 = eff(tm * ((N + 127) / 128) * batch);
+    const double eff256 = eff(tm * ((N + 255) / 256) * batch, use_pair);
+    const double eff128 = eff(tm * ((N + 127) / 128) * batch, false);
     bn = (eff256 + 0.08 >= eff128 && N > 128) ? 256 : 128;
     // 160-wide tiles when N is a multiple of 160 and they fill the waves better than both
     if (N % 160 == 0 && !b_mn) {
-      const double eff160 = eff(tm * (N / 160) * batch);
+      const double eff160 = eff(tm * (N / 160) * batch, false);
       const double best = bn == 256 ? eff256 : eff128 * 0.92;
       if (eff160 * 0.97 > best + 0.03) bn = 160;
     }

@@ -147,7 +147,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       uint32_t phase = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p, num_kb, pair, num_pairs);
+      wi.init(p, num_kb, pair, num_pairs, BN);
       int tile, kb0, kb1;
       bool partial;
       const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);   // the leader's full barriers
@@ -156,14 +156,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         int b, mi, nj;
         tile_coords<BN>(p, tile, b, mi, nj);
         const int m0 = mi * PM + (int)rank * BM;
-        const int n0 = nj * BN + (int)rank * C_::kBHalf;
+        const int n0 = nj * BN + wi.n_off + (int)rank * (wi.n_w / 2);   // a column slice loads the same boxes, uses fewer rows
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
           if (!ok) break;
           uint8_t* sa = smem + stage * C_::kStageBytes;
           uint8_t* sb = sa + C_::kABytes;
-          if (rank == 0)
-            mbar_arrive_expect_tx(&full_bar[stage], 2u * (C_::kABytes + (p.b_mn ? (uint32_t)C_::kBBytes : kBLoadBytes)));
+          if (rank == 0) {
+            const uint32_t b_bytes = p.b_mn ? (uint32_t)((wi.n_w / 2 + 63) / 64) * (64 * BK * 2) : kBLoadBytes;
+            mbar_arrive_expect_tx(&full_bar[stage], 2u * (C_::kABytes + b_bytes));
+          }
           const uint32_t fb = full0 + stage * 8;
           const int k0 = kb * BK;
           if (!p.a_mn) {
@@ -177,7 +179,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           } else {
 #pragma unroll
             for (int g = 0; g < C_::kBHalfLoad / 64; ++g)
-              tma_load_3d_pair(sb + g * (BK * 128), &map_b, fb, n0 + g * 64, k0, b);
+              if (g * 64 < wi.n_w / 2) tma_load_3d_pair(sb + g * (BK * 128), &map_b, fb, n0 + g * 64, k0, b);
           }
           if (++stage == C_::kStages) {
             stage = 0;
@@ -189,7 +191,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && elect_one()) {
-      const uint32_t idesc = make_idesc(1, 1, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u, PM, BN);
       const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, b_lbo = p.b_mn ? BK * 128 : 16;
       const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : UMMA_K * 2;
       const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : UMMA_K * 2;
@@ -198,7 +199,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       int local = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p, num_kb, pair, num_pairs);
+      wi.init(p, num_kb, pair, num_pairs, BN);
       int tile, kb0, kb1;
       bool partial;
       for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
@@ -208,6 +209,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * C_::kAccStride);
+        const uint32_t idesc = make_idesc(1, 1, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u, PM, (uint32_t)wi.n_w);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201);
           if (!ok) break;
@@ -235,7 +237,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int local = 0;
     bool ok = true;
     WorkIter wi;
-    wi.init(p, num_kb, pair, num_pairs);
+    wi.init(p, num_kb, pair, num_pairs, BN);
     int tile, kb0, kb1;
     bool partial;
     const uint32_t tempty0 = map_to_cta(smem_u32(&tempty_bar[0]), 0);
@@ -255,12 +257,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C) + (size_t)b * p.strideC * (p.c_fp32 ? 4 : 2);
       const uint8_t* cinbase =
           p.Cin ? reinterpret_cast<const uint8_t*>(p.Cin) + (size_t)b * p.strideCin * (p.cin_fp32 ? 4 : 2) : nullptr;
+      const int nch = (wi.n_w + 31) / 32;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
+      for (int ch = 0; ch < nch; ++ch) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + ch * 32, v);
         tc_wait_ld();
-        const int c0 = nj * BN + ch * 32;
+        const int c0 = nj * BN + wi.n_off + ch * 32;
         if (row_ok && c0 < p.N) {
           float f[32];
 #pragma unroll
@@ -298,12 +301,17 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int
   int pairs = num_sms() / 2;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
   if (pairs < 1) pairs = 1;
+  p.tail_split = 1;
   if (p.splitk) {
     const long long units = (long long)p.num_tiles * ((p.K + BK - 1) / BK);
     if (units < pairs) pairs = (int)units;
     if (p.num_tiles % pairs == 0) p.splitk = 0;
-  } else if (p.num_tiles < pairs) {
-    pairs = p.num_tiles;
+  } else {
+    // last, partial wave: when at most half of the pairs would have a tile, cut those tiles into two 128-wide
+    // column slices so that the wave takes half as long
+    const int rem = p.num_tiles % pairs;
+    if (BN == 256 && rem > 0 && 2 * rem <= pairs) p.tail_split = 2;
+    if (p.num_tiles < pairs) pairs = p.num_tiles * p.tail_split;
   }
   if (pairs <= 0) return 0;
   cudaLaunchConfig_t cfg{};

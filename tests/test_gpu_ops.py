@@ -52,6 +52,27 @@ def test_gemm_fp32_accumulate_and_device_alpha(K, Mo, No, bn):
     assert torch.allclose(acc, ref, rtol=2e-3, atol=2e-3 * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn,bn", [
+    (8192, 2560, 320, False, True, 256),    # 320 pair tiles: 4 full waves + a column-sliced tail
+    (8192, 2500, 264, False, False, 256),   # same with a ragged right edge inside the sliced tiles
+    (512, 512, 512, False, False, 256),     # fewer tiles than CTA pairs
+    (2048, 1280, 512, True, False, 160), (1024, 896, 384, True, True, 128), (300, 200, 136, False, True, 0),
+])
+def test_gemm_pair_and_single_cta_kernels(pair, M, N, K, a_mn, b_mn, bn):
+    """The CTA-pair kernel (default) and the single-CTA kernel give the same product on every operand layout."""
+    from slowrun_b200.ops.gemm import gemm, gemm_reference, set_pair_mode
+    A = _bf(*((K, M) if a_mn else (M, K)), scale=0.1, seed=5)
+    B = _bf(*((K, N) if b_mn else (N, K)), scale=0.1, seed=6)
+    set_pair_mode(pair)
+    try:
+        out = gemm(A, B, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    finally:
+        set_pair_mode(True)
+    _status_ok()
+    _close(out, gemm_reference(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32))
+
+
 @pytest.mark.parametrize("n,g,k,bn", [(3, 768, 512, 0), (2, 640, 256, 128), (1, 2560, 1024, 0)])
 def test_gemm_symmetric(n, g, k, bn):
     from slowrun_b200.ops.gemm import gemm, gemm_reference
