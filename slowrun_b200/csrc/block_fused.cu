@@ -191,10 +191,8 @@ __global__ void iha_mix_bwd_w_kernel(const float* __restrict__ mix, const __nv_b
       a += sm[h * H + m] * x[h].x;
       b += sm[h * H + m] * x[h].y;
     }
-    float2 cur = *reinterpret_cast<float2*>(o + (long)m * J);
-    cur.x += a;
-    cur.y += b;
-    *reinterpret_cast<float2*>(o + (long)m * J) = cur;
+    // fire-and-forget vector reduction: a load-add-store here would serialise H DRAM round trips per thread
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(o + (long)m * J), "f"(a), "f"(b) : "memory");
   }
 }
 
@@ -203,7 +201,7 @@ __global__ void iha_mix_bwd_w_kernel(const float* __restrict__ mix, const __nv_b
 // one block for one slice of the staged columns, so every shared-memory word it loads feeds four multiply-adds.
 // Slices are combined with shared-memory atomics, CTAs with one global atomicAdd per entry.
 constexpr int kCols = 512;
-constexpr int kChunksPerCta = 8;
+constexpr int kChunksPerCta = 3;
 template <int H>
 __global__ void __launch_bounds__(kThreads)
 iha_mix_bwd_mix_kernel(const __nv_bfloat16* __restrict__ dWp, const __nv_bfloat16* __restrict__ W,
@@ -272,6 +270,64 @@ iha_mix_bwd_mix_kernel(const __nv_bfloat16* __restrict__ dWp, const __nv_bfloat1
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------- per-head gates
+// gate[r, h] = scale * sigmoid(bf16(sum_c a[r, c] * bf16(W[h, c]))) over the first nc channels of the normed input
+// (the reference's attn_gate / ve_gate linears under bf16 autocast, train.py:296-312). One thread per (row, head).
+__global__ void gate_fwd_kernel(const __nv_bfloat16* __restrict__ a, long lda, const float* __restrict__ W,
+                                float* __restrict__ gate, long M, int H, int nc, float scale) {
+  extern __shared__ float gsm[];   // [H * nc] weights rounded to bf16
+  for (int i = threadIdx.x; i < H * nc; i += blockDim.x) gsm[i] = __bfloat162float(__float2bfloat16(W[i]));
+  __syncthreads();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= M * H) return;
+  const long r = idx / H;
+  const int h = (int)(idx - r * H);
+  const __nv_bfloat16* ar = a + r * lda;
+  float z = 0.f;
+  for (int c = 0; c < nc; ++c) z += __bfloat162float(ar[c]) * gsm[h * nc + c];
+  z = __bfloat162float(__float2bfloat16(z));
+  gate[idx] = scale / (1.f + __expf(-z));
+}
+
+// dz = dgate * gate * (1 - gate / scale);  dW[h, c] += sum_r dz[r, h] * a[r, c];  da[r, c] += bf16(sum_h dz[r, h] * bf16(W[h, c])).
+// A CTA stages kGateRows rows; thread (h, c) owns one weight-gradient entry, then the threads sweep the (row, c) pairs.
+constexpr int kGateRows = 64;
+__global__ void gate_bwd_kernel(const float* __restrict__ dgate, const float* __restrict__ gate,
+                                const __nv_bfloat16* __restrict__ a, long lda, const float* __restrict__ W,
+                                float* __restrict__ dW, __nv_bfloat16* __restrict__ da, long ldda, long M, int H, int nc,
+                                float scale) {
+  extern __shared__ float gsm[];
+  float* sw = gsm;                       // [H * nc]
+  float* sdz = sw + H * nc;              // [kGateRows * H]
+  float* sa = sdz + kGateRows * H;       // [kGateRows * nc]
+  const long r0 = (long)blockIdx.x * kGateRows;
+  const int rows = (int)min((long)kGateRows, M - r0);
+  for (int i = threadIdx.x; i < H * nc; i += blockDim.x) sw[i] = __bfloat162float(__float2bfloat16(W[i]));
+  for (int i = threadIdx.x; i < rows * H; i += blockDim.x) {
+    const float g = gate[r0 * H + i];
+    sdz[i] = dgate[r0 * H + i] * g * (1.f - g / scale);
+  }
+  for (int i = threadIdx.x; i < rows * nc; i += blockDim.x) {
+    const int r = i / nc, c = i - r * nc;
+    sa[i] = __bfloat162float(a[(r0 + r) * lda + c]);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < H * nc; e += blockDim.x) {
+    const int h = e / nc, c = e - h * nc;
+    float acc = 0.f;
+    for (int r = 0; r < rows; ++r) acc += sdz[r * H + h] * sa[r * nc + c];
+    atomicAdd(dW + e, acc);
+  }
+  for (int i = threadIdx.x; i < rows * nc; i += blockDim.x) {
+    const int r = i / nc, c = i - r * nc;
+    float acc = 0.f;
+    for (int h = 0; h < H; ++h) acc += sdz[r * H + h] * sw[h * nc + c];
+    __nv_bfloat16* d = da + (r0 + r) * ldda + c;
+    *d = __float2bfloat16(__bfloat162float(*d) + __bfloat162float(__float2bfloat16(acc)));
+  }
+}
+
 inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
 
 template <int H>
@@ -336,4 +392,24 @@ extern "C" int sr_iha_mix_fwd(const float* mix, const void* W, void* out, int P,
 extern "C" int sr_iha_mix_bwd(const float* mix, const void* W, const void* dWp, float* gradW, float* dmix, int P, int H,
                               long J, cudaStream_t s) {
   return iha_dispatch(1, H, mix, W, dWp, nullptr, gradW, dmix, P, J, s);
+}
+
+// gate[M, H] (fp32) = scale * sigmoid(a[:, :nc] @ bf16(W)^T); a: bf16 rows with leading dimension lda; W: fp32 [H, nc]
+extern "C" int sr_gate_fwd(const void* a, long lda, const float* W, float* gate, long M, int H, int nc, float scale,
+                           cudaStream_t s) {
+  if (M <= 0) return 0;
+  const long n = M * H;
+  gate_fwd_kernel<<<(unsigned)((n + kThreads - 1) / kThreads), kThreads, H * nc * sizeof(float), s>>>(BF(a), lda, W, gate,
+                                                                                                     M, H, nc, scale);
+  return rc();
+}
+// Backward of sr_gate_fwd: dW (fp32 [H, nc]) is accumulated into, da[:, :nc] (bf16, leading dimension ldda) is added to.
+extern "C" int sr_gate_bwd(const float* dgate, const float* gate, const void* a, long lda, const float* W, float* dW,
+                           void* da, long ldda, long M, int H, int nc, float scale, cudaStream_t s) {
+  if (M <= 0) return 0;
+  const size_t smem = (size_t)(H * nc + kGateRows * H + kGateRows * nc) * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+  gate_bwd_kernel<<<(unsigned)((M + kGateRows - 1) / kGateRows), kThreads, smem, s>>>(dgate, gate, BF(a), lda, W, dW,
+                                                                                     BFM(da), ldda, M, H, nc, scale);
+  return rc();
 }

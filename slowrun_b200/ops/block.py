@@ -91,6 +91,22 @@ def iha_mix_backward(mixes, w16, dwp, grad_w, H):
     return dmix
 
 
+def _gate_fwd(a, w, H, nc, scale):
+    """[M, H] fp32 gate = scale * sigmoid(a[:, :nc] @ bf16(w)^T), the bf16-autocast linear + sigmoid of the reference."""
+    M = a.size(0)
+    gate = torch.empty((M, H), dtype=torch.float32, device=a.device)
+    _call("sr_gate_fwd", [P, L, P, P, L, I, I, F32, P], a.data_ptr(), a.stride(0), w.data_ptr(), gate.data_ptr(), M, H, nc,
+          scale, _sp())
+    return gate
+
+
+def _gate_bwd(dgate, gate, a, w_param, da, H, nc, scale):
+    """Adds the gate linear's weight gradient into w_param.grad (fp32) and its input gradient into da[:, :nc]."""
+    _call("sr_gate_bwd", [P, P, P, L, P, P, P, L, L, I, I, F32, P], dgate.data_ptr(), gate.data_ptr(), a.data_ptr(),
+          a.stride(0), w_param.data.data_ptr(), w_param.grad.data_ptr(), da.data_ptr(), da.stride(0), a.size(0), H, nc,
+          scale, _sp())
+
+
 class _BlockFn(Function):
     @staticmethod
     def forward(ctx, x_prev, x0, skip, model, block, i, j, do_mix, ve_lin, window, scale, training):
@@ -133,12 +149,8 @@ class _BlockFn(Function):
             w_qkv = fz["qkv_w16"]
         qkv = gemm(a, w_qkv)
         # ---- gates (tiny [M, H] tensors: library ops)
-        agw = attn.attn_gate.weight.data
-        agate = torch.sigmoid((a[:, :attn.attn_gate_channels] @ agw.to(torch.bfloat16).t()).float())
-        ve_gate = None
-        if ve is not None:
-            vgw = attn.ve_gate.weight.data
-            ve_gate = 2 * torch.sigmoid((a[:, :attn.ve_gate_channels] @ vgw.to(torch.bfloat16).t()).float())
+        agate = _gate_fwd(a, attn.attn_gate.weight.data, H, attn.attn_gate_channels, 1.0)
+        ve_gate = _gate_fwd(a, attn.ve_gate.weight.data, H, attn.ve_gate_channels, 2.0) if ve is not None else None
         # ---- split + value residual + RoPE + QK norm
         cos, sin = model.rotary.cos, model.rotary.sin
         cos2, sin2 = cos.view(-1, cos.size(-1)), sin.view(-1, sin.size(-1))
@@ -227,17 +239,10 @@ class _BlockFn(Function):
         else:
             gemm(dqkv, a, out=fz["qkv_grad"], cin=fz["qkv_grad"], a_mn=True, b_mn=True, beta=1.0)
         # ---- gates (tiny)
-        nc = attn.attn_gate_channels
-        dz = dagate * agate * (1 - agate)
-        a_s = a[:, :max(nc, attn.ve_gate_channels)].float()
-        attn.attn_gate.weight.grad.addmm_(dz.t(), a_s[:, :nc])
-        da[:, :nc] += (dz @ attn.attn_gate.weight.data.to(torch.bfloat16).float()).to(torch.bfloat16)
+        _gate_bwd(dagate, agate, a, attn.attn_gate.weight, da, H, attn.attn_gate_channels, 1.0)
         dx0 = None
         if ve is not None:
-            vc = attn.ve_gate_channels
-            dzv = dvegate * ve_gate * (1 - 0.5 * ve_gate)
-            attn.ve_gate.weight.grad.addmm_(dzv.t(), a_s[:, :vc])
-            da[:, :vc] += (dzv @ attn.ve_gate.weight.data.to(torch.bfloat16).float()).to(torch.bfloat16)
+            _gate_bwd(dvegate, ve_gate, a, attn.ve_gate.weight, da, H, attn.ve_gate_channels, 2.0)
             gemm(dve, x0_2, out=ve_lin.fused["grad"], cin=ve_lin.fused["grad"], a_mn=True, b_mn=True, beta=1.0)
         # ---- back through the first norm and the lambda mix
         if g_in is not None:
