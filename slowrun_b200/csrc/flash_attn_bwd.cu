@@ -130,7 +130,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
-  const uint32_t tdQ = tS;   // the S columns are reused for the dQ tile once S has been consumed
+  const uint32_t tdQ = tdP;  // the dP columns are reused for the dQ tile once dP has been consumed
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -165,13 +165,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t ph = it & 1u;
         ok = mbar_wait(qdo_full, ph, abort_flag, p.status, 2201);
         if (!ok) break;
-        if (it > 0) {   // the previous dQ tile still lives in the S columns until the compute warps have read it
-          ok = mbar_wait(dq_read, (it - 1) & 1u, abort_flag, p.status, 2202);
-          if (!ok) break;
-        }
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tS, kmaj(aQ, k), kmaj(aK, k), id_kk, k != 0 ? 1u : 0u);
+        if (it > 0) {   // the previous dQ tile still lives in the dP columns until the compute warps have read it
+          ok = mbar_wait(dq_read, (it - 1) & 1u, abort_flag, p.status, 2202);
+          if (!ok) break;
+          tc_fence_after();
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdP, kmaj(adO, k), kmaj(aV, k), id_kk, k != 0 ? 1u : 0u);
         tc_commit(sdp_full);
@@ -182,10 +183,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdV, mnmaj(aP, k), mnmaj(adO, k), id_mm, (it | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdK, mnmaj(adS, k), mnmaj(aQ, k), id_mm, (it | k) != 0 ? 1u : 0u);
+        tc_commit(qdo_empty);   // Q_i / dO_i are free once dV and dK are done: the next loads overlap the dQ product
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ss(tdQ, kmaj(adS, k), mnmaj(aK, k), id_km, k != 0 ? 1u : 0u);
         tc_commit(dq_full);
-        tc_commit(qdo_empty);
       }
     }
   } else {
@@ -210,6 +211,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      // tiles strictly inside the visible band need no per-element mask (most tiles of a long sequence)
+      const bool tile_full = (k0 + BKV - 1 <= q0) && (q0 + BQ - 1 < p.T) && (p.window < 0 || k0 >= q0 + BQ - 1 - p.window);
 #pragma unroll 1
       for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {
         uint32_t s[32], dp[32];
@@ -217,21 +220,34 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tmem_ld_32x32(tdP + lane_addr + ch * 32, dp);
         tc_wait_ld();
         uint32_t pp[16], dd[16];
+        if (tile_full) {
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kg = k0 + ch * 32 + jj + e;
-            const bool vis = row_ok && kg <= k_hi && kg >= k_lo;
-            const float pr = vis ? exp2f(__uint_as_float(s[jj + e]) * p.scale_log2 - lse2) : 0.f;
-            pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(dp[jj + e]) - dlt) * p.scale;
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float p0 = exp2f(__uint_as_float(s[jj]) * p.scale_log2 - lse2);
+            const float p1 = exp2f(__uint_as_float(s[jj + 1]) * p.scale_log2 - lse2);
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            const __nv_bfloat162 db = __floats2bfloat162_rn(p0 * (__uint_as_float(dp[jj]) - dlt) * p.scale,
+                                                            p1 * (__uint_as_float(dp[jj + 1]) - dlt) * p.scale);
+            pp[jj / 2] = *reinterpret_cast<const uint32_t*>(&pb);
+            dd[jj / 2] = *reinterpret_cast<const uint32_t*>(&db);
           }
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
-          const __nv_bfloat162 db = __floats2bfloat162_rn(dv[0], dv[1]);
-          pp[jj / 2] = *reinterpret_cast<const uint32_t*>(&pb);
-          dd[jj / 2] = *reinterpret_cast<const uint32_t*>(&db);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kg = k0 + ch * 32 + jj + e;
+              const bool vis = row_ok && kg <= k_hi && kg >= k_lo;
+              const float pr = vis ? exp2f(__uint_as_float(s[jj + e]) * p.scale_log2 - lse2) : 0.f;
+              pv[e] = pr;
+              dv[e] = pr * (__uint_as_float(dp[jj + e]) - dlt) * p.scale;
+            }
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
+            const __nv_bfloat162 db = __floats2bfloat162_rn(dv[0], dv[1]);
+            pp[jj / 2] = *reinterpret_cast<const uint32_t*>(&pb);
+            dd[jj / 2] = *reinterpret_cast<const uint32_t*>(&db);
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
