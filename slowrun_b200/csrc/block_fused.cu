@@ -81,7 +81,8 @@ __global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
                                     const __nv_bfloat16* __restrict__ sinb, const __nv_bfloat16* __restrict__ dq,
                                     const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ dv,
                                     __nv_bfloat16* __restrict__ dqkv, __nv_bfloat16* __restrict__ dve,
-                                    float* __restrict__ dgate, long tokens, int H, int T, float eps) {
+                                    float* __restrict__ dgate, long tokens, int H, int T, float eps,
+                                    const float* __restrict__ dq_f32) {
   const long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (wid >= tokens * H) return;
   const int lane = threadIdx.x & 31;
@@ -100,8 +101,16 @@ __global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
     o1.y = x1.y * c.y + x2.y * s.y;
     o2.x = -x1.x * s.x + x2.x * c.x;
     o2.y = -x1.y * s.y + x2.y * c.y;
-    const __nv_bfloat16* gp = (which == 0 ? dq : dk) + wid * 128;
-    const float2 g1 = ld2(gp + 2 * lane), g2 = ld2(gp + 64 + 2 * lane);
+    float2 g1, g2;
+    if (which == 0 && dq_f32 != nullptr) {   // dQ straight from the attention kernel's fp32 accumulator
+      const float* gp = dq_f32 + wid * 128;
+      g1 = *reinterpret_cast<const float2*>(gp + 2 * lane);
+      g2 = *reinterpret_cast<const float2*>(gp + 64 + 2 * lane);
+    } else {
+      const __nv_bfloat16* gp = (which == 0 ? dq : dk) + wid * 128;
+      g1 = ld2(gp + 2 * lane);
+      g2 = ld2(gp + 64 + 2 * lane);
+    }
     float ss = o1.x * o1.x + o1.y * o1.y + o2.x * o2.x + o2.y * o2.y;
     float dot = o1.x * g1.x + o1.y * g1.y + o2.x * g2.x + o2.y * g2.y;
     ss = warp_sum(ss);
@@ -381,7 +390,19 @@ extern "C" int sr_qkv_prep_bwd(const void* qkv, const void* ve, const float* gat
   const long n = tokens * H;
   if (n <= 0) return 0;
   qkv_prep_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
-      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BF(dq), BF(dk), BF(dv), BFM(dqkv), BFM(dve), dgate, tokens, H, T, eps);
+      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BF(dq), BF(dk), BF(dv), BFM(dqkv), BFM(dve), dgate, tokens, H, T, eps,
+      nullptr);
+  return rc();
+}
+// Same with dQ given as the fp32 accumulator of the attention backward, (tokens, H, 128) contiguous.
+extern "C" int sr_qkv_prep_bwd_f32dq(const void* qkv, const void* ve, const float* gate, const void* cosb,
+                                     const void* sinb, const float* dq_f32, const void* dk, const void* dv, void* dqkv,
+                                     void* dve, float* dgate, long tokens, int H, int T, float eps, cudaStream_t s) {
+  const long n = tokens * H;
+  if (n <= 0) return 0;
+  qkv_prep_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), nullptr, BF(dk), BF(dv), BFM(dqkv), BFM(dve), dgate, tokens, H, T, eps,
+      dq_f32);
   return rc();
 }
 // out[p] = bf16(mix[p]) @ W[p] for P stacked projections, W viewed as [P, H, J]

@@ -310,7 +310,7 @@ __global__ void head_gate_fwd_kernel(const __nv_bfloat16* __restrict__ a, const 
 __global__ void head_gate_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ other,
                                      const float* __restrict__ gate, __nv_bfloat16* __restrict__ dother,
                                      float* __restrict__ dgate, long tokens, int H, long ld_g, long ld_other,
-                                     long ld_dother) {
+                                     long ld_dother, float* __restrict__ delta, int T) {
   const long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (wid >= tokens * H) return;
   const int lane = threadIdx.x & 31;
@@ -325,7 +325,11 @@ __global__ void head_gate_bwd_kernel(const __nv_bfloat16* __restrict__ g, const 
   const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bp + 2));
   float dot = g0.x * b0.x + g0.y * b0.y + g1.x * b1.x + g1.y * b1.y;
   dot = warp_sum(dot);
-  if (lane == 0) dgate[wid] = dot;
+  if (lane == 0) {
+    dgate[wid] = dot;
+    // rowsum(d_other * other) = gate * dot: the `delta` term of the attention backward, laid out (B, H, T)
+    if (delta != nullptr) delta[((tok / T) * H + h) * T + (tok % T)] = gt * dot;
+  }
   __nv_bfloat16* op = dother + tok * ld_dother + h * 128 + lane * 4;
   *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(gt * g0.x, gt * g0.y);
   *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(gt * g1.x, gt * g1.y);
@@ -505,7 +509,16 @@ extern "C" int sr_head_gate_bwd(const void* g, const void* other, const float* g
                                 long tokens, int H, long ld_g, long ld_other, long ld_dother, cudaStream_t s) {
   const long n = tokens * H;
   if (n <= 0) return 0;
-  head_gate_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(BF(g), BF(other), gate, BFM(dother), dgate, tokens, H, ld_g, ld_other, ld_dother);
+  head_gate_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(BF(g), BF(other), gate, BFM(dother), dgate, tokens, H, ld_g, ld_other, ld_dother, nullptr, 1);
+  return rc();
+}
+// Scale-mode backward that also emits delta[b, h, t] = sum_d dother * other (tokens = B * T rows, row = b * T + t).
+extern "C" int sr_head_gate_bwd_delta(const void* g, const void* other, const float* gate, void* dother, float* dgate,
+                                      float* delta, long tokens, int H, int T, long ld_g, long ld_other, long ld_dother,
+                                      cudaStream_t s) {
+  const long n = tokens * H;
+  if (n <= 0) return 0;
+  head_gate_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(BF(g), BF(other), gate, BFM(dother), dgate, tokens, H, ld_g, ld_other, ld_dother, delta, T);
   return rc();
 }
 extern "C" int sr_swiglu_fwd(const void* gf, void* out, long M, int h, cudaStream_t s) {

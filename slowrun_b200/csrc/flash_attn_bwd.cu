@@ -7,14 +7,16 @@
 //     dQ_i = dS K_j                                                 (A K-major, B MN-major)
 // with P = exp(scale*S - lse) and dS = P * (dP - delta) * scale formed by the compute warps (thread = query row) and
 // written as bf16 into 128B-swizzled shared-memory tiles; the same dS tile is read K-major for dQ and MN-major for dK.
-// dV/dK accumulate in TMEM across the query loop; dQ tiles are added into an fp32 global accumulator with vector
-// reductions and converted to bf16 by a second kernel. delta = rowsum(dO * O) comes from a small pre-pass.
+// dV/dK accumulate in TMEM across the query loop; dQ tiles are staged as fp32 in the (then idle) P/dS buffers and added
+// into an fp32 global accumulator by bulk tensor reduce-adds (four per tile instead of 4096 vector atomics), and
+// converted to bf16 by a second kernel. delta = rowsum(dO * O) comes from a small pre-pass.
 // Warp roles (320 threads): warp 0 TMA, warp 1 MMA issuer + TMEM owner, warps 2..9 compute / epilogue; every row of a
 // tile is shared by two threads (columns 0..63 and 64..127) so each scheduler has two compute warps to interleave.
 #include "sm100_common.cuh"
 
 namespace sr_attn {
 int encode_bthd(CUtensorMap* map, const void* ptr, int B, int T, int H, long ld_t, int rows);
+int encode_bthd_f32(CUtensorMap* map, const void* ptr, int B, int T, int H, int rows);
 }
 
 namespace {
@@ -72,10 +74,38 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
   }
 }
 
+// smem tile (128B-swizzled box of the fp32 map) += into global memory, tracked by the thread's bulk async-group
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2,
+                                                  int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// barrier among the 256 compute threads only (id 1; id 0 is __syncthreads)
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// the same barrier as an AND-reduction: every compute thread learns whether all of their bounded waits succeeded, so
+// they leave the loop together and none is left behind at a later barrier
+__device__ __forceinline__ bool compute_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return r != 0;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                 const BwdParams p) {
+                 const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = smem + kTileBytes;
@@ -120,6 +150,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
     tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_dq);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -196,6 +227,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int r = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float log2e = 1.4426950408889634f;
+    const bool issuer = (threadIdx.x == 64);   // first compute thread: issues and tracks the dQ bulk reductions
+    uint8_t* stage = sP;                       // sP + sdS = 64 KB = four [128 x 32] fp32 boxes
     bool ok = true;
     for (int it = 0; it < n_q; ++it) {
       const uint32_t ph = it & 1u;
@@ -208,7 +241,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int k_hi = min(qg, p.T - 1);
       const int k_lo = (p.window < 0) ? 0 : max(0, qg - p.window);
       ok = mbar_wait(sdp_full, ph, abort_flag, p.status, 2300);
-      ok = __all_sync(0xffffffffu, ok);
+      if (it > 0 && issuer) bulk_wait_read_all();   // the previous dQ tile has left the P/dS buffers
+      ok = compute_all(ok);
       if (!ok) break;
       tc_fence_after();
       // tiles strictly inside the visible band need no per-element mask (most tiles of a long sequence)
@@ -261,27 +295,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_arrive(pds_full);
       // dQ tile -> fp32 accumulator in global memory
       ok = mbar_wait(dq_full, ph, abort_flag, p.status, 2301);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = compute_all(ok);
       if (!ok) break;
       tc_fence_after();
-      float* dst = p.dq_acc + (((size_t)b * p.T + (row_ok ? qg : 0)) * p.H + h) * D;
 #pragma unroll 1
       for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {
         uint32_t v[32];
         tmem_ld_32x32(tdQ + lane_addr + ch * 32, v);
         tc_wait_ld();
-        if (row_ok) {
+        uint8_t* rowp = stage + ch * 16384 + r * 128;
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + ch * 32 + jj),
-                         "f"(__uint_as_float(v[jj])), "f"(__uint_as_float(v[jj + 1])), "f"(__uint_as_float(v[jj + 2])),
-                         "f"(__uint_as_float(v[jj + 3]))
-                         : "memory");
-        }
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
       }
       tc_fence_before();
       mbar_arrive(dq_read);
+      fence_proxy_async_smem();
+      compute_sync();
+      if (issuer) {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) tma_reduce_add_4d(&map_dq, stage + ch * 16384, ch * 32, h, q0, b);
+        bulk_commit_group();
+      }
     }
+    if (issuer) bulk_wait_all();
     // ---- dK / dV epilogue: the last dq_full commit covers every product issued before it
     if (ok && n_q > 0) {
       tc_fence_after();
@@ -325,9 +362,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
 // All tensors contiguous (B, T, H, 128) bf16 except lse/delta fp32 (B, H, T) and dq_acc fp32 (B, T, H, 128), which must
 // be zero on entry. window < 0 = full causal.
-extern "C" int sr_flash_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
-                                 const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int T,
-                                 int H, int window, float scale, int* status, cudaStream_t stream) {
+// flags: bit 0 = `delta` already holds rowsum(dO * O) (skip the pre-pass); bit 1 = leave dQ in `dq_acc` (fp32), do not
+// write `dq`.
+extern "C" int sr_flash_attn_bwd_ex(const void* dO, const void* q, const void* k, const void* v, const void* out,
+                                    const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B,
+                                    int T, int H, int window, float scale, int flags, int* status, cudaStream_t stream) {
   if (B <= 0 || T <= 0 || H <= 0) return 0;
   static bool configured = false;
   if (!configured) {
@@ -342,9 +381,12 @@ extern "C" int sr_flash_attn_bwd(const void* dO, const void* q, const void* k, c
   if ((rc = sr_attn::encode_bthd(&mk, k, B, T, H, ld, 128))) return rc - 10;
   if ((rc = sr_attn::encode_bthd(&mv, v, B, T, H, ld, 128))) return rc - 20;
   if ((rc = sr_attn::encode_bthd(&mdo, dO, B, T, H, ld, 128))) return rc - 30;
+  CUtensorMap mdq;
+  if ((rc = sr_attn::encode_bthd_f32(&mdq, dq_acc, B, T, H, 128))) return rc - 40;
   const long rows = (long)B * T * H;
-  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dO),
-                                                                     reinterpret_cast<const __nv_bfloat16*>(out), delta, B, T, H);
+  if (!(flags & 1))
+    attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dO),
+                                                                       reinterpret_cast<const __nv_bfloat16*>(out), delta, B, T, H);
   BwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
@@ -355,10 +397,18 @@ extern "C" int sr_flash_attn_bwd(const void* dO, const void* q, const void* k, c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   dim3 grid((T + BKV - 1) / BKV, B * H);
-  flash_bwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
-  const long n4 = rows * D / 4;
-  long blocks = (n4 + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  attn_dq_convert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n4);
+  flash_bwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, mdo, mdq, p);
+  if (!(flags & 2)) {
+    const long n4 = rows * D / 4;
+    long blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    attn_dq_convert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n4);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int sr_flash_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
+                                 const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int T,
+                                 int H, int window, float scale, int* status, cudaStream_t stream) {
+  return sr_flash_attn_bwd_ex(dO, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, B, T, H, window, scale, 0, status, stream);
 }

@@ -350,6 +350,22 @@ int encode_bthd(CUtensorMap* map, const void* ptr, int B, int T, int H, long ld_
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// Contiguous (B, T, H, 128) fp32 tensor; box = 32 columns (128 B) x `rows` tokens of one head, 128B swizzle. Used for the
+// bulk reduce-add of dQ tiles from shared memory.
+int encode_bthd_f32(CUtensorMap* map, const void* ptr, int B, int T, int H, int rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return -2;
+  cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[3] = {128 * 4, (cuuint64_t)H * 128 * 4, (cuuint64_t)H * 128 * 4 * (cuuint64_t)T};
+  cuuint32_t box[4] = {32, 1, (cuuint32_t)rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 }  // namespace sr_attn
 
 // q, k, v: (B, T, H, 128) bf16 with token stride ld_* elements (contiguous tensors: H*128); out contiguous;

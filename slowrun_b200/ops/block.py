@@ -217,17 +217,25 @@ class _BlockFn(Function):
         gemm(do, y2.view(M, C), out=fz["proj_grad"], cin=fz["proj_grad"], a_mn=True, b_mn=True, beta=1.0)
         dy = torch.empty_like(y)
         dagate = torch.empty((M, H), dtype=torch.float32, device=g.device)
-        _call("sr_head_gate_bwd", [P] * 5 + [L, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), agate.data_ptr(), dy.data_ptr(),
-              dagate.data_ptr(), M, H, H * D, H * D, H * D, _sp())
-        dq, dk, dv = impl.bwd(attn_saved, dy)
+        fused_attn_bwd = getattr(impl, "has_bwd", False) and hasattr(impl, "bwd_fused")
+        if fused_attn_bwd:
+            # the gate backward already forms rowsum(dy * y); the attention backward leaves dQ in fp32 for qkv_prep_bwd
+            delta = torch.empty((B, H, T), dtype=torch.float32, device=g.device)
+            _call("sr_head_gate_bwd_delta", [P] * 6 + [L, I, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), agate.data_ptr(),
+                  dy.data_ptr(), dagate.data_ptr(), delta.data_ptr(), M, H, T, H * D, H * D, H * D, _sp())
+            dq, dk, dv = impl.bwd_fused(attn_saved, dy, delta)
+        else:
+            _call("sr_head_gate_bwd", [P] * 5 + [L, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), agate.data_ptr(), dy.data_ptr(),
+                  dagate.data_ptr(), M, H, H * D, H * D, H * D, _sp())
+            dq, dk, dv = impl.bwd(attn_saved, dy)
         dqkv = torch.empty_like(qkv)
         dve = torch.empty((M, C), dtype=torch.bfloat16, device=g.device) if ve is not None else None
         dvegate = torch.empty((M, H), dtype=torch.float32, device=g.device) if ve is not None else None
         cos, sin = model.rotary.cos, model.rotary.sin
         cos2, sin2 = cos.view(-1, cos.size(-1)), sin.view(-1, sin.size(-1))
-        _call("sr_qkv_prep_bwd", [P] * 11 + [L, I, I, F32, P], qkv.data_ptr(), _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(),
-              sin2.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dqkv.data_ptr(), _lib.ptr(dve), _lib.ptr(dvegate),
-              M, H, T, eps, _sp())
+        _call("sr_qkv_prep_bwd_f32dq" if fused_attn_bwd else "sr_qkv_prep_bwd", [P] * 11 + [L, I, I, F32, P], qkv.data_ptr(),
+              _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(), sin2.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+              dqkv.data_ptr(), _lib.ptr(dve), _lib.ptr(dvegate), M, H, T, eps, _sp())
         da = gemm(dqkv, w_qkv, b_mn=True)
         if mixes is not None:
             dwp = gemm(dqkv, a, a_mn=True, b_mn=True)

@@ -48,18 +48,23 @@ def native_fwd(q, k, v, window, scale, bkv=None):
     return out, lse, sc, w
 
 
-def native_bwd(dout, q, k, v, out, lse, sc, w):
+def native_bwd(dout, q, k, v, out, lse, sc, w, delta=None, dq_fp32=False):
+    """dq, dk, dv. `delta` (B, H, T) fp32 = rowsum(dout * out) may be supplied by the caller (the head-gate backward
+    produces it for free); `dq_fp32` returns dQ as the kernel's fp32 accumulator instead of a bf16 copy."""
     B, T, H, D = q.shape
-    dq = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=q.device)
-    dk, dv = torch.empty_like(dq), torch.empty_like(dq)
+    dk = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty_like(dk)
+    dq = None if dq_fp32 else torch.empty_like(dk)
     dq_acc = torch.zeros((B, T, H, D), dtype=torch.float32, device=q.device)
-    delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
-    rc = _lib.fn("sr_flash_attn_bwd", [P] * 11 + [I, I, I, I, F32, P, P])(
+    flags = (1 if delta is not None else 0) | (2 if dq_fp32 else 0)
+    if delta is None:
+        delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    rc = _lib.fn("sr_flash_attn_bwd_ex", [P] * 11 + [I, I, I, I, F32, I, P, P])(
         dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-        dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, T, H, w, sc,
+        dq_acc.data_ptr(), _lib.ptr(dq), dk.data_ptr(), dv.data_ptr(), B, T, H, w, sc, flags,
         _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
-    _lib.check_rc(rc, "sr_flash_attn_bwd")
-    return dq, dk, dv
+    _lib.check_rc(rc, "sr_flash_attn_bwd_ex")
+    return (dq_acc if dq_fp32 else dq), dk, dv
 
 
 class NativeAttention:
@@ -85,6 +90,11 @@ class NativeAttention:
         q, k, v = (t if (t.stride(3) == 1 and t.stride(2) == 128) else t.contiguous() for t in (q, k, v))
         out, lse, sc, w = native_fwd(q, k, v, window, scale)
         return out, (q, k, v, out, lse, sc, w)
+
+    def bwd_fused(self, saved, dy, delta):
+        """Backward for callers that already hold delta = rowsum(dy * out) and consume dQ in fp32 (the fused block)."""
+        q, k, v, out, lse, sc, w = saved
+        return native_bwd(dy, q.contiguous(), k.contiguous(), v.contiguous(), out, lse, sc, w, delta=delta, dq_fp32=True)
 
     def bwd(self, saved, dy):
         q, k, v, out, lse, sc, w = saved
