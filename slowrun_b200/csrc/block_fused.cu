@@ -349,9 +349,11 @@ int iha_launch(int which, const float* mix, const void* W, const void* dWp, void
     iha_mix_fwd_kernel<H><<<grid, kThreads, 0, s>>>(mix, w, reinterpret_cast<__nv_bfloat16*>(out), J);
   } else {
     iha_mix_bwd_w_kernel<H><<<grid, kThreads, 0, s>>>(mix, g, gradW, J);
-    const long chunks = (J + kCols - 1) / kCols;
-    const dim3 grid2((unsigned)((chunks + kChunksPerCta - 1) / kChunksPerCta), P);
-    iha_mix_bwd_mix_kernel<H><<<grid2, kThreads, 0, s>>>(g, w, dmix, J);
+    if (dmix != nullptr) {   // callers with a split-K GEMM at hand form dmix = dW' W^T there and pass null
+      const long chunks = (J + kCols - 1) / kCols;
+      const dim3 grid2((unsigned)((chunks + kChunksPerCta - 1) / kChunksPerCta), P);
+      iha_mix_bwd_mix_kernel<H><<<grid2, kThreads, 0, s>>>(g, w, dmix, J);
+    }
   }
   return rc();
 }

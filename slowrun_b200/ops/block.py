@@ -78,8 +78,14 @@ def iha_mix_backward(mixes, w16, dwp, grad_w, H):
     Pn = mixes.size(0)
     J = w16.numel() // (Pn * H)
     dmix = torch.zeros_like(mixes)
+    # dmix[p] = dW'[p] W[p]^T: a [H x J] x [J x H] product with a very long K, done by the split-K tcgen05 GEMM
+    # (every CTA takes a share of K and adds its partial H x H tile)
+    use_gemm = J % 8 == 0
     rc = _lib.fn("sr_iha_mix_bwd", [P, P, P, P, P, I, I, L, P])(mixes.data_ptr(), w16.data_ptr(), dwp.data_ptr(),
-                                                               grad_w.data_ptr(), dmix.data_ptr(), Pn, H, J, _sp())
+                                                               grad_w.data_ptr(), 0 if use_gemm else dmix.data_ptr(),
+                                                               Pn, H, J, _sp())
+    if rc == 0 and use_gemm:
+        gemm(dwp.view(Pn, H, J), w16.view(Pn, H, J), out=dmix, cin=dmix, beta=1.0, bn=128)
     if rc == -7:
         d3 = dwp.view(Pn, H, J)
         m16 = mixes.to(torch.bfloat16)
