@@ -547,8 +547,12 @@ def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_siz
         torch.manual_seed(seed)
         if device.type == "cuda":
             torch.cuda.manual_seed(seed)
-    with torch.device(device):
+    # Built on the meta device and materialised empty, as the reference scripts do (train.py:1044-1047): the module
+    # constructors then draw nothing from the generator, so init_weights() starts from the freshly seeded state and
+    # the same seed gives the reference's parameters on the GPU as well.
+    with torch.device("meta"):
         model = GPT(config)
+    model.to_empty(device=device)
     model.init_weights()
     if device.type == "cuda":
         model.norm_eps = ops.BF16_EPS

@@ -14,7 +14,9 @@ def _pair(n_layer=4, dupe=False, mtp=0.3, iha=True):
     rcfg = ref.GPTConfig(sequence_len=64, vocab_size=50257, n_layer=n_layer, n_head=4, n_kv_head=4, n_embd=128,
                          dropout=0.0, stoch_depth=0.0, use_iha=iha, iha_mix_v=iha)
     torch.manual_seed(42)
-    rmodel = ref.GPT(rcfg)
+    with torch.device("meta"):        # the script's own construction sequence (train.py:1044-1047)
+        rmodel = ref.GPT(rcfg)
+    rmodel.to_empty(device="cpu")
     rmodel.init_weights()
     mc = ModelConfig(sequence_len=64, n_layer=n_layer, n_head=4, n_kv_head=4, n_embd=128, dropout=0.0, stoch_depth=0.0,
                      use_iha=iha, iha_mix_v=iha, mtp_weight=mtp, logit_cap=10.0)
