@@ -78,6 +78,12 @@ def main():
 
     res = {k: timed(o) for k, o in opts.items()}
     _lib.check_status()
+    phases = None
+    if "fused" in opts:
+        opts["fused"].trace_phases = True
+        opts["fused"].step()
+        phases = {k: round(v, 3) for k, v in opts["fused"].phase_report().items()}
+        opts["fused"].trace_phases = False
     # traffic and FLOPs per rank
     g_bytes = sum(ga.G.numel() * 4 for ga in model.arena.groups.values())            # fp32 stacked gradients
     u_bytes = g_bytes // 2                                                            # bf16 updates
@@ -100,7 +106,7 @@ def main():
         out = {"what": "optimizer_step", "size": a.size, "n_gpus": W, "ms": res,
                "nvlink_bytes_in_per_rank": {"grad_pull": rs_in, "update_pull": ag_in},
                "ns_tflop_per_rank": ns_flops / 1e12, "roofline_ms": {"compute": t_compute, "link": t_link, "peaks": src},
-               "frac_of_roofline": {k: roof / v for k, v in res.items()}}
+               "frac_of_roofline": {k: roof / v for k, v in res.items()}, "fused_phases_ms_rank0": phases}
         print(json.dumps(out))
     if W > 1:
         dist.barrier()

@@ -56,62 +56,70 @@ __global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_
 }
 
 // One warp per row of the owned stack. G_r points at rank r's full gradient arena of this group; `base` is the element
-// offset of the owned chunk inside it.
-__global__ void muon_pre_multi_kernel(PtrTable G, int world, long base, float* __restrict__ Mom,
-                                      __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r,
-                                      int c, float mu, float gscale) {
+// offset of the owned chunk inside it. Pass 1 pulls the row from every rank (two column steps of W independent 16-byte
+// loads per lane are issued before any is consumed, so a warp keeps W KB in flight over NVLink), reduces it, updates the
+// momentum and parks the Nesterov gradient in this rank's own copy of the row (dead once reduced; the other ranks only
+// read the rows of their own chunks). Pass 2 rereads it from L2, applies the row norm and writes the bf16 input of the
+// Newton-Schulz iteration.
+constexpr int kPullWorld = 8;   // peers handled by the unrolled load stage; larger worlds take extra rounds
+__global__ void __launch_bounds__(kThreads, 2)
+muon_pre_multi_kernel(PtrTable G, int world, int rank, long base, float* __restrict__ Mom,
+                      __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
+                      float gscale) {
   const long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5);
   if (row >= rows_total) return;
   const int lane = threadIdx.x & 31;
   float* m = Mom + row * c;
   __nv_bfloat16* x = X + row * c;
   const long off = base + row * c;
+  float* park = reinterpret_cast<float*>(const_cast<void*>(G.p[rank])) + off;
   float ss = 0.f;
-  // pass 1 reduces the row over all ranks and updates the momentum. The Nesterov gradient is needed again after the
-  // row norm is known; it is kept per lane (64 floats cover rows up to 8192 columns) so the peers are read only once.
-  constexpr int kCache = 64;
-  float cache[kCache];
-  const bool fits = c <= kCache * 32;
-  int ci = 0;
-  for (int j = lane * 4; j < c; j += 128, ci += 4) {
-    float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < world; ++p) {
-      const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(G.p[p]) + off + j);
-      gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
+  for (int j0 = lane * 4; j0 < c; j0 += 256) {
+    const int j1 = j0 + 128;
+    const bool has1 = j1 < c;
+    float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+    for (int p0 = 0; p0 < world; p0 += kPullWorld) {
+      float4 t0[kPullWorld], t1[kPullWorld];
+#pragma unroll
+      for (int p = 0; p < kPullWorld; ++p) {
+        if (p0 + p < world) {
+          const float* src = reinterpret_cast<const float*>(G.p[p0 + p]) + off;
+          t0[p] = *reinterpret_cast<const float4*>(src + j0);
+          if (has1) t1[p] = *reinterpret_cast<const float4*>(src + j1);
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < kPullWorld; ++p) {
+        if (p0 + p < world) {
+          g0.x += t0[p].x; g0.y += t0[p].y; g0.z += t0[p].z; g0.w += t0[p].w;
+          if (has1) { g1.x += t1[p].x; g1.y += t1[p].y; g1.z += t1[p].z; g1.w += t1[p].w; }
+        }
+      }
     }
-    gv.x *= gscale; gv.y *= gscale; gv.z *= gscale; gv.w *= gscale;
-    float4 mv = *reinterpret_cast<const float4*>(m + j);
-    mv.x += (1.f - mu) * (gv.x - mv.x); mv.y += (1.f - mu) * (gv.y - mv.y);
-    mv.z += (1.f - mu) * (gv.z - mv.z); mv.w += (1.f - mu) * (gv.w - mv.w);
-    *reinterpret_cast<float4*>(m + j) = mv;
-    const float a = gv.x + mu * (mv.x - gv.x), b = gv.y + mu * (mv.y - gv.y);
-    const float cc = gv.z + mu * (mv.z - gv.z), d = gv.w + mu * (mv.w - gv.w);
-    ss += a * a + b * b + cc * cc + d * d;
-    if (fits) {
-      cache[ci] = a; cache[ci + 1] = b; cache[ci + 2] = cc; cache[ci + 3] = d;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !has1) break;
+      const int j = u == 0 ? j0 : j1;
+      float4 gv = u == 0 ? g0 : g1;
+      gv.x *= gscale; gv.y *= gscale; gv.z *= gscale; gv.w *= gscale;
+      float4 mv = *reinterpret_cast<const float4*>(m + j);
+      mv.x += (1.f - mu) * (gv.x - mv.x); mv.y += (1.f - mu) * (gv.y - mv.y);
+      mv.z += (1.f - mu) * (gv.z - mv.z); mv.w += (1.f - mu) * (gv.w - mv.w);
+      *reinterpret_cast<float4*>(m + j) = mv;
+      float4 nv;
+      nv.x = gv.x + mu * (mv.x - gv.x); nv.y = gv.y + mu * (mv.y - gv.y);
+      nv.z = gv.z + mu * (mv.z - gv.z); nv.w = gv.w + mu * (mv.w - gv.w);
+      ss += nv.x * nv.x + nv.y * nv.y + nv.z * nv.z + nv.w * nv.w;
+      *reinterpret_cast<float4*>(park + j) = nv;
     }
   }
   ss = warp_sum(ss);
   const float inv = 1.f / fmaxf(sqrtf(ss), 1e-7f);
   float xs = 0.f;
-  ci = 0;
-  for (int j = lane * 4; j < c; j += 128, ci += 4) {
-    float a, b, cc, d;
-    if (fits) {
-      a = cache[ci]; b = cache[ci + 1]; cc = cache[ci + 2]; d = cache[ci + 3];
-    } else {
-      float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int p = 0; p < world; ++p) {
-        const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(G.p[p]) + off + j);
-        gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
-      }
-      gv.x *= gscale; gv.y *= gscale; gv.z *= gscale; gv.w *= gscale;
-      const float4 mv = *reinterpret_cast<const float4*>(m + j);
-      a = gv.x + mu * (mv.x - gv.x); b = gv.y + mu * (mv.y - gv.y);
-      cc = gv.z + mu * (mv.z - gv.z); d = gv.w + mu * (mv.w - gv.w);
-    }
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(a * inv, b * inv);
-    const __nv_bfloat162 hi = __floats2bfloat162_rn(cc * inv, d * inv);
+  for (int j = lane * 4; j < c; j += 128) {
+    const float4 nv = *reinterpret_cast<const float4*>(park + j);   // written by this same lane above
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(nv.x * inv, nv.y * inv);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(nv.z * inv, nv.w * inv);
     *reinterpret_cast<__nv_bfloat162*>(x + j) = lo;
     *reinterpret_cast<__nv_bfloat162*>(x + j + 2) = hi;
     const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
@@ -215,16 +223,17 @@ extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, in
   return rc();
 }
 
-extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, int world, long base, float* Mom, void* X,
+// `rank`: index of the calling rank in g_ptrs; its own copy of the owned rows is overwritten (used as scratch).
+extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, int world, int rank, long base, float* Mom, void* X,
                                  float* sumsq, int n, int r, int c, float mu, float gscale, cudaStream_t s) {
   if (n <= 0) return 0;
-  if (c % 4) return -2;
+  if (c % 4 || rank < 0 || rank >= world) return -2;
   PtrTable t;
   if (!fill(t, g_ptrs, world)) return -2;
   const long rows = (long)n * r;
   cudaMemsetAsync(sumsq, 0, sizeof(float) * n, s);
   muon_pre_multi_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(
-      t, world, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
+      t, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
   const long total = rows * c;
   fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total);
   return rc();

@@ -227,6 +227,23 @@ class ShardedMuonAdamW:
         for item in pending:
             item()
 
+    # ------------------------------------------------------------------ phase tracing (off unless `trace_phases` is set)
+    def _mark(self, name):
+        """With `self.trace_phases = True` every call records a CUDA event; `phase_report()` turns the list of one step
+        into (phase, ms) pairs. Costs nothing when off."""
+        if getattr(self, "trace_phases", False):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def phase_report(self):
+        torch.cuda.synchronize()
+        marks = getattr(self, "_marks", [])
+        out = {}
+        for (n0, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
+            out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
+        return out
+
     # ------------------------------------------------------------------ fused peer-memory step
     @torch.no_grad()
     def _step_fused(self):
@@ -239,7 +256,10 @@ class ShardedMuonAdamW:
         gscale = 1.0 / W
         head = self.model.lm_head.weight
         cvp = ctypes.c_void_p
+        self._marks = []
+        self._mark("start")
         comm.device_barrier()                                                                      # A
+        self._mark("barrier_a")
         small_sum = None
         if arena.small_grads.numel() > 0:
             if "small_sum" not in self.state:
@@ -259,15 +279,18 @@ class ShardedMuonAdamW:
                     if "X" in st:
                         X = st["X"][:n_own]
                         sc = st["scratch"]
-                        rc = _lib.fn("sr_muon_pre_multi", [cvp, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
-                            ctypes.cast(comm.peer_ptrs(ga.G), cvp), W, base, st["momentum"].data_ptr(), X.data_ptr(),
+                        rc = _lib.fn("sr_muon_pre_multi", [cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
+                            ctypes.cast(comm.peer_ptrs(ga.G), cvp), W, rank, base, st["momentum"].data_ptr(), X.data_ptr(),
                             st["sumsq"].data_ptr(), n_own, r, c, mu, gscale, _lib.stream_ptr())
                         _lib.check_rc(rc, "sr_muon_pre_multi")
+                        self._mark("muon_pull_pre")
                         Xo = newton_schulz_cuda(X, ns, st["ws"])
+                        self._mark("newton_schulz")
                         rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
                             Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), st["U"].data_ptr(),
                             n_own, r, c, _bf16(beta2), _lib.stream_ptr())
                         _lib.check_rc(rc, "sr_muon_post")
+                        self._mark("muon_post")
                     else:
                         tmp = torch.empty((n_own, r, c), dtype=torch.float32, device=self.device)
                         comm.reduce_from_peers(ga.G, base, tmp)
@@ -297,7 +320,9 @@ class ShardedMuonAdamW:
                         comm.reduce_from_peers(grad, 0, st["gfull32"])
                         shadow = arena.head_w16 if (p is head and arena.head_w16 is not None) else None
                         self._adamw_launch(p.data, st["gfull32"], st["m"], st["v"], shadow, g, gscale)
+        self._mark("adamw_pull")
         comm.device_barrier()                                                                      # B
+        self._mark("barrier_b")
         for g, st, ga in applies:
             r, c = ga.shape
             lr_eff = float(g["lr"]) * max(1.0, r / c) ** 0.5
@@ -311,10 +336,12 @@ class ShardedMuonAdamW:
             else:
                 comm.all_gather(st["U_all"], st["U"], async_op=False)
                 muon_apply_ref(ga.P, st["U_all"][:ga.n], lr_eff, wd)
+        self._mark("muon_apply_pull")
         for p in gathers:
             comm.gather_slices(p.data)
             if p is head and arena.head_w16 is not None:
                 arena.head_w16.copy_(p.data)
+        self._mark("adamw_gather")
 
     def _adamw_small(self, grp, smalls, grads_flat, gscale):
         """One launch per run of parameters that are adjacent in the flat small-parameter buffer."""

@@ -76,4 +76,4 @@ def test_fused_peer_memory_step_matches_nccl_path(tmp_path):
     num = sum((a0["params"][n] - f0["params"][n]).pow(2).sum() for n in a0["params"])
     den = sum(a0["params"][n].pow(2).sum() for n in a0["params"])
     assert (num / den).sqrt().item() < 2e-2, (num / den).sqrt().item()
-    assert f0["losses"][-1] < f0["losses"][0]
+    assert abs(a0["losses"][-1] - f0["losses"][-1]) < 5e-2      # both paths follow the same trajectory
