@@ -66,9 +66,10 @@ __global__ void __launch_bounds__(kThreads, 2)
 muon_pre_multi_kernel(PtrTable G, int world, int rank, long base, float* __restrict__ Mom,
                       __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
                       float gscale) {
-  const long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5);
-  if (row >= rows_total) return;
   const int lane = threadIdx.x & 31;
+  // at most one CTA per SM (the launcher caps the grid): the kernel is meant to share the SMs with the Newton-Schulz
+  // GEMMs of the neighbouring shape group, which need one CTA's worth of registers and shared memory on every SM
+  for (long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5); row < rows_total; row += (long)gridDim.x * kWarps) {
   float* m = Mom + row * c;
   __nv_bfloat16* x = X + row * c;
   const long off = base + row * c;
@@ -127,6 +128,7 @@ muon_pre_multi_kernel(PtrTable G, int world, int rank, long base, float* __restr
   }
   xs = warp_sum(xs);
   if (lane == 0) atomicAdd(sumsq + row / r, xs);
+  }
 }
 
 __global__ void fnorm_scale_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__ sumsq, long per_mat,
@@ -232,7 +234,9 @@ extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, int world, in
   if (!fill(t, g_ptrs, world)) return -2;
   const long rows = (long)n * r;
   cudaMemsetAsync(sumsq, 0, sizeof(float) * n, s);
-  muon_pre_multi_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(
+  long pull_grid = (rows + kWarps - 1) / kWarps;
+  if (pull_grid > 148) pull_grid = 148;
+  muon_pre_multi_kernel<<<(unsigned)pull_grid, kThreads, 0, s>>>(
       t, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
   const long total = rows * c;
   fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total);

@@ -248,8 +248,17 @@ class ShardedMuonAdamW:
     @torch.no_grad()
     def _step_fused(self):
         """Same update as `step()`, with every collective replaced by a kernel that reads the peers' symmetric buffers
-        and consumes the data in the same pass (csrc/comm_fused.cu). Two device-side barriers bracket the work:
-        A = every rank's gradients are final; B = every owner's update chunk / parameter slice is final."""
+        and consumes the data in the same pass (csrc/comm_fused.cu), pipelined over two streams:
+
+          side stream   barrier A (every rank's gradients are final) -> gradient pull + Muon prologue of every shape
+                        group, then the AdamW row-slice pulls and updates -> per group, once its updates are final on
+                        this rank: barrier B_g and the update pull fused with the cautious-weight-decay apply ->
+                        last barrier, slice gathers of the sharded AdamW parameters
+          main stream   small replicated parameters; per group, as soon as its pull has landed: Newton-Schulz and
+                        the variance-reduction epilogue
+
+        so NVLink traffic (pulls, applies) overlaps the Newton-Schulz GEMMs of the neighbouring groups. All
+        device-side barriers are issued on the side stream, in the same order on every rank."""
         import ctypes
         self.step_count += 1
         W, rank, comm, arena = self.world, self.rank, self.comm, self.arena
@@ -258,49 +267,35 @@ class ShardedMuonAdamW:
         cvp = ctypes.c_void_p
         self._marks = []
         self._mark("start")
-        comm.device_barrier()                                                                      # A
-        self._mark("barrier_a")
-        small_sum = None
-        if arena.small_grads.numel() > 0:
-            if "small_sum" not in self.state:
-                self.state["small_sum"] = torch.empty(arena.small_grads.numel(), dtype=torch.float32, device=self.device)
-            small_sum = self.state["small_sum"]
-            comm.reduce_from_peers(arena.small_grads, 0, small_sum)
-        gathers, applies = [], []
-        for g in self.param_groups:
-            if g["kind"] == "muon":
-                st = self.state[g["name"]]
-                ga = st["arena"]
-                r, c = ga.shape
-                n_own = self.num_owned(ga)
-                mu, beta2, ns = float(g["momentum"]), float(g["beta2"]), int(g["ns_steps"])
-                base = rank * ga.chunk * r * c
-                if n_own > 0:
-                    if "X" in st:
-                        X = st["X"][:n_own]
-                        sc = st["scratch"]
-                        rc = _lib.fn("sr_muon_pre_multi", [cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
-                            ctypes.cast(comm.peer_ptrs(ga.G), cvp), W, rank, base, st["momentum"].data_ptr(), X.data_ptr(),
-                            st["sumsq"].data_ptr(), n_own, r, c, mu, gscale, _lib.stream_ptr())
-                        _lib.check_rc(rc, "sr_muon_pre_multi")
-                        self._mark("muon_pull_pre")
-                        Xo = newton_schulz_cuda(X, ns, st["ws"])
-                        self._mark("newton_schulz")
-                        rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
-                            Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), st["U"].data_ptr(),
-                            n_own, r, c, _bf16(beta2), _lib.stream_ptr())
-                        _lib.check_rc(rc, "sr_muon_post")
-                        self._mark("muon_post")
-                    else:
-                        tmp = torch.empty((n_own, r, c), dtype=torch.float32, device=self.device)
-                        comm.reduce_from_peers(ga.G, base, tmp)
-                        tmp.mul_(gscale)
-                        st["U"][:n_own].copy_(muon_update_ref(tmp, st["momentum"][:n_own], st["second"][:n_own], mu, beta2, ns))
-                applies.append((g, st, ga))
-            else:
-                smalls = [p for p in g["params"] if self.state[id(p)]["small"]]
-                if smalls:
-                    self._adamw_small(g, smalls, small_sum, gscale)
+        main = torch.cuda.current_stream(self.device)
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        side = self._side
+        muon = [(g, self.state[g["name"]]) for g in self.param_groups if g["kind"] == "muon"]
+        fast = [(g, st) for g, st in muon if "X" in st and st["arena"].W16 is not None]
+        slow = [(g, st) for g, st in muon if not ("X" in st and st["arena"].W16 is not None)]
+        gathers = []
+
+        def pull(i):
+            """Side stream: gradient pull + Muon prologue of fast group i; returns the event that marks its end."""
+            g, st = fast[i]
+            ga = st["arena"]
+            r, c = ga.shape
+            n_own = self.num_owned(ga)
+            if n_own > 0:
+                rc = _lib.fn("sr_muon_pre_multi", [cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
+                    ctypes.cast(comm.peer_ptrs(ga.G), cvp), W, rank, rank * ga.chunk * r * c, st["momentum"].data_ptr(),
+                    st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale, _lib.stream_ptr())
+                _lib.check_rc(rc, "sr_muon_pre_multi")
+            ev = torch.cuda.Event()
+            ev.record(side)
+            return ev
+
+        def adamw_big():
+            """Side stream: row-slice pulls and updates of the large AdamW parameters (lm_head, wte, ...)."""
+            for g in self.param_groups:
+                if g["kind"] == "muon":
+                    continue
                 for p in g["params"]:
                     st = self.state[id(p)]
                     if st["small"]:
@@ -320,28 +315,77 @@ class ShardedMuonAdamW:
                         comm.reduce_from_peers(grad, 0, st["gfull32"])
                         shadow = arena.head_w16 if (p is head and arena.head_w16 is not None) else None
                         self._adamw_launch(p.data, st["gfull32"], st["m"], st["v"], shadow, g, gscale)
-        self._mark("adamw_pull")
-        comm.device_barrier()                                                                      # B
-        self._mark("barrier_b")
-        for g, st, ga in applies:
+
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            comm.device_barrier()                                                                  # A
+            ev_a = torch.cuda.Event()
+            ev_a.record(side)
+            pull_done = [pull(i) for i in range(len(fast))]      # all pulls first: they gate the compute
+            adamw_big()
+        # ---- main stream: small replicated parameters (one packed all-reduce read), then the per-group compute
+        main.wait_event(ev_a)
+        self._mark("barrier_a")
+        if arena.small_grads.numel() > 0:
+            if "small_sum" not in self.state:
+                self.state["small_sum"] = torch.empty(arena.small_grads.numel(), dtype=torch.float32, device=self.device)
+            small_sum = self.state["small_sum"]
+            comm.reduce_from_peers(arena.small_grads, 0, small_sum)
+            for g in self.param_groups:
+                if g["kind"] != "muon":
+                    smalls = [p for p in g["params"] if self.state[id(p)]["small"]]
+                    if smalls:
+                        self._adamw_small(g, smalls, small_sum, gscale)
+        for i, (g, st) in enumerate(fast):
+            ga = st["arena"]
             r, c = ga.shape
-            lr_eff = float(g["lr"]) * max(1.0, r / c) ** 0.5
-            wd = float(g["weight_decay"])
-            if ga.W16 is not None:
-                lr_b = _bf16(lr_eff)
+            n_own = self.num_owned(ga)
+            main.wait_event(pull_done[i])
+            self._mark("wait_pull")
+            if n_own > 0:
+                sc = st["scratch"]
+                Xo = newton_schulz_cuda(st["X"][:n_own], int(g["ns_steps"]), st["ws"])
+                self._mark("newton_schulz")
+                rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
+                    Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), st["U"].data_ptr(),
+                    n_own, r, c, _bf16(float(g["beta2"])), _lib.stream_ptr())
+                _lib.check_rc(rc, "sr_muon_post")
+                self._mark("muon_post")
+            ev_post = torch.cuda.Event()
+            ev_post.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(ev_post)
+                comm.device_barrier()                                                              # B_g
+                lr_b = _bf16(float(g["lr"]) * max(1.0, r / c) ** 0.5)
                 rc = _lib.fn("sr_muon_apply_multi", [cvp, cvp, c_int, c_long, cvp, c_long, c_float, c_float, cvp])(
                     ga.P.data_ptr(), ctypes.cast(comm.peer_ptrs(st["U"]), cvp), W, ga.chunk * r * c, ga.W16.data_ptr(),
-                    ga.P.numel(), lr_b, _bf16(lr_b * _bf16(wd)), _lib.stream_ptr())
+                    ga.P.numel(), lr_b, _bf16(lr_b * _bf16(float(g["weight_decay"]))), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_apply_multi")
-            else:
+        # ---- side stream: shape groups without the kernel path (no bf16 shadow), then the AdamW slice gathers
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for g, st in slow:
+                ga = st["arena"]
+                r, c = ga.shape
+                n_own = self.num_owned(ga)
+                if n_own > 0:
+                    tmp = torch.empty((n_own, r, c), dtype=torch.float32, device=self.device)
+                    comm.reduce_from_peers(ga.G, rank * ga.chunk * r * c, tmp)
+                    tmp.mul_(gscale)
+                    st["U"][:n_own].copy_(muon_update_ref(tmp, st["momentum"][:n_own], st["second"][:n_own],
+                                                          float(g["momentum"]), float(g["beta2"]), int(g["ns_steps"])))
+            comm.device_barrier()                                                                  # last
+            for g, st in slow:
+                ga = st["arena"]
+                r, c = ga.shape
                 comm.all_gather(st["U_all"], st["U"], async_op=False)
-                muon_apply_ref(ga.P, st["U_all"][:ga.n], lr_eff, wd)
-        self._mark("muon_apply_pull")
-        for p in gathers:
-            comm.gather_slices(p.data)
-            if p is head and arena.head_w16 is not None:
-                arena.head_w16.copy_(p.data)
-        self._mark("adamw_gather")
+                muon_apply_ref(ga.P, st["U_all"][:ga.n], float(g["lr"]) * max(1.0, r / c) ** 0.5, float(g["weight_decay"]))
+            for p in gathers:
+                comm.gather_slices(p.data)
+                if p is head and arena.head_w16 is not None:
+                    arena.head_w16.copy_(p.data)
+        main.wait_stream(side)
+        self._mark("join")
 
     def _adamw_small(self, grp, smalls, grads_flat, gscale):
         """One launch per run of parameters that are adjacent in the flat small-parameter buffer."""
