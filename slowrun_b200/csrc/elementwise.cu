@@ -432,6 +432,86 @@ __global__ void dropout_add_bwd_kernel(const __nv_bfloat16* __restrict__ g, cons
   }
 }
 
+
+// ------------------------------------------------------------------ residual + dropout fused with the following RMSNorm
+// x_mid = x + drop(y);  n = rmsnorm(x_mid).  One warp per row; the norm is taken of the bf16-rounded x_mid, exactly as
+// the two separate kernels would. Element (row, c) uses the same mask index as dropout_add_fwd_kernel (row * D + c).
+__global__ void add_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
+                                    __nv_bfloat16* __restrict__ x_mid, __nv_bfloat16* __restrict__ n, long rows, int D,
+                                    float eps, float p, uint64_t salt, const unsigned long long* __restrict__ seed_ptr) {
+  const long row = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint64_t seed = salt + (seed_ptr ? (*seed_ptr) * 0x9E3779B97F4A7C15ull : 0ull);
+  const float scale = 1.f / (1.f - p);
+  const long base = row * (long)D;
+  float ss = 0.f;
+  for (int c = lane * 8; c < D; c += 256) {
+    float a[8], b[8];
+    load8(x + base + c, a);
+    load8(y + base + c, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (p > 0.f) b[j] = keep_elem(seed, (uint64_t)(base + c + j), p) ? b[j] * scale : 0.f;
+      a[j] = __bfloat162float(__float2bfloat16(a[j] + b[j]));
+      ss += a[j] * a[j];
+    }
+    store8(x_mid + base + c, a);
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / D + eps);
+  for (int c = lane * 8; c < D; c += 256) {
+    float f[8];
+    load8(x_mid + base + c, f);   // this lane's own stores
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= r;
+    store8(n + base + c, f);
+  }
+}
+
+// Backward of the pair above seen from the MLP side: dx_mid = rmsnorm_bwd(x_mid, dn) + g_res, and the gradient of the
+// dropped branch dy = mask/(1-p) * dx_mid (of the bf16-rounded dx_mid), in one pass over the row.
+__global__ void norm_bwd_drop_kernel(const __nv_bfloat16* __restrict__ x_mid, const __nv_bfloat16* __restrict__ dn,
+                                     const __nv_bfloat16* __restrict__ g_res, __nv_bfloat16* __restrict__ dx_mid,
+                                     __nv_bfloat16* __restrict__ dy, long rows, int D, float eps, float p, uint64_t salt,
+                                     const unsigned long long* __restrict__ seed_ptr) {
+  const long row = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint64_t seed = salt + (seed_ptr ? (*seed_ptr) * 0x9E3779B97F4A7C15ull : 0ull);
+  const float scale = 1.f / (1.f - p);
+  const long base = row * (long)D;
+  float ss = 0.f, dot = 0.f;
+  for (int c = lane * 8; c < D; c += 256) {
+    float f[8], g[8];
+    load8(x_mid + base + c, f);
+    load8(dn + base + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ss += f[i] * f[i];
+      dot += f[i] * g[i];
+    }
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float r = rsqrtf(ss / D + eps);
+  const float k = r * r * r * dot / D;
+  for (int c = lane * 8; c < D; c += 256) {
+    float f[8], g[8], a[8], o[8], d[8];
+    load8(x_mid + base + c, f);
+    load8(dn + base + c, g);
+    load8(g_res + base + c, a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[i] = __bfloat162float(__float2bfloat16(r * g[i] - k * f[i] + a[i]));
+      const bool keep = (p > 0.f) ? keep_elem(seed, (uint64_t)(base + c + i), p) : true;
+      d[i] = keep ? scale * o[i] : 0.f;
+    }
+    store8(dx_mid + base + c, o);
+    store8(dy + base + c, d);
+  }
+}
+
 // grad_fp32 += g (bf16)   -- accumulation of a bf16 weight gradient into the fp32 gradient arena
 __global__ void acc_bf16_into_f32_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ g, long n8) {
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
@@ -547,5 +627,25 @@ extern "C" int sr_dropout_add_bwd(const void* g, const float* keep, void* dy, vo
 extern "C" int sr_acc_bf16_into_f32(float* acc, const void* g, long n, cudaStream_t s) {
   if (n % 8) return -2;
   acc_bf16_into_f32_kernel<<<grid_for(n / 8, kThreads), kThreads, 0, s>>>(acc, BF(g), n / 8);
+  return rc();
+}
+
+// x_mid = x + dropout(y); n = rmsnorm(x_mid). Contiguous [rows, D] bf16, D % 8 == 0. Same mask as sr_dropout_add_fwd.
+extern "C" int sr_add_norm_fwd(const void* x, const void* y, void* x_mid, void* n, long rows, int D, float eps, float p,
+                               unsigned long long seed, const unsigned long long* seed_ptr, cudaStream_t s) {
+  if (D % 8) return -2;
+  if (rows <= 0) return 0;
+  add_norm_fwd_kernel<<<(unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(x), BF(y), BFM(x_mid), BFM(n), rows, D, eps, p, seed, seed_ptr);
+  return rc();
+}
+// dx_mid = rmsnorm_bwd(x_mid, dn) + g_res; dy = dropout_bwd(dx_mid) with the mask of sr_add_norm_fwd / sr_dropout_add_fwd.
+extern "C" int sr_norm_bwd_drop(const void* x_mid, const void* dn, const void* g_res, void* dx_mid, void* dy, long rows,
+                                int D, float eps, float p, unsigned long long seed, const unsigned long long* seed_ptr,
+                                cudaStream_t s) {
+  if (D % 8) return -2;
+  if (rows <= 0) return 0;
+  norm_bwd_drop_kernel<<<(unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(x_mid), BF(dn), BF(g_res), BFM(dx_mid), BFM(dy), rows, D, eps, p, seed, seed_ptr);
   return rc();
 }

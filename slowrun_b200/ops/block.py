@@ -174,8 +174,9 @@ class _BlockFn(Function):
         p_mlp = float(mlp.dropout) if training else 0.0
         seed1 = ops.next_dropout_seed() if p_attn > 0 else 0
         seed2 = ops.next_dropout_seed() if p_mlp > 0 else 0
-        x_mid = _dropout_add_fwd(x, o, p_attn, seed1)
-        n = _rmsnorm_fwd(x_mid, eps)
+        x_mid, n = torch.empty_like(x), torch.empty_like(x)
+        _call("sr_add_norm_fwd", [P] * 4 + [L, I, F32, F32, ULL, P, P], x.data_ptr(), o.data_ptr(), x_mid.data_ptr(), n.data_ptr(),
+              M, C, eps, p_attn, seed1, ops.dropout_state(x.device).data_ptr(), _sp())
         mz = mlp.fused
         gf = gemm(n, mz["gf_w16"])
         hdim = gf.size(1) // 2
@@ -216,9 +217,10 @@ class _BlockFn(Function):
         _call("sr_swiglu_bwd", [P, P, P, L, I, P], gf.data_ptr(), dhdn.data_ptr(), dgf.data_ptr(), M, gf.size(1) // 2, _sp())
         dn = gemm(dgf, mz["gf_w16"], b_mn=True)
         gemm(dgf, n, out=mz["gf_grad"], cin=mz["gf_grad"], a_mn=True, b_mn=True, beta=1.0)
-        g_mid_tot = _rmsnorm_bwd(x_mid, dn, g_mid, eps)
-        # ---- attention branch
-        do, _, _ = _dropout_add_bwd(g_mid_tot, p_attn, seed1)
+        # ---- attention branch: norm backward + residual gradient + gradient of the dropped branch in one pass
+        g_mid_tot, do = torch.empty_like(x_mid), torch.empty_like(x_mid)
+        _call("sr_norm_bwd_drop", [P] * 5 + [L, I, F32, F32, ULL, P, P], x_mid.data_ptr(), dn.data_ptr(), g_mid.data_ptr(),
+              g_mid_tot.data_ptr(), do.data_ptr(), M, C, eps, p_attn, seed1, ops.dropout_state(g.device).data_ptr(), _sp())
         dy2 = gemm(do, fz["proj_w16"], b_mn=True)
         gemm(do, y2.view(M, C), out=fz["proj_grad"], cin=fz["proj_grad"], a_mn=True, b_mn=True, beta=1.0)
         dy = torch.empty_like(y)

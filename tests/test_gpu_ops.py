@@ -506,3 +506,59 @@ def test_iha_mixing_kernels(H, J):
     dmix_ref = torch.bmm(dwp.view(P, H, J).float(), w.view(P, H, J).float().transpose(1, 2))
     assert torch.allclose(gw.view(P, H, J), gw_ref, rtol=1e-3, atol=1e-3)
     assert torch.allclose(dmix, dmix_ref, rtol=2e-3, atol=2e-3 * dmix_ref.abs().max().item())
+
+
+@pytest.mark.parametrize("nc,scale", [(12, 1.0), (32, 2.0)])
+def test_per_head_gate_kernels(nc, scale):
+    """gate = scale * sigmoid(a[:, :nc] @ bf16(W)^T) and its backward (weight gradient accumulated, input gradient added)."""
+    from slowrun_b200.ops.block import _gate_bwd, _gate_fwd
+    M, C, H = 1000, 256, 20
+    a = _bf(M, C, seed=51)
+    w = torch.nn.Parameter(torch.randn(H, nc, device="cuda") * 0.3)
+    gate = _gate_fwd(a, w.data, H, nc, scale)
+    af = a.float().requires_grad_(True)
+    wf = w.detach().bfloat16().float().requires_grad_(True)
+    z = (af[:, :nc] @ wf.t()).bfloat16().float()
+    ref = scale * torch.sigmoid(z)
+    _status_ok()
+    assert torch.allclose(gate, ref, rtol=1e-3, atol=1e-3)
+    dg = torch.randn(M, H, device="cuda")
+    zz = af[:, :nc] @ wf.t()
+    (scale * torch.sigmoid(zz) * dg).sum().backward()
+    w.grad = torch.full_like(w, 0.5)
+    da = _bf(M, C, seed=52)
+    da0 = da.clone()
+    _gate_bwd(dg, gate, a, w, da, H, nc, scale)
+    _status_ok()
+    assert torch.allclose(w.grad - 0.5, wf.grad, rtol=2e-2, atol=2e-2 * wf.grad.abs().max().item())
+    assert torch.equal(da[:, nc:], da0[:, nc:])
+    _close(da[:, :nc].float() - da0[:, :nc].float(), af.grad[:, :nc], 4e-2, 4e-2)
+
+
+def test_attention_backward_with_gate_delta_and_fp32_dq():
+    """The fused-block form of the attention backward: delta comes out of the head-gate backward, dQ stays in fp32."""
+    from slowrun_b200.ops import _lib
+    from slowrun_b200.ops.block import P, I, L, _call, _sp
+    from slowrun_b200.ops.flash_attention import _has, native_available, native_bwd, native_fwd
+    if not (native_available() and _has("sr_flash_attn_bwd_ex")):
+        pytest.skip("native attention backward not built")
+    B, T, H, D = 2, 512, 3, 128
+    q, k, v = _bf(B, T, H, D, seed=61), _bf(B, T, H, D, seed=62), _bf(B, T, H, D, seed=63)
+    y, lse, sc, w = native_fwd(q, k, v, 200, None)
+    gate = torch.rand(B * T, H, device="cuda")
+    dy2 = _bf(B, T, H, D, seed=64)
+    dy = torch.empty_like(y)
+    dgate = torch.empty(B * T, H, device="cuda")
+    delta = torch.empty(B, H, T, device="cuda")
+    _call("sr_head_gate_bwd_delta", [P] * 6 + [L, I, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), gate.data_ptr(), dy.data_ptr(),
+          dgate.data_ptr(), delta.data_ptr(), B * T, H, T, H * D, H * D, H * D, _sp())
+    _status_ok()
+    delta_ref = (dy.float() * y.float()).sum(-1).permute(0, 2, 1)
+    assert torch.allclose(delta, delta_ref, rtol=2e-2, atol=2e-2 * delta_ref.abs().max().item())
+    dq32, dk, dv = native_bwd(dy, q, k, v, y, lse, sc, w, delta=delta, dq_fp32=True)
+    dq, dk2, dv2 = native_bwd(dy, q, k, v, y, lse, sc, w)
+    _status_ok()
+    assert dq32.dtype == torch.float32
+    _close(dq32, dq, 2e-2, 2e-2)
+    _close(dk, dk2, 2e-2, 2e-2)
+    _close(dv, dv2, 2e-2, 2e-2)
