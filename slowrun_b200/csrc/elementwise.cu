@@ -204,6 +204,122 @@ __global__ void lambda_mix_bwd_kernel(const __nv_bfloat16* __restrict__ g, const
   }
 }
 
+
+// ------------------------------------------------------------------ lambda mix fused with the block's first RMSNorm
+// x = lr*(xp + ws*skip) + l0*x0 ; a = rmsnorm(x) (of the bf16-rounded x). One warp per row.
+__global__ void mix_norm_fwd_kernel(const __nv_bfloat16* __restrict__ xp, const __nv_bfloat16* __restrict__ x0,
+                                    const __nv_bfloat16* __restrict__ skip, __nv_bfloat16* __restrict__ x,
+                                    __nv_bfloat16* __restrict__ a_out, const float* __restrict__ lr_p,
+                                    const float* __restrict__ l0_p, const float* __restrict__ ws_p, long rows, int D,
+                                    float eps) {
+  const long row = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float lr = *lr_p, l0 = *l0_p, ws = skip ? *ws_p : 0.f;
+  const long base = row * (long)D;
+  float ss = 0.f;
+  for (int c = lane * 8; c < D; c += 256) {
+    float a[8], b[8];
+    load8(xp + base + c, a);
+    load8(x0 + base + c, b);
+    if (skip) {
+      float s[8];
+      load8(skip + base + c, s);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += ws * s[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[j] = __bfloat162float(__float2bfloat16(lr * a[j] + l0 * b[j]));
+      ss += a[j] * a[j];
+    }
+    store8(x + base + c, a);
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / D + eps);
+  for (int c = lane * 8; c < D; c += 256) {
+    float f[8];
+    load8(x + base + c, f);   // this lane's own stores
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= r;
+    store8(a_out + base + c, f);
+  }
+}
+
+// Backward of the pair above: g = rmsnorm_bwd(x, da) + g_res (rounded to bf16, never stored), then
+// dxp = lr*g ; dskip = lr*ws*g ; dx0 = l0*g ; dscal[0..2] += (sum g*(xp + ws*skip), sum g*x0, sum g*lr*skip).
+__global__ void norm_bwd_mix_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ da,
+                                    const __nv_bfloat16* __restrict__ g_res, const __nv_bfloat16* __restrict__ xp,
+                                    const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ skip,
+                                    __nv_bfloat16* __restrict__ dxp, __nv_bfloat16* __restrict__ dx0,
+                                    __nv_bfloat16* __restrict__ dskip, const float* __restrict__ lr_p,
+                                    const float* __restrict__ l0_p, const float* __restrict__ ws_p,
+                                    float* __restrict__ d_lr, float* __restrict__ d_l0, float* __restrict__ d_ws,
+                                    long rows, int D, float eps) {
+  __shared__ float red[32];
+  const long row = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const float lr = *lr_p, l0 = *l0_p, ws = skip ? *ws_p : 0.f;
+  float s_lr = 0.f, s_l0 = 0.f, s_ws = 0.f;
+  if (row < rows) {
+    const long base = row * (long)D;
+    float ss = 0.f, dot = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+      float f[8], g[8];
+      load8(x + base + c, f);
+      load8(da + base + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        ss += f[i] * f[i];
+        dot += f[i] * g[i];
+      }
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float r = rsqrtf(ss / D + eps);
+    const float k = r * r * r * dot / D;
+    for (int c = lane * 8; c < D; c += 256) {
+      float f[8], g[8], e[8], a[8], b[8], o[8];
+      load8(x + base + c, f);
+      load8(da + base + c, g);
+      load8(g_res + base + c, e);
+      load8(xp + base + c, a);
+      load8(x0 + base + c, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g[i] = __bfloat162float(__float2bfloat16(r * g[i] - k * f[i] + e[i]));
+      if (skip) {
+        float sk[8];
+        load8(skip + base + c, sk);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          a[j] += ws * sk[j];
+          s_ws += g[j] * lr * sk[j];
+          o[j] = lr * ws * g[j];
+        }
+        store8(dskip + base + c, o);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s_lr += g[j] * a[j];
+        s_l0 += g[j] * b[j];
+        o[j] = lr * g[j];
+      }
+      store8(dxp + base + c, o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = l0 * g[j];
+      store8(dx0 + base + c, o);
+    }
+  }
+  s_lr = block_sum(s_lr, red);
+  s_l0 = block_sum(s_l0, red);
+  s_ws = block_sum(s_ws, red);
+  if (threadIdx.x == 0) {
+    atomicAdd(d_lr, s_lr);
+    atomicAdd(d_l0, s_l0);
+    if (skip) atomicAdd(d_ws, s_ws);
+  }
+}
+
 // ------------------------------------------------------------------ RoPE + QK-norm, head_dim = 128
 // One warp per (token, head). Lane l owns elements {2l, 2l+1} of the first half and {64+2l, 64+2l+1} of the second.
 // in : [tokens, ld_in] with head h at column offset h*128 ; out: [tokens, H, 128] contiguous
@@ -647,5 +763,27 @@ extern "C" int sr_norm_bwd_drop(const void* x_mid, const void* dn, const void* g
   if (rows <= 0) return 0;
   norm_bwd_drop_kernel<<<(unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
       BF(x_mid), BF(dn), BF(g_res), BFM(dx_mid), BFM(dy), rows, D, eps, p, seed, seed_ptr);
+  return rc();
+}
+
+// x = lr*(xp + ws*skip) + l0*x0 and a = rmsnorm(x) in one pass; scalars are device pointers; skip may be null.
+extern "C" int sr_mix_norm_fwd(const void* xp, const void* x0, const void* skip, void* x, void* a, const float* lr,
+                               const float* l0, const float* ws, long rows, int D, float eps, cudaStream_t s) {
+  if (D % 8) return -2;
+  if (rows <= 0) return 0;
+  mix_norm_fwd_kernel<<<(unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(xp), BF(x0), BF(skip), BFM(x), BFM(a), lr, l0, ws, rows, D, eps);
+  return rc();
+}
+// Backward through the first norm and the lambda mix: see norm_bwd_mix_kernel. d_lr / d_l0 / d_ws: the fp32 gradient
+// entries of the three scalars, accumulated into (d_ws is not touched without a skip input).
+extern "C" int sr_norm_bwd_mix(const void* x, const void* da, const void* g_res, const void* xp, const void* x0,
+                               const void* skip, void* dxp, void* dx0, void* dskip, const float* lr, const float* l0,
+                               const float* ws, float* d_lr, float* d_l0, float* d_ws, long rows, int D, float eps,
+                               cudaStream_t s) {
+  if (D % 8) return -2;
+  if (rows <= 0) return 0;
+  norm_bwd_mix_kernel<<<(unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
+      BF(x), BF(da), BF(g_res), BF(xp), BF(x0), BF(skip), BFM(dxp), BFM(dx0), BFM(dskip), lr, l0, ws, d_lr, d_l0, d_ws, rows, D, eps);
   return rc();
 }

@@ -134,13 +134,14 @@ class _BlockFn(Function):
             sk = sk if sk.is_contiguous() else sk.contiguous()
         # ---- lambda mix
         if do_mix:
-            x = torch.empty_like(xp)
+            x, a = torch.empty_like(xp), torch.empty_like(xp)
             rl, xl, sw = model.resid_lambdas, model.x0_lambdas, model.skip_weights
-            _call("sr_lambda_mix_fwd", [P] * 7 + [L, P], xp.data_ptr(), x0_2.data_ptr(), _lib.ptr(sk), x.data_ptr(),
-                  rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i, sw.data_ptr() + 4 * j if sk is not None else 0, xp.numel(), _sp())
+            _call("sr_mix_norm_fwd", [P] * 8 + [L, I, F32, P], xp.data_ptr(), x0_2.data_ptr(), _lib.ptr(sk), x.data_ptr(),
+                  a.data_ptr(), rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i, sw.data_ptr() + 4 * j if sk is not None else 0,
+                  M, C, eps, _sp())
         else:
             x = xp
-        a = _rmsnorm_fwd(x, eps)
+            a = _rmsnorm_fwd(x, eps)
         # ---- projections
         ve = gemm(x0_2, ve_lin.fused["w16"]) if ve_lin is not None else None
         fz = attn.fused
@@ -263,23 +264,21 @@ class _BlockFn(Function):
         # ---- back through the first norm and the lambda mix
         if g_in is not None:
             g_mid_tot.add_(g_in)
-        g_x = _rmsnorm_bwd(x, da, g_mid_tot, eps)
         if not do_mix:
+            g_x = _rmsnorm_bwd(x, da, g_mid_tot, eps)
             if ve is not None:
                 dx0 = gemm(dve, ve_lin.fused["w16"], b_mn=True)
             return (g_x.view(B, T, C), dx0.view(B, T, C) if dx0 is not None else None, None) + (None,) * 9
-        dxp = torch.empty_like(g_x)
-        dx0 = torch.empty_like(g_x)
-        dsk = torch.empty_like(g_x) if has_skip else None
-        dscal = torch.zeros(3, dtype=torch.float32, device=g.device)
+        dxp = torch.empty_like(x)
+        dx0 = torch.empty_like(x)
+        dsk = torch.empty_like(x) if has_skip else None
         rl, xl, sw = model.resid_lambdas, model.x0_lambdas, model.skip_weights
-        _call("sr_lambda_mix_bwd", [P] * 11 + [L, P], g_x.data_ptr(), xp.data_ptr(), x0_2.data_ptr(), sk.data_ptr() if has_skip else 0,
-              dxp.data_ptr(), dx0.data_ptr(), _lib.ptr(dsk), rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i,
-              sw.data_ptr() + 4 * j if has_skip else 0, dscal.data_ptr(), g_x.numel(), _sp())
-        rl.grad[i] += dscal[0]
-        xl.grad[i] += dscal[1]
-        if has_skip:
-            sw.grad[j] += dscal[2]
+        # the three scalar gradients are accumulated straight into the (fp32, arena-backed) .grad entries
+        _call("sr_norm_bwd_mix", [P] * 15 + [L, I, F32, P], x.data_ptr(), da.data_ptr(), g_mid_tot.data_ptr(), xp.data_ptr(),
+              x0_2.data_ptr(), sk.data_ptr() if has_skip else 0, dxp.data_ptr(), dx0.data_ptr(), _lib.ptr(dsk),
+              rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i, sw.data_ptr() + 4 * j if has_skip else 0,
+              rl.grad.data_ptr() + 4 * i, xl.grad.data_ptr() + 4 * i, sw.grad.data_ptr() + 4 * j if has_skip else 0,
+              M, C, eps, _sp())
         if ve is not None:
             gemm(dve, ve_lin.fused["w16"], out=dx0, cin=dx0, b_mn=True, beta=1.0)
         return (dxp.view(B, T, C), dx0.view(B, T, C), dsk.view(B, T, C) if dsk is not None else None) + (None,) * 9
