@@ -106,7 +106,8 @@ def main():
         out = {"what": "optimizer_step", "size": a.size, "n_gpus": W, "ms": res,
                "nvlink_bytes_in_per_rank": {"grad_pull": rs_in, "update_pull": ag_in},
                "ns_tflop_per_rank": ns_flops / 1e12, "roofline_ms": {"compute": t_compute, "link": t_link, "peaks": src},
-               "frac_of_roofline": {k: roof / v for k, v in res.items()}, "fused_phases_ms_rank0": phases}
+               "frac_of_roofline": {k: roof / v for k, v in res.items()}, "fused_phases_ms_rank0": phases,
+               "nvls_multimem_pull": bool(fused is not None and fused.multicast_ptr(next(iter(model.arena.groups.values())).G))}
         print(json.dumps(out))
     if W > 1:
         dist.barrier()

@@ -62,46 +62,33 @@ __global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_
 // read the rows of their own chunks). Pass 2 rereads it from L2, applies the row norm and writes the bf16 input of the
 // Newton-Schulz iteration.
 constexpr int kPullWorld = 8;   // peers handled by the unrolled load stage; larger worlds take extra rounds
+
+// sum over all ranks of the 16 bytes at this multicast address, reduced inside the NVSwitch (NVLS): one load returns
+// what W peer loads would, and only 1/W of the bytes cross this GPU's links
+__device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
 __global__ void __launch_bounds__(kThreads, 2)
-muon_pre_multi_kernel(PtrTable G, int world, int rank, long base, float* __restrict__ Mom,
+muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int rank, long base, float* __restrict__ Mom,
                       __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
                       float gscale) {
   const int lane = threadIdx.x & 31;
   // at most one CTA per SM (the launcher caps the grid): the kernel is meant to share the SMs with the Newton-Schulz
   // GEMMs of the neighbouring shape group, which need one CTA's worth of registers and shared memory on every SM
   for (long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5); row < rows_total; row += (long)gridDim.x * kWarps) {
-  float* m = Mom + row * c;
-  __nv_bfloat16* x = X + row * c;
-  const long off = base + row * c;
-  float* park = reinterpret_cast<float*>(const_cast<void*>(G.p[rank])) + off;
-  float ss = 0.f;
-  for (int j0 = lane * 4; j0 < c; j0 += 256) {
-    const int j1 = j0 + 128;
-    const bool has1 = j1 < c;
-    float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
-    for (int p0 = 0; p0 < world; p0 += kPullWorld) {
-      float4 t0[kPullWorld], t1[kPullWorld];
-#pragma unroll
-      for (int p = 0; p < kPullWorld; ++p) {
-        if (p0 + p < world) {
-          const float* src = reinterpret_cast<const float*>(G.p[p0 + p]) + off;
-          t0[p] = *reinterpret_cast<const float4*>(src + j0);
-          if (has1) t1[p] = *reinterpret_cast<const float4*>(src + j1);
-        }
-      }
-#pragma unroll
-      for (int p = 0; p < kPullWorld; ++p) {
-        if (p0 + p < world) {
-          g0.x += t0[p].x; g0.y += t0[p].y; g0.z += t0[p].z; g0.w += t0[p].w;
-          if (has1) { g1.x += t1[p].x; g1.y += t1[p].y; g1.z += t1[p].z; g1.w += t1[p].w; }
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      if (u == 1 && !has1) break;
-      const int j = u == 0 ? j0 : j1;
-      float4 gv = u == 0 ? g0 : g1;
+    float* m = Mom + row * c;
+    __nv_bfloat16* x = X + row * c;
+    const long off = base + row * c;
+    float* park = reinterpret_cast<float*>(const_cast<void*>(G.p[rank])) + off;
+    float ss = 0.f;
+    // momentum update + Nesterov gradient of four reduced columns; the Nesterov value is parked in the local row
+    auto consume = [&](int j, float4 gv) {
       gv.x *= gscale; gv.y *= gscale; gv.z *= gscale; gv.w *= gscale;
       float4 mv = *reinterpret_cast<const float4*>(m + j);
       mv.x += (1.f - mu) * (gv.x - mv.x); mv.y += (1.f - mu) * (gv.y - mv.y);
@@ -112,22 +99,59 @@ muon_pre_multi_kernel(PtrTable G, int world, int rank, long base, float* __restr
       nv.z = gv.z + mu * (mv.z - gv.z); nv.w = gv.w + mu * (mv.w - gv.w);
       ss += nv.x * nv.x + nv.y * nv.y + nv.z * nv.z + nv.w * nv.w;
       *reinterpret_cast<float4*>(park + j) = nv;
+    };
+    if (mc != nullptr) {
+      // NVLS path: four independent in-switch reductions in flight per lane
+      for (int j0 = lane * 4; j0 < c; j0 += 512) {
+        float4 g[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + u * 128 < c) g[u] = multimem_sum_f32x4(mc + off + j0 + u * 128);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + u * 128 < c) consume(j0 + u * 128, g[u]);
+      }
+    } else {
+      for (int j0 = lane * 4; j0 < c; j0 += 256) {
+        const int j1 = j0 + 128;
+        const bool has1 = j1 < c;
+        float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+        for (int p0 = 0; p0 < world; p0 += kPullWorld) {
+          float4 t0[kPullWorld], t1[kPullWorld];
+#pragma unroll
+          for (int p = 0; p < kPullWorld; ++p) {
+            if (p0 + p < world) {
+              const float* src = reinterpret_cast<const float*>(G.p[p0 + p]) + off;
+              t0[p] = *reinterpret_cast<const float4*>(src + j0);
+              if (has1) t1[p] = *reinterpret_cast<const float4*>(src + j1);
+            }
+          }
+#pragma unroll
+          for (int p = 0; p < kPullWorld; ++p) {
+            if (p0 + p < world) {
+              g0.x += t0[p].x; g0.y += t0[p].y; g0.z += t0[p].z; g0.w += t0[p].w;
+              if (has1) { g1.x += t1[p].x; g1.y += t1[p].y; g1.z += t1[p].z; g1.w += t1[p].w; }
+            }
+          }
+        }
+        consume(j0, g0);
+        if (has1) consume(j1, g1);
+      }
     }
-  }
-  ss = warp_sum(ss);
-  const float inv = 1.f / fmaxf(sqrtf(ss), 1e-7f);
-  float xs = 0.f;
-  for (int j = lane * 4; j < c; j += 128) {
-    const float4 nv = *reinterpret_cast<const float4*>(park + j);   // written by this same lane above
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(nv.x * inv, nv.y * inv);
-    const __nv_bfloat162 hi = __floats2bfloat162_rn(nv.z * inv, nv.w * inv);
-    *reinterpret_cast<__nv_bfloat162*>(x + j) = lo;
-    *reinterpret_cast<__nv_bfloat162*>(x + j + 2) = hi;
-    const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
-    xs += l.x * l.x + l.y * l.y + h.x * h.x + h.y * h.y;
-  }
-  xs = warp_sum(xs);
-  if (lane == 0) atomicAdd(sumsq + row / r, xs);
+    ss = warp_sum(ss);
+    const float inv = 1.f / fmaxf(sqrtf(ss), 1e-7f);
+    float xs = 0.f;
+    for (int j = lane * 4; j < c; j += 128) {
+      const float4 nv = *reinterpret_cast<const float4*>(park + j);   // written by this same lane above
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(nv.x * inv, nv.y * inv);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(nv.z * inv, nv.w * inv);
+      *reinterpret_cast<__nv_bfloat162*>(x + j) = lo;
+      *reinterpret_cast<__nv_bfloat162*>(x + j + 2) = hi;
+      const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
+      xs += l.x * l.x + l.y * l.y + h.x * h.x + h.y * h.y;
+    }
+    xs = warp_sum(xs);
+    if (lane == 0) atomicAdd(sumsq + row / r, xs);
   }
 }
 
@@ -226,7 +250,9 @@ extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, in
 }
 
 // `rank`: index of the calling rank in g_ptrs; its own copy of the owned rows is overwritten (used as scratch).
-extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, int world, int rank, long base, float* Mom, void* X,
+// `mc`: multicast (NVLS) address of the same symmetric buffer, or null for plain peer loads.
+extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* mc, int world, int rank, long base,
+                                 float* Mom, void* X,
                                  float* sumsq, int n, int r, int c, float mu, float gscale, cudaStream_t s) {
   if (n <= 0) return 0;
   if (c % 4 || rank < 0 || rank >= world) return -2;
@@ -237,7 +263,7 @@ extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, int world, in
   long pull_grid = (rows + kWarps - 1) / kWarps;
   if (pull_grid > 148) pull_grid = 148;
   muon_pre_multi_kernel<<<(unsigned)pull_grid, kThreads, 0, s>>>(
-      t, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
+      t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
   const long total = rows * c;
   fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total);
   return rc();

@@ -283,8 +283,9 @@ class ShardedMuonAdamW:
             r, c = ga.shape
             n_own = self.num_owned(ga)
             if n_own > 0:
-                rc = _lib.fn("sr_muon_pre_multi", [cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
-                    ctypes.cast(comm.peer_ptrs(ga.G), cvp), W, rank, rank * ga.chunk * r * c, st["momentum"].data_ptr(),
+                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
+                    ctypes.cast(comm.peer_ptrs(ga.G), cvp), comm.multicast_ptr(ga.G), W, rank, rank * ga.chunk * r * c,
+                    st["momentum"].data_ptr(),
                     st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale, _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_pre_multi")
             ev = torch.cuda.Event()

@@ -73,6 +73,24 @@ class FusedComm(TorchComm):
         raise KeyError("tensor was not allocated through FusedComm.alloc")
 
     # ------------------------------------------------------------------ device-side barrier
+    def multicast_ptr(self, t: torch.Tensor) -> int:
+        """NVLS multicast address of `t` (reads through it return the sum over all ranks, reduced in the switch), or 0
+        when the allocation has no multicast mapping or SLOWRUN_MULTIMEM=0."""
+        import os
+        if os.environ.get("SLOWRUN_MULTIMEM", "1") == "0":
+            return 0
+        a = t.data_ptr()
+        for base, nbytes, hdl in self._allocs:
+            if base <= a < base + max(nbytes, 1):
+                try:
+                    mc = int(hdl.multicast_ptr or 0)
+                except Exception:  # noqa: BLE001
+                    mc = 0
+                if mc == 0:
+                    return 0
+                return mc + (a - int(list(hdl.buffer_ptrs)[hdl.rank]))
+        return 0
+
     def device_barrier(self):
         """All ranks' preceding work on the current stream is complete and visible before any rank proceeds."""
         self.epoch += 1
