@@ -50,6 +50,7 @@ def main():
     opts = {"nccl": ShardedMuonAdamW(model, groups, TorchComm())}
     if fused is not None:
         opts["fused"] = ShardedMuonAdamW(model, groups, fused)
+        opts["fused_overlap"] = opts["fused"]
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
     for ga in model.arena.groups.values():
         ga.G.normal_(0, 0.02, generator=gen)
@@ -76,7 +77,17 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    res = {k: timed(o) for k, o in opts.items()}
+    res = {}
+    for k, o in opts.items():
+        o.overlap = (k == "fused_overlap")
+        res[k] = timed(o)
+    if fused is not None:
+        o = opts["fused"]
+        o.overlap = "auto"
+        for _ in range(4):
+            o.step()
+        res["fused_auto"] = timed(o)
+        o.overlap = False
     _lib.check_status()
     phases = None
     if "fused" in opts:
@@ -107,6 +118,7 @@ def main():
                "nvlink_bytes_in_per_rank": {"grad_pull": rs_in, "update_pull": ag_in},
                "ns_tflop_per_rank": ns_flops / 1e12, "roofline_ms": {"compute": t_compute, "link": t_link, "peaks": src},
                "frac_of_roofline": {k: roof / v for k, v in res.items()}, "fused_phases_ms_rank0": phases,
+               "auto_choice": getattr(opts.get("fused"), "tuned", None) if fused is not None else None,
                "nvls_multimem_pull": bool(fused is not None and fused.multicast_ptr(next(iter(model.arena.groups.values())).G))}
         print(json.dumps(out))
     if W > 1:

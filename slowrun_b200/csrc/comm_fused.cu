@@ -186,6 +186,50 @@ __global__ void muon_apply_multi_kernel(float* __restrict__ P, PtrTable U, long 
   }
 }
 
+// Same update, eight elements per thread and two independent groups per iteration: 16-byte peer loads and four times
+// the bytes in flight per thread (the kernel is bound by the latency of the remote reads otherwise).
+__device__ __forceinline__ void apply8(float* __restrict__ P, const uint4& raw, __nv_bfloat16* __restrict__ shadow, long i,
+                                       float lr_b, float lrwd_b) {
+  float4 p0 = *reinterpret_cast<float4*>(P + i), p1 = *reinterpret_cast<float4*>(P + i + 4);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 u0 = __bfloat1622float2(h[0]), u1 = __bfloat1622float2(h[1]), u2 = __bfloat1622float2(h[2]),
+               u3 = __bfloat1622float2(h[3]);
+  p0.x -= bf16_round(lr_b * u0.x) + ((u0.x * p0.x >= 0.f) ? lrwd_b * p0.x : 0.f);
+  p0.y -= bf16_round(lr_b * u0.y) + ((u0.y * p0.y >= 0.f) ? lrwd_b * p0.y : 0.f);
+  p0.z -= bf16_round(lr_b * u1.x) + ((u1.x * p0.z >= 0.f) ? lrwd_b * p0.z : 0.f);
+  p0.w -= bf16_round(lr_b * u1.y) + ((u1.y * p0.w >= 0.f) ? lrwd_b * p0.w : 0.f);
+  p1.x -= bf16_round(lr_b * u2.x) + ((u2.x * p1.x >= 0.f) ? lrwd_b * p1.x : 0.f);
+  p1.y -= bf16_round(lr_b * u2.y) + ((u2.y * p1.y >= 0.f) ? lrwd_b * p1.y : 0.f);
+  p1.z -= bf16_round(lr_b * u3.x) + ((u3.x * p1.z >= 0.f) ? lrwd_b * p1.z : 0.f);
+  p1.w -= bf16_round(lr_b * u3.y) + ((u3.y * p1.w >= 0.f) ? lrwd_b * p1.w : 0.f);
+  *reinterpret_cast<float4*>(P + i) = p0;
+  *reinterpret_cast<float4*>(P + i + 4) = p1;
+  if (shadow != nullptr) {
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+    oh[0] = __floats2bfloat162_rn(p0.x, p0.y); oh[1] = __floats2bfloat162_rn(p0.z, p0.w);
+    oh[2] = __floats2bfloat162_rn(p1.x, p1.y); oh[3] = __floats2bfloat162_rn(p1.z, p1.w);
+    *reinterpret_cast<uint4*>(shadow + i) = o;
+  }
+}
+__global__ void muon_apply_multi8_kernel(float* __restrict__ P, PtrTable U, long chunk_elems,
+                                         __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total) {
+  const long stride = (long)gridDim.x * blockDim.x * 8;
+  for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < total; i += 2 * stride) {
+    const long i2 = i + stride;
+    const bool has2 = i2 < total;
+    const long o1 = i / chunk_elems;
+    const uint4 r1 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(U.p[o1]) + (i - o1 * chunk_elems));
+    uint4 r2 = make_uint4(0, 0, 0, 0);
+    if (has2) {
+      const long o2 = i2 / chunk_elems;
+      r2 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(U.p[o2]) + (i2 - o2 * chunk_elems));
+    }
+    apply8(P, r1, shadow, i, lr_b, lrwd_b);
+    if (has2) apply8(P, r2, shadow, i2, lr_b, lrwd_b);
+  }
+}
+
 template <bool BF16>
 __global__ void reduce_multi_kernel(PtrTable src, int world, long offset, float* __restrict__ out, long n) {
   for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long)gridDim.x * blockDim.x * 4) {
@@ -251,9 +295,12 @@ extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, in
 
 // `rank`: index of the calling rank in g_ptrs; its own copy of the owned rows is overwritten (used as scratch).
 // `mc`: multicast (NVLS) address of the same symmetric buffer, or null for plain peer loads.
+// `shared_sms`: 1 = at most one CTA per SM (the kernel runs beside the Newton-Schulz GEMMs on another stream),
+// 0 = two CTAs per SM (it has the GPU to itself).
 extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* mc, int world, int rank, long base,
                                  float* Mom, void* X,
-                                 float* sumsq, int n, int r, int c, float mu, float gscale, cudaStream_t s) {
+                                 float* sumsq, int n, int r, int c, float mu, float gscale, int shared_sms,
+                                 cudaStream_t s) {
   if (n <= 0) return 0;
   if (c % 4 || rank < 0 || rank >= world) return -2;
   PtrTable t;
@@ -261,7 +308,8 @@ extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* 
   const long rows = (long)n * r;
   cudaMemsetAsync(sumsq, 0, sizeof(float) * n, s);
   long pull_grid = (rows + kWarps - 1) / kWarps;
-  if (pull_grid > 148) pull_grid = 148;
+  const long cap = shared_sms ? 148 : 296;
+  if (pull_grid > cap) pull_grid = cap;
   muon_pre_multi_kernel<<<(unsigned)pull_grid, kThreads, 0, s>>>(
       t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
   const long total = rows * c;
@@ -275,7 +323,10 @@ extern "C" int sr_muon_apply_multi(float* P, const unsigned long long* u_ptrs, i
   if (total % 4 || chunk_elems % 4) return -2;
   PtrTable t;
   if (!fill(t, u_ptrs, world)) return -2;
-  muon_apply_multi_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
+  if (total % 8 == 0 && chunk_elems % 8 == 0)
+    muon_apply_multi8_kernel<<<grid_for(total / 16, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
+  else
+    muon_apply_multi_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
   return rc();
 }
 

@@ -191,7 +191,7 @@ class ShardedMuonAdamW:
     @torch.no_grad()
     def step(self):
         if self.fused:
-            return self._step_fused()
+            return self._step_fused_tuned()
         self.step_count += 1
         W, rank, comm = self.world, self.rank, self.comm
         gscale = 1.0 / W
@@ -244,6 +244,38 @@ class ShardedMuonAdamW:
             out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
         return out
 
+    # ------------------------------------------------------------------ one-stream or two-stream order, measured
+    def _step_fused_tuned(self):
+        """`self.overlap` is True / False, or "auto" (default): steps 2 and 4 of the run are timed on the device in the
+        back-to-back and the two-stream order (steps 1 and 3 warm them up), the maximum over ranks is compared and
+        the faster order is kept. Both orders issue the same barriers in the same sequence and compute the same
+        update, so ranks may even disagree for a step without harm."""
+        mode = getattr(self, "overlap", "auto")
+        if mode != "auto":
+            return self._step_fused()
+        k = len(self._tune) if hasattr(self, "_tune") else 0
+        if not hasattr(self, "_tune"):
+            self._tune = []
+        self.overlap = k >= 2          # calls 0,1 back to back; calls 2,3 on two streams
+        timed = k in (1, 3)
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        try:
+            self._step_fused()
+        finally:
+            self.overlap = "auto"
+        ms = 0.0
+        if timed:
+            e1.record()
+            e1.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float32, device=self.device)
+            ms = float(self.comm.all_reduce_max(t).item())
+        self._tune.append(ms)
+        if k == 3:
+            self.overlap = bool(self._tune[3] < self._tune[1])
+            self.tuned = {"back_to_back_ms": self._tune[1], "two_stream_ms": self._tune[3], "overlap": self.overlap}
+
     # ------------------------------------------------------------------ fused peer-memory step
     @torch.no_grad()
     def _step_fused(self):
@@ -268,9 +300,12 @@ class ShardedMuonAdamW:
         self._marks = []
         self._mark("start")
         main = torch.cuda.current_stream(self.device)
-        if getattr(self, "_side", None) is None:
-            self._side = torch.cuda.Stream(device=self.device)
-        side = self._side
+        if getattr(self, "overlap", False) is True:
+            if getattr(self, "_side", None) is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            side = self._side
+        else:
+            side = main        # one stream: the same sequence, run back to back (every wait below is then a no-op)
         muon = [(g, self.state[g["name"]]) for g in self.param_groups if g["kind"] == "muon"]
         fast = [(g, st) for g, st in muon if "X" in st and st["arena"].W16 is not None]
         slow = [(g, st) for g, st in muon if not ("X" in st and st["arena"].W16 is not None)]
@@ -283,10 +318,11 @@ class ShardedMuonAdamW:
             r, c = ga.shape
             n_own = self.num_owned(ga)
             if n_own > 0:
-                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, cvp])(
+                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, c_int, cvp])(
                     ctypes.cast(comm.peer_ptrs(ga.G), cvp), comm.multicast_ptr(ga.G), W, rank, rank * ga.chunk * r * c,
                     st["momentum"].data_ptr(),
-                    st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale, _lib.stream_ptr())
+                    st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale,
+                    int(side is not main), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_pre_multi")
             ev = torch.cuda.Event()
             ev.record(side)
