@@ -67,10 +67,11 @@ constexpr int kPullWorld = 8;   // peers handled by the unrolled load stage; lar
 // what W peer loads would, and only 1/W of the bytes cross this GPU's links
 __device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
   float4 v;
+  // no memory clobber: the data was published by the barrier that precedes the kernel, and the compiler is free
+  // to keep several of these in flight around the surrounding arithmetic
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(mc_addr)
-               : "memory");
+               : "l"(mc_addr));
   return v;
 }
 
@@ -101,14 +102,14 @@ muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int r
       *reinterpret_cast<float4*>(park + j) = nv;
     };
     if (mc != nullptr) {
-      // NVLS path: four independent in-switch reductions in flight per lane
-      for (int j0 = lane * 4; j0 < c; j0 += 512) {
-        float4 g[4];
+      // NVLS path: eight independent in-switch reductions in flight per lane
+      for (int j0 = lane * 4; j0 < c; j0 += 1024) {
+        float4 g[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
           if (j0 + u * 128 < c) g[u] = multimem_sum_f32x4(mc + off + j0 + u * 128);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
           if (j0 + u * 128 < c) consume(j0 + u * 128, g[u]);
       }
     } else {

@@ -358,11 +358,18 @@ class ShardedMuonAdamW:
             comm.device_barrier()                                                                  # A
             ev_a = torch.cuda.Event()
             ev_a.record(side)
+            if side is main:
+                self._mark("barrier_a")
             pull_done = [pull(i) for i in range(len(fast))]      # all pulls first: they gate the compute
+            if side is main:
+                self._mark("muon_pull_pre")
             adamw_big()
+            if side is main:
+                self._mark("adamw_big")
         # ---- main stream: small replicated parameters (one packed all-reduce read), then the per-group compute
         main.wait_event(ev_a)
-        self._mark("barrier_a")
+        if side is not main:
+            self._mark("barrier_a")
         if arena.small_grads.numel() > 0:
             if "small_sum" not in self.state:
                 self.state["small_sum"] = torch.empty(arena.small_grads.numel(), dtype=torch.float32, device=self.device)
@@ -373,6 +380,7 @@ class ShardedMuonAdamW:
                     smalls = [p for p in g["params"] if self.state[id(p)]["small"]]
                     if smalls:
                         self._adamw_small(g, smalls, small_sum, gscale)
+        self._mark("adamw_small")
         for i, (g, st) in enumerate(fast):
             ga = st["arena"]
             r, c = ga.shape
