@@ -1,0 +1,82 @@
+"""Failure detection without any GPU fault: failures are made on the host.
+
+* a rank that leaves between steps: the surviving rank's next collective ends with an error inside the process-group
+  timeout instead of hanging (Gloo ranks on CPU);
+* a failing launcher return code and a non-zero kernel status word are turned into exceptions by the loader
+  (`ops/_lib.check_rc`, `check_status` semantics exercised on a fake status buffer).
+The reference has no failure handling at all (its collectives use the default 10-minute NCCL timeout, train.py:956).
+"""
+import os
+import socket
+import sys
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from slowrun_b200.parallel.comm import TorchComm, init_distributed
+    init_distributed(device="cpu", timeout_s=4)
+    comm = TorchComm()
+    t = torch.ones(4)
+    comm.all_reduce_sum(t, async_op=False)          # step 1: both ranks take part
+    assert float(t[0]) == world
+    if rank == 1:
+        os._exit(0)                                 # leaves between steps, nothing in flight
+    t0 = time.time()
+    try:
+        comm.all_reduce_sum(torch.ones(4), async_op=False)   # step 2: the peer is gone
+        outcome = "completed"
+    except Exception as e:  # noqa: BLE001
+        outcome = f"error:{type(e).__name__}"
+    with open(os.path.join(out, "rank0.txt"), "w") as f:
+        f.write(f"{outcome} {time.time() - t0:.1f}")
+    os._exit(0)
+
+
+@pytest.mark.timeout(120)
+def test_rank_that_leaves_is_detected_within_the_timeout(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+        assert not p.is_alive(), "a rank hung instead of reporting the lost peer"
+    outcome, secs = open(tmp_path / "rank0.txt").read().split()
+    assert outcome.startswith("error:"), outcome
+    assert float(secs) < 60
+
+
+def test_launcher_codes_and_status_word_raise():
+    from slowrun_b200.ops import _lib
+    _lib.check_rc(0, "ok")
+    with pytest.raises(RuntimeError, match="returned -5"):
+        _lib.check_rc(-5, "sr_fake_launch")
+    # the status word a kernel writes when a bounded wait runs out: [code, site, block, detail]
+    fake = torch.tensor([2, 900, 0, 3], dtype=torch.int32)
+    saved = _lib.status_buffer
+    try:
+        _lib.status_buffer = lambda device=None: fake
+        with pytest.raises(_lib.KernelStatusError, match="code=2 site=900"):
+            _lib.check_status()
+        assert int(fake[0]) == 0, "the word is cleared after it has been reported"
+        _lib.check_status()
+    finally:
+        _lib.status_buffer = saved
