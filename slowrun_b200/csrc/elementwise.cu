@@ -249,7 +249,8 @@ __global__ void mix_norm_fwd_kernel(const __nv_bfloat16* __restrict__ xp, const 
 // Backward of the pair above: g = rmsnorm_bwd(x, da) + g_res (rounded to bf16, never stored), then
 // dxp = lr*g ; dskip = lr*ws*g ; dx0 = l0*g ; dscal[0..2] += (sum g*(xp + ws*skip), sum g*x0, sum g*lr*skip).
 __global__ void norm_bwd_mix_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ da,
-                                    const __nv_bfloat16* __restrict__ g_res, const __nv_bfloat16* __restrict__ xp,
+                                    const __nv_bfloat16* __restrict__ g_res, const __nv_bfloat16* __restrict__ g_res2,
+                                    const __nv_bfloat16* __restrict__ xp,
                                     const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ skip,
                                     __nv_bfloat16* __restrict__ dxp, __nv_bfloat16* __restrict__ dx0,
                                     __nv_bfloat16* __restrict__ dskip, const float* __restrict__ lr_p,
@@ -283,6 +284,12 @@ __global__ void norm_bwd_mix_kernel(const __nv_bfloat16* __restrict__ x, const _
       load8(x + base + c, f);
       load8(da + base + c, g);
       load8(g_res + base + c, e);
+      if (g_res2 != nullptr) {   // second residual gradient (the stochastic-depth bypass), added in bf16 like a separate add would
+        float e2[8];
+        load8(g_res2 + base + c, e2);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = __bfloat162float(__float2bfloat16(e[i] + e2[i]));
+      }
       load8(xp + base + c, a);
       load8(x0 + base + c, b);
 #pragma unroll
@@ -776,14 +783,16 @@ extern "C" int sr_mix_norm_fwd(const void* xp, const void* x0, const void* skip,
   return rc();
 }
 // Backward through the first norm and the lambda mix: see norm_bwd_mix_kernel. d_lr / d_l0 / d_ws: the fp32 gradient
-// entries of the three scalars, accumulated into (d_ws is not touched without a skip input).
-extern "C" int sr_norm_bwd_mix(const void* x, const void* da, const void* g_res, const void* xp, const void* x0,
+// entries of the three scalars, accumulated into (d_ws is not touched without a skip input). g_res2: optional second
+// residual gradient, added to g_res first.
+extern "C" int sr_norm_bwd_mix(const void* x, const void* da, const void* g_res, const void* g_res2, const void* xp,
+                               const void* x0,
                                const void* skip, void* dxp, void* dx0, void* dskip, const float* lr, const float* l0,
                                const float* ws, float* d_lr, float* d_l0, float* d_ws, long rows, int D, float eps,
                                cudaStream_t s) {
   if (D % 8) return -2;
   if (rows <= 0) return 0;
   norm_bwd_mix_kernel<<<(unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
-      BF(x), BF(da), BF(g_res), BF(xp), BF(x0), BF(skip), BFM(dxp), BFM(dx0), BFM(dskip), lr, l0, ws, d_lr, d_l0, d_ws, rows, D, eps);
+      BF(x), BF(da), BF(g_res), BF(g_res2), BF(xp), BF(x0), BF(skip), BFM(dxp), BFM(dx0), BFM(dskip), lr, l0, ws, d_lr, d_l0, d_ws, rows, D, eps);
   return rc();
 }

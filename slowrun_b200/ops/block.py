@@ -262,9 +262,9 @@ class _BlockFn(Function):
             _gate_bwd(dvegate, ve_gate, a, attn.ve_gate.weight, da, H, attn.ve_gate_channels, 2.0)
             gemm(dve, x0_2, out=ve_lin.fused["grad"], cin=ve_lin.fused["grad"], a_mn=True, b_mn=True, beta=1.0)
         # ---- back through the first norm and the lambda mix
-        if g_in is not None:
-            g_mid_tot.add_(g_in)
         if not do_mix:
+            if g_in is not None:
+                g_mid_tot.add_(g_in)
             g_x = _rmsnorm_bwd(x, da, g_mid_tot, eps)
             if ve is not None:
                 dx0 = gemm(dve, ve_lin.fused["w16"], b_mn=True)
@@ -274,8 +274,8 @@ class _BlockFn(Function):
         dsk = torch.empty_like(x) if has_skip else None
         rl, xl, sw = model.resid_lambdas, model.x0_lambdas, model.skip_weights
         # the three scalar gradients are accumulated straight into the (fp32, arena-backed) .grad entries
-        _call("sr_norm_bwd_mix", [P] * 15 + [L, I, F32, P], x.data_ptr(), da.data_ptr(), g_mid_tot.data_ptr(), xp.data_ptr(),
-              x0_2.data_ptr(), sk.data_ptr() if has_skip else 0, dxp.data_ptr(), dx0.data_ptr(), _lib.ptr(dsk),
+        _call("sr_norm_bwd_mix", [P] * 16 + [L, I, F32, P], x.data_ptr(), da.data_ptr(), g_mid_tot.data_ptr(), _lib.ptr(g_in),
+              xp.data_ptr(), x0_2.data_ptr(), sk.data_ptr() if has_skip else 0, dxp.data_ptr(), dx0.data_ptr(), _lib.ptr(dsk),
               rl.data_ptr() + 4 * i, xl.data_ptr() + 4 * i, sw.data_ptr() + 4 * j if has_skip else 0,
               rl.grad.data_ptr() + 4 * i, xl.grad.data_ptr() + 4 * i, sw.grad.data_ptr() + 4 * j if has_skip else 0,
               M, C, eps, _sp())
