@@ -2,8 +2,8 @@
 
 The reference scripts run their whole training at import, so tests cut out the self-contained sections (model,
 optimizer math, loader, schedules) by their banner comments and exec them with the few globals they read. The
-source tree is looked up at baseline/_ref (the copy that travels with the repo) or /root/reference; tests that need
-it are skipped when neither exists.
+source tree is looked up at baseline/_ref (the copy that travels with the repo), then at the directory named by
+SLOWRUN_REFERENCE_DIR; tests that need it are skipped when neither exists.
 """
 import math
 import os
@@ -21,7 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def ref_root():
-    for p in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
+    for p in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("SLOWRUN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))):
         if os.path.isfile(os.path.join(p, "train.py")):
             return p
     return None

@@ -80,3 +80,16 @@ def test_launcher_codes_and_status_word_raise():
         _lib.check_status()
     finally:
         _lib.status_buffer = saved
+
+
+def test_reference_arm_reports_unavailable_without_a_gpu():
+    """`bench.py --impl reference` must print one JSON line and exit 0 even where the reference cannot run."""
+    import json
+    import subprocess
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the arm would run the reference")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
