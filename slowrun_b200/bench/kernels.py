@@ -111,13 +111,16 @@ def main():
         byts = a.m * a.v * 2 * 2.0      # one read from HBM, one write (second read is served by L2)
         out.update(shape=[a.m, a.v], ms=ms, gbs=byts / ms / 1e6, frac_of_peak=byts / ms / 1e6 / hbm)
     else:
-        from slowrun_b200.optim.muon_adamw import _NSWorkspace, newton_schulz_cuda
+        from slowrun_b200.optim.muon_adamw import _NSWorkspace, newton_schulz_cuda, newton_schulz_ref
         X = (torch.randn(a.n, a.r, a.c, device="cuda") / (a.r * a.c) ** 0.5).bfloat16()
         ws = _NSWorkspace(a.n, a.r, a.c, "cuda")
         ms = timed(lambda: newton_schulz_cuda(X.clone(), 5, ws), a.iters, not a.no_flush)
+        # the same five iterations as the reference runs them: 15 batched bf16 products through the library
+        ms_lib = timed(lambda: newton_schulz_ref(X.clone(), 5), a.iters, not a.no_flush)
         g, o = min(a.r, a.c), max(a.r, a.c)
         fl = 5 * a.n * (4.0 * g * g * o + 2.0 * g ** 3)      # full (non-symmetric) cost, the reference's bmm count
-        out.update(shape=[a.n, a.r, a.c], ms=ms, tflops_equiv=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tf)
+        out.update(shape=[a.n, a.r, a.c], ms=ms, ms_library_bmm=ms_lib, speedup_vs_library=ms_lib / ms,
+                   tflops_equiv=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tf)
     torch.cuda.synchronize()
     _lib.check_status()
     print(json.dumps(out))
