@@ -289,11 +289,19 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
       const double waves = (double)full + (rem == 0 ? 0.0 : (splittable && 2 * rem <= workers ? 0.5 : 1.0));
       return (double)tiles / (waves * workers);
     };
-    const double eff256 = eff(tm * ((N + 255) / 256) * batch, use_pair);
-    const double eff128 = eff(tm * ((N + 127) / 128) * batch, false);
+    // tiles of one matrix: all of them, or in symmetric mode only those that touch the upper triangle
+    auto tiles_of = [&](int w) {
+      const long long tn = (N + w - 1) / w;
+      if (!sym) return tm * tn;
+      long long t = 0;
+      for (long long r = 0; r < tm; ++r) t += tn - (r * BM) / w;
+      return t;
+    };
+    const double eff256 = eff(tiles_of(256) * batch, use_pair);
+    const double eff128 = eff(tiles_of(128) * batch, false);
     bn = (eff256 + 0.08 >= eff128 && N > 128) ? 256 : 128;
     // 160-wide tiles when N is a multiple of 160 and they fill the waves better than both
-    if (N % 160 == 0 && !b_mn) {
+    if (N % 160 == 0 && !b_mn && !sym) {
       const double eff160 = eff(tm * (N / 160) * batch, false);
       const double best = bn == 256 ? eff256 : eff128 * 0.92;
       if (eff160 * 0.97 > best + 0.03) bn = 160;
