@@ -5,6 +5,7 @@ that the ncu captures under profiles/ are taken on.
     python -m slowrun_b200.bench.kernels attn --b 4 --t 2048 --h 20 --window 1024 [--bwd]
     python -m slowrun_b200.bench.kernels ce --m 8192 --v 50304
     python -m slowrun_b200.bench.kernels ns --n 4 --r 2560 --c 2560
+    python -m slowrun_b200.bench.kernels lmhead_ce --m 16384 --d 2560 --v 50304 [--fp8]
 Prints one JSON line per run with the achieved rate and its fraction of the measured peaks in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1590 TFLOP/s when the file is absent).
 """
@@ -46,9 +47,102 @@ def timed(fn, iters, flush=True):
     return total / iters
 
 
+def _reference_head(a):
+    """The reference's formulation of the same op (tiny/cuda_kernels.py:338-414: three torch._scaled_mm products, its
+    NVRTC loss kernel and its Triton transposes), loaded unmodified from the reference tree. Its loss kernel is
+    compiled for sm_90 only, so the one call that compiles it is redirected to this GPU's architecture from here, the
+    file itself is untouched. Returns (callable, None) or (None, reason)."""
+    import importlib.util
+    ref = os.environ.get("SLOWRUN_REFERENCE_DIR") or os.path.join(ROOT, "baseline", "_ref")
+    path = os.path.join(ref, "tiny", "cuda_kernels.py")
+    if not os.path.isfile(path):
+        return None, f"{path} not present"
+    if a.v != 50304:
+        return None, "the reference loss kernel is compiled for a vocabulary of exactly 50304"
+    orig = torch.cuda._compile_kernel
+    cc = "".join(str(x) for x in torch.cuda.get_device_capability())
+
+    def compile_for_this_gpu(*args, **kw):
+        kw["compute_capability"] = cc
+        return orig(*args, **kw)
+
+    try:
+        torch.cuda._compile_kernel = compile_for_this_gpu
+        spec = importlib.util.spec_from_file_location("ref_tiny_cuda_kernels", path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    except Exception as e:  # noqa: BLE001
+        return None, f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:200]
+    finally:
+        torch.cuda._compile_kernel = orig
+    return mod.FusedSoftcappedCrossEntropy, None
+
+
+def lmhead_ce_bench(a, hbm, tf):
+    """lm-head + soft-capped CE, forward and backward (dx and dW), at [m tokens, d] x [v, d]: the fused kernels
+    against this library's own GEMM -> logits -> loss-kernel path and against the reference's formulation."""
+    from slowrun_b200.ops import functional as ops
+    M, d, V = a.m, a.d, a.v
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(M, d, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(V, d, device="cuda", generator=g) * 0.02).bfloat16()
+    tgt = torch.randint(0, V - 47, (M,), device="cuda", generator=g)
+    acc = torch.zeros(V, d, device="cuda", dtype=torch.float32)
+    vocab = V - 47 if V == 50304 else V
+    res = {"shape": [M, d, V], "fp8": bool(a.fp8)}
+
+    def ours(fused, fp8):
+        def step():
+            ops.set_fused_head(fused)
+            xa = x.detach().requires_grad_(not a.fwd_only)
+            loss = ops.lm_head_loss(xa, w, tgt, 15.0, vocab, grad_acc=acc, fp8=fp8)
+            if not a.fwd_only:
+                loss.backward()
+            ops.set_fused_head(True)
+        return step
+
+    ms_fused = timed(ours(True, a.fp8), a.iters, not a.no_flush)
+    res["ms_fused"] = ms_fused
+    if a.fwd_only:
+        fl = 2.0 * M * d * V
+        res.update(tflops=fl / ms_fused / 1e9, frac_of_peak=fl / ms_fused / 1e9 / tf)
+        return res
+    ms_unfused = timed(ours(False, False), a.iters, not a.no_flush)
+    fl = 3 * 2.0 * M * d * V
+    # roofline: three products at the measured bf16 rate (the fp8 forward could run at twice that), or the bytes that
+    # must move (E' written once and read twice, operands and gradients once) at the measured copy rate
+    byts = 3.0 * M * V * 2 + 2.0 * M * d * 2 * 2 + V * d * (2 + 8)
+    t_roof = max(fl / (tf * 1e9), byts / (hbm * 1e6))
+    res.update(ms_unfused=ms_unfused, speedup_vs_unfused=ms_unfused / ms_fused, tflops=fl / ms_fused / 1e9,
+               roofline_ms=t_roof, frac_of_roofline=t_roof / ms_fused)
+    ref_fn, why = _reference_head(a)
+    if ref_fn is None:
+        res["reference"] = {"unavailable": why}
+        return res
+    try:
+        wt = w.t().contiguous()                 # the tiny track stores the head as [d, V]
+        wts = torch.tensor([1.0], device="cuda")
+
+        def ref_step():
+            xa = x.detach().requires_grad_(True)
+            wa = wt.detach().requires_grad_(True)
+            losses = ref_fn.apply(xa, tgt, wts, wa, ops.FP8_X_SCALE, ops.FP8_W_SCALE, 0.75 / 448, 1.0 / M, 15.0)
+            losses.mean().backward()
+
+        ms_ref = timed(ref_step, a.iters, not a.no_flush)
+        res["reference"] = {"ms": ms_ref, "what": "tiny/cuda_kernels.py FusedSoftcappedCrossEntropy fwd+bwd (fp8 _scaled_mm x3)"}
+        res["speedup_vs_reference"] = ms_ref / ms_fused
+    except Exception as e:  # noqa: BLE001
+        res["reference"] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:200]}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "ce", "ns"])
+    ap.add_argument("what", choices=["gemm", "attn", "ce", "ns", "lmhead_ce"])
+    ap.add_argument("--d", type=int, default=2560)
+    ap.add_argument("--fp8", action="store_true", help="lmhead_ce: e4m3 forward product (per-tensor scales)")
+    ap.add_argument("--fwd-only", action="store_true", help="lmhead_ce: time only the forward (the small ncu workload)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=7680)
     ap.add_argument("--k", type=int, default=2560)
@@ -110,6 +204,8 @@ def main():
         ms = timed(fn, a.iters, not a.no_flush)
         byts = a.m * a.v * 2 * 2.0      # one read from HBM, one write (second read is served by L2)
         out.update(shape=[a.m, a.v], ms=ms, gbs=byts / ms / 1e6, frac_of_peak=byts / ms / 1e6 / hbm)
+    elif a.what == "lmhead_ce":
+        out.update(lmhead_ce_bench(a, hbm, tf))
     else:
         from slowrun_b200.optim.muon_adamw import _NSWorkspace, newton_schulz_cuda, newton_schulz_ref
         X = (torch.randn(a.n, a.r, a.c, device="cuda") / (a.r * a.c) ** 0.5).bfloat16()

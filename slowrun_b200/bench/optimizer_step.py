@@ -48,6 +48,7 @@ def main():
     model = build_model(cfg.model, dev, seed=0, world_size=W, alloc=fused.alloc if fused else None)
     groups = build_param_groups(model, cfg)
     opts = {"nccl": ShardedMuonAdamW(model, groups, TorchComm())}
+    wire = os.environ.get("SLOWRUN_WIRE_DTYPE", "bf16")
     if fused is not None:
         opts["fused"] = ShardedMuonAdamW(model, groups, fused)
         opts["fused_overlap"] = opts["fused"]
@@ -79,22 +80,26 @@ def main():
 
     res = {}
     for k, o in opts.items():
-        o.overlap = (k == "fused_overlap")
+        if k != "nccl":
+            o.mode = "fused_two_streams" if k == "fused_overlap" else "fused"
         res[k] = timed(o)
     if fused is not None:
         o = opts["fused"]
-        o.overlap = "auto"
-        for _ in range(4):
+        o.mode = "auto"                      # six measuring steps, then the fastest formulation
+        for _ in range(6):
             o.step()
-        res["fused_auto"] = timed(o)
-        o.overlap = False
+        res["auto"] = timed(o)
     _lib.check_status()
     phases = None
     if "fused" in opts:
-        opts["fused"].trace_phases = True
-        opts["fused"].step()
-        phases = {k: round(v, 3) for k, v in opts["fused"].phase_report().items()}
-        opts["fused"].trace_phases = False
+        o = opts["fused"]
+        chosen = getattr(o, "tuned", None)
+        o.mode = "fused"
+        o.trace_phases = True
+        o.step()
+        phases = {k: round(v, 3) for k, v in o.phase_report().items()}
+        o.trace_phases = False
+        o.tuned = chosen
     # traffic and FLOPs per rank
     g_bytes = sum(ga.G.numel() * 4 for ga in model.arena.groups.values())            # fp32 stacked gradients
     u_bytes = g_bytes // 2                                                            # bf16 updates

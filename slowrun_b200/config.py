@@ -49,7 +49,7 @@ class ModelConfig:
     resid_lambda_init: float = 1.0
     cproj_zero_init: bool = False
     attn_gate_adamw: bool = False     # tiny steps attn_gate with AdamW; the other tracks hand it to Muon
-    fp8_lm_head: bool = False         # e4m3 forward / e5m2 gradient lm-head GEMMs (tiny training path)
+    fp8_lm_head: bool = False         # e4m3 operands for the lm-head forward product of the training loss (tiny track)
     mlp_hidden: Optional[int] = None  # override; default 256*ceil((8d/3)/256)
     label_smoothing: float = 0.0      # unlimited
 

@@ -1,7 +1,10 @@
-// Collectives fused with their consumers, over NVLink peer memory (plain P2P loads; no multimem, no TMA on remote
-// memory). Every rank maps every peer's symmetric buffers; kernels take a small device array of W base pointers.
+// Collectives fused with their consumers, over NVLink peer memory: plain P2P loads, or multimem.ld_reduce through the
+// NVSwitch for the gradient sum when the buffer has a multicast mapping; never TMA on remote memory. Every rank maps
+// every peer's symmetric buffers; kernels take a small device array of W base pointers.
 //
-//   peer_barrier          all-ranks barrier on symmetric flag words, monotonic epochs, bounded wait -> status word
+//   peer_barrier          all-ranks barrier on symmetric flag words, monotonic epochs, bounded wait -> status word.
+//                         When a wait runs out the status word becomes non-zero; every consumer kernel below reads
+//                         it first and returns without writing, so a step whose barrier failed changes no state.
 //   muon_pre_multi        gradient reduce-scatter fused with the Muon prologue: the owner of a matrix reads that
 //                         matrix's gradient rows from all W ranks, sums and scales them, updates momentum, applies
 //                         Nesterov + row normalisation and writes the bf16 Newton-Schulz input directly
@@ -34,7 +37,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
 // flags: on every rank an array uint32[W]; slot s of rank d is written only by rank s.
-__global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_t epoch, int* status) {
+__global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_t epoch, int* status,
+                                    unsigned long long limit_ns) {
   const int t = threadIdx.x;
   if (t >= world) return;
   __threadfence_system();
@@ -47,7 +51,7 @@ __global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (static_cast<int32_t>(v - epoch) >= 0) break;
-    if ((++it & 255u) == 0u && globaltimer_ns() - t0 > kWaitLimitNs) {
+    if ((++it & 255u) == 0u && globaltimer_ns() - t0 > limit_ns) {
       report_error(status, SR_ERR_PEER_TIMEOUT, 900, t);
       break;
     }
@@ -78,7 +82,8 @@ __device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
 __global__ void __launch_bounds__(kThreads, 2)
 muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int rank, long base, float* __restrict__ Mom,
                       __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
-                      float gscale) {
+                      float gscale, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;   // a barrier gave up: touch nothing
   const int lane = threadIdx.x & 31;
   // at most one CTA per SM (the launcher caps the grid): the kernel is meant to share the SMs with the Newton-Schulz
   // GEMMs of the neighbouring shape group, which need one CTA's worth of registers and shared memory on every SM
@@ -157,7 +162,8 @@ muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int r
 }
 
 __global__ void fnorm_scale_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__ sumsq, long per_mat,
-                                   long total) {
+                                   long total, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 2; i < total; i += (long)gridDim.x * blockDim.x * 2) {
     const float s = 1.f / (1.02f * sqrtf(sumsq[i / per_mat]) + 1e-6f);
     const float2 v = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(X + i));
@@ -167,7 +173,9 @@ __global__ void fnorm_scale_kernel(__nv_bfloat16* __restrict__ X, const float* _
 
 // U_r points at rank r's update chunk [chunk_elems]; element i of the stack belongs to rank i / chunk_elems.
 __global__ void muon_apply_multi_kernel(float* __restrict__ P, PtrTable U, long chunk_elems,
-                                        __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total) {
+                                        __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total,
+                                        const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += (long)gridDim.x * blockDim.x * 4) {
     const long owner = i / chunk_elems;
     const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(U.p[owner]) + (i - owner * chunk_elems);
@@ -214,7 +222,9 @@ __device__ __forceinline__ void apply8(float* __restrict__ P, const uint4& raw, 
   }
 }
 __global__ void muon_apply_multi8_kernel(float* __restrict__ P, PtrTable U, long chunk_elems,
-                                         __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total) {
+                                         __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total,
+                                         const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   const long stride = (long)gridDim.x * blockDim.x * 8;
   for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < total; i += 2 * stride) {
     const long i2 = i + stride;
@@ -232,7 +242,9 @@ __global__ void muon_apply_multi8_kernel(float* __restrict__ P, PtrTable U, long
 }
 
 template <bool BF16>
-__global__ void reduce_multi_kernel(PtrTable src, int world, long offset, float* __restrict__ out, long n) {
+__global__ void reduce_multi_kernel(PtrTable src, int world, long offset, float* __restrict__ out, long n,
+                                    const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long)gridDim.x * blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i + 3 < n) {
@@ -261,7 +273,8 @@ __global__ void reduce_multi_kernel(PtrTable src, int world, long offset, float*
 }
 
 // bufs[r] = rank r's replica (same layout everywhere); copy slice s (bytes [s*slice, (s+1)*slice)) from rank s for all s != rank
-__global__ void gather_multi_kernel(PtrTable bufs, int world, int rank, long slice_bytes) {
+__global__ void gather_multi_kernel(PtrTable bufs, int world, int rank, long slice_bytes, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   const long vecs = slice_bytes / 16;
   const int s = blockIdx.y;
   if (s == rank) return;
@@ -270,9 +283,18 @@ __global__ void gather_multi_kernel(PtrTable bufs, int world, int rank, long sli
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (long)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
 inline int grid_for(long n, int per_block) {
   long b = (n + per_block - 1) / per_block;
-  const long cap = 148L * 8;
+  const long cap = (long)sm_count() * 8;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
@@ -286,11 +308,14 @@ inline bool fill(PtrTable& t, const unsigned long long* ptrs, int world) {
 }  // namespace
 
 // `ptrs` arguments are HOST arrays of `world` device addresses (one per rank, this rank's own included).
+// `status` arguments are the device int[4] status word (sm100_common.cuh); consumer kernels return at once when it is
+// non-zero. `limit_ns`: how long the barrier waits for each peer before it records SR_ERR_PEER_TIMEOUT (site 900,
+// detail = the peer) and returns; 0 selects the library default.
 extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, int world, unsigned int epoch, int* status,
-                               cudaStream_t s) {
+                               unsigned long long limit_ns, cudaStream_t s) {
   PtrTable t;
   if (!fill(t, flag_ptrs, world)) return -2;
-  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, epoch, status);
+  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, epoch, status, limit_ns ? limit_ns : kWaitLimitNs);
   return rc();
 }
 
@@ -301,7 +326,7 @@ extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, in
 extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* mc, int world, int rank, long base,
                                  float* Mom, void* X,
                                  float* sumsq, int n, int r, int c, float mu, float gscale, int shared_sms,
-                                 cudaStream_t s) {
+                                 const int* status, cudaStream_t s) {
   if (n <= 0) return 0;
   if (c % 4 || rank < 0 || rank >= world) return -2;
   PtrTable t;
@@ -309,47 +334,48 @@ extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* 
   const long rows = (long)n * r;
   cudaMemsetAsync(sumsq, 0, sizeof(float) * n, s);
   long pull_grid = (rows + kWarps - 1) / kWarps;
-  const long cap = shared_sms ? 148 : 296;
+  const long cap = shared_sms ? sm_count() : 2L * sm_count();
   if (pull_grid > cap) pull_grid = cap;
   muon_pre_multi_kernel<<<(unsigned)pull_grid, kThreads, 0, s>>>(
-      t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
+      t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, status);
   const long total = rows * c;
-  fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total);
+  fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total, status);
   return rc();
 }
 
 extern "C" int sr_muon_apply_multi(float* P, const unsigned long long* u_ptrs, int world, long chunk_elems, void* shadow,
-                                   long total, float lr_b, float lrwd_b, cudaStream_t s) {
+                                   long total, float lr_b, float lrwd_b, const int* status, cudaStream_t s) {
   if (total <= 0) return 0;
   if (total % 4 || chunk_elems % 4) return -2;
   PtrTable t;
   if (!fill(t, u_ptrs, world)) return -2;
   if (total % 8 == 0 && chunk_elems % 8 == 0)
-    muon_apply_multi8_kernel<<<grid_for(total / 16, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
+    muon_apply_multi8_kernel<<<grid_for(total / 16, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total, status);
   else
-    muon_apply_multi_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
+    muon_apply_multi_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total, status);
   return rc();
 }
 
 extern "C" int sr_reduce_multi(const unsigned long long* src_ptrs, int world, long offset, float* out, long n,
-                               int src_bf16, cudaStream_t s) {
+                               int src_bf16, const int* status, cudaStream_t s) {
   if (n <= 0) return 0;
   if (offset % 4) return -2;
   PtrTable t;
   if (!fill(t, src_ptrs, world)) return -2;
   if (src_bf16)
-    reduce_multi_kernel<true><<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(t, world, offset, out, n);
+    reduce_multi_kernel<true><<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(t, world, offset, out, n, status);
   else
-    reduce_multi_kernel<false><<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(t, world, offset, out, n);
+    reduce_multi_kernel<false><<<grid_for((n + 3) / 4, kThreads), kThreads, 0, s>>>(t, world, offset, out, n, status);
   return rc();
 }
 
-extern "C" int sr_gather_multi(const unsigned long long* buf_ptrs, int world, int rank, long slice_bytes, cudaStream_t s) {
+extern "C" int sr_gather_multi(const unsigned long long* buf_ptrs, int world, int rank, long slice_bytes,
+                               const int* status, cudaStream_t s) {
   if (slice_bytes <= 0) return 0;
   if (slice_bytes % 16) return -2;
   PtrTable t;
   if (!fill(t, buf_ptrs, world)) return -2;
   dim3 grid(grid_for(slice_bytes / 16, kThreads) / 2 + 1, world);
-  gather_multi_kernel<<<grid, kThreads, 0, s>>>(t, world, rank, slice_bytes);
+  gather_multi_kernel<<<grid, kThreads, 0, s>>>(t, world, rank, slice_bytes, status);
   return rc();
 }

@@ -649,9 +649,18 @@ __global__ void acc_bf16_into_f32_kernel(float* __restrict__ acc, const __nv_bfl
   }
 }
 
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
 inline int grid_for(long n, int per_block) {
   long b = (n + per_block - 1) / per_block;
-  const long cap = 148L * 16;
+  const long cap = (long)sm_count() * 16;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }

@@ -401,7 +401,10 @@ extern "C" int sr_flash_attn_bwd_ex(const void* dO, const void* q, const void* k
   if (!(flags & 2)) {
     const long n4 = rows * D / 4;
     long blocks = (n4 + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (blocks > (long)sms * 16) blocks = (long)sms * 16;
     attn_dq_convert_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n4);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

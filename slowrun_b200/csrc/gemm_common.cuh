@@ -30,6 +30,18 @@ struct GemmParams {
   int splitk;              // fp32 accumulate-into output: CTAs own equal shares of (tile, k-block) units and add their
                            // partial tiles with vector reductions, so the last wave is never partly idle
 
+  const float* row_scale;  // optional fp32 [batch, M]: output row r is scaled by row_scale[r] (before beta * Cin)
+  int a_fmt, b_fmt;        // fp8 operands (kind::f8f6f4): 0 = e4m3, 1 = e5m2; ignored for bf16
+
+  // Soft-capped cross-entropy epilogue (lmhead_ce.cu); unused by the plain GEMM.
+  struct Ce {
+    const long* targets;   // int64 [M]; row r is scored against targets[r + k], k < n_predict (flattened index)
+    float* partials;       // fp32 [tiles_n, M]: per-tile row sums of exp(z - cap)
+    float* ztgt;           // fp32 [M, 4]: soft-capped logit at each of the row's targets
+    int n_predict, V;      // targets per row (<= 4); valid vocabulary (columns >= V do not enter the sum)
+    float cap, inv_cap;
+  } ce;
+
   int* status;
 };
 
@@ -271,6 +283,23 @@ int encode_bf16_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
   cuuint32_t box[3] = {box_inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+// Same for 1-byte (fp8) elements: {inner, rows, batch} with the leading dimension given in elements (= bytes).
+int encode_u8_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t ld,
+                  uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((ld % 16) != 0 || (reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return -2;
+  if (batch > 1 && (batch_stride % 16) != 0) return -2;
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t strides[2] = {ld, (batch > 1 ? batch_stride : rows * ld)};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;

@@ -173,10 +173,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       ok = mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, 300);
       ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the .sync.aligned TMEM loads
       if (!ok) break;
-      const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
+      float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
       tc_fence_after();
       const int r = mi * BM + q * 32 + lane;
       const bool row_ok = r < p.M;
+      if (p.row_scale != nullptr && row_ok) alpha *= __ldg(p.row_scale + (size_t)b * p.M + r);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * C_::kAccStride);
       uint8_t* cbase = reinterpret_cast<uint8_t*>(p.C) + (size_t)b * p.strideC * (p.c_fp32 ? 4 : 2);
       const uint8_t* cinbase =
@@ -245,8 +246,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int max_
 extern "C" int sr_gemm_bf16_pair(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                                  long long lda, long long ldb, long long ldc, long long ldcin, long long strideA,
                                  long long strideB, long long strideC, long long strideCin, int a_mn, int b_mn,
-                                 int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr, int splitk,
-                                 int bn, int max_ctas, int* status, cudaStream_t stream);
+                                 int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr,
+                                 const float* row_scale, int splitk, int bn, int max_ctas, int* status,
+                                 cudaStream_t stream);
 
 static int g_pair_mode = 1;
 // 1 (default): eligible problems run on the CTA-pair kernel (gemm_tcgen05_pair.cu); 0: single-CTA kernel only.
@@ -256,14 +258,15 @@ extern "C" void sr_gemm_set_pair_mode(int on) { g_pair_mode = on; }
 //   a_mn / b_mn : 0 = operand stored [rows, K] (K contiguous), 1 = stored [K, rows] (rows contiguous)
 //   lda / ldb   : leading dimension (elements) of the stored 2-D array; stride* : per-batch element stride
 //   alpha_ptr   : optional device fp32 scalar; the product is scaled by alpha * (*alpha_ptr)
+//   row_scale   : optional device fp32 [batch, M]; row r of the product is also scaled by row_scale[r]
 //   bn          : N tile (128 or 256), 0 = choose
 //   status      : device int[4]; written only when a bounded wait ran out (see sm100_common.cuh)
 // Returns 0 on successful launch, negative on bad arguments / launch failure.
 extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                             long long lda, long long ldb, long long ldc, long long ldcin, long long strideA,
                             long long strideB, long long strideC, long long strideCin, int a_mn, int b_mn,
-                            int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr, int sym,
-                            int bn, int max_ctas, int* status, cudaStream_t stream) {
+                            int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr,
+                            const float* row_scale, int sym, int bn, int max_ctas, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if (sym && M != N) return -6;
   GemmParams p{};
@@ -271,7 +274,7 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.C = C; p.ldc = ldc; p.strideC = strideC; p.c_fp32 = c_fp32;
   p.Cin = Cin; p.ldcin = ldcin; p.strideCin = strideCin; p.cin_fp32 = cin_fp32;
-  p.alpha = alpha; p.beta = beta; p.alpha_ptr = alpha_ptr; p.sym = sym; p.status = status;
+  p.alpha = alpha; p.beta = beta; p.alpha_ptr = alpha_ptr; p.row_scale = row_scale; p.sym = sym; p.status = status;
   // accumulate-into fp32 output (weight gradients): balance the k-loop over all SMs instead of whole tiles
   p.splitk = (c_fp32 && Cin == C && beta == 1.0f && !sym && ldcin == ldc && strideCin == strideC) ? 1 : 0;
   if (bn < 0) { p.splitk = 0; bn = -bn; }   // negative bn: caller forces the plain tile schedule
@@ -310,8 +313,8 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   if (bn != 128 && bn != 160 && bn != 256) return -7;
   if (use_pair && !(bn == 160 && b_mn))
     return sr_gemm_bf16_pair(A, B, C, Cin, M, N, K, batch, lda, ldb, ldc, ldcin, strideA, strideB, strideC, strideCin,
-                             a_mn, b_mn, c_fp32, cin_fp32, alpha, beta, alpha_ptr, p.splitk, bn, max_ctas, status,
-                             stream);
+                             a_mn, b_mn, c_fp32, cin_fp32, alpha, beta, alpha_ptr, row_scale, p.splitk, bn, max_ctas,
+                             status, stream);
   CUtensorMap ma, mb;
   int rc;
   if (!a_mn) rc = encode_bf16_map(&ma, A, K, M, batch, lda, strideA, BK, BM);

@@ -16,6 +16,8 @@
  *     the internal array could not be obtained, -10 unsupported device ordinal.
  *   - The first call on a device performs a one-time lookup of the array's device address; issue it before any
  *     stream capture begins on that device.
+ *   - The stream must belong to the device that is current when the function is called; the first call for a device
+ *     must not race with another thread's first call for the same device.
  *   - Calls share the internal array. Calls whose kernels may overlap on the GPU must be ordered by the caller
  *     (same stream, or events); unordered concurrent calls race.
  *   - The caller still owns and passes X (bf16, read), S (fp32 state, updated) and U (bf16, written).

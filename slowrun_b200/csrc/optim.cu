@@ -225,9 +225,18 @@ __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bflo
   }
 }
 
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
 inline int grid_for(long n, int per_block) {
   long b = (n + per_block - 1) / per_block;
-  const long cap = 148L * 16;
+  const long cap = (long)sm_count() * 16;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
@@ -314,6 +323,8 @@ extern "C" int sr_cast_f32_to_bf16(const float* src, void* dst, long n, cudaStre
 //  * All calls share the one array and it keeps whatever the last call left in it. What has to start at zero (the
 //    column sums) is cleared on the caller's stream before use. Two calls whose kernels overlap on the GPU (different
 //    streams, no ordering between them) race on the array: order them.
+//  * The stream must belong to the device that is current at the call, and two threads must not race on the first
+//    call for the same device (later calls only read the cached address).
 //  * No cudaMalloc, cudaFree or allocating library routine is called on any path of this function.
 constexpr long kNoAllocMaxElems = 1L << 18;
 static __device__ __align__(256) float g_noalloc_scratch[2 * kNoAllocMaxElems];
@@ -343,21 +354,7 @@ extern "C" int sr_muon_post_noalloc(const void* X, float* S, void* U, int n, int
   }
   float* vmean = g_noalloc_ptr[dev];
   float* fs = vmean + kNoAllocMaxElems;
-  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(X);
-  if (row_mode) {
-    const long rows = (long)n * r;
-    muon_rowstat_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(x, vmean, rows, c);
-  } else {
-    if (cudaMemsetAsync(vmean, 0, sizeof(float) * (long)n * c, s) != cudaSuccess) return -5;
-    int slices = r / 128;
-    if (slices < 1) slices = 1;
-    if (slices > 32) slices = 32;
-    dim3 grid((c / 2 + 127) / 128, n, slices);
-    muon_colstat_kernel<<<grid, 128, 0, s>>>(x, vmean, n, r, c);
-  }
-  const int n_red = row_mode ? c : r;
-  muon_finalize_kernel<<<n, kThreads, 0, s>>>(vmean, S, fs, len, n_red, beta2);
-  const long total = (long)n * r * c;
-  muon_scale_update_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(x, fs, reinterpret_cast<__nv_bfloat16*>(U), r, c, row_mode, total);
-  return rc();
+  // Same launch sequence as the ordinary entry point, on the library's own work arrays (it clears what must start at
+  // zero on the caller's stream and allocates nothing).
+  return sr_muon_post(X, vmean, S, fs, U, n, r, c, beta2, s);
 }

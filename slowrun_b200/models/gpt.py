@@ -528,7 +528,8 @@ class GPT(nn.Module):
             return (loss + self.mtp_weight * mtp_loss if mtp_loss is not None else loss), {"lm_loss": loss}
         if c.fused_mtp and self.training and mtp_weights is not None:
             # tiny: one head scored against shifted targets over the whole padded vocabulary (tiny/train.py:682-696)
-            return ops.lm_head_loss(x, w, targets, c.logit_cap, self.padded_vocab, acc, w_t, weights=mtp_weights)
+            return ops.lm_head_loss(x, w, targets, c.logit_cap, self.padded_vocab, acc, w_t, weights=mtp_weights,
+                                    fp8=c.fp8_lm_head)
         if loss_reduction != "mean":
             return ops.lm_head_rows(x, w, targets, c.logit_cap, c.vocab_size, w_t).view(targets.shape)
         lm_loss = ops.lm_head_loss(x, w, targets, c.logit_cap, c.vocab_size, acc, w_t)

@@ -487,13 +487,108 @@ class _LMHeadLossFn(Function):
         return dx, dw, None, None, None, None, None, None, None, None
 
 
-def lm_head_loss(x, w, targets, cap, vocab, grad_acc=None, w_t=False, weights=None):
+# ---- fused head: the GEMM epilogue does the softcap, the row sums and the unnormalised gradient (csrc/lmhead_ce.cu)
+FP8_X_SCALE = 100.0 / 448.0     # static per-tensor scales of the reference's fp8 head (tiny/train.py:187-189)
+FP8_W_SCALE = 1.6 / 448.0
+_head = {"fused": True}
+
+
+def set_fused_head(on: bool) -> None:
+    """A/B switch: True (default) = lm-head GEMM with the cross-entropy epilogue, False = GEMM -> bf16 logits ->
+    separate loss kernel."""
+    _head["fused"] = bool(on)
+
+
+_HEAD_ARGS = [c_void_p, c_void_p, c_void_p, _lib.c_ll, c_int, c_int, c_int, _lib.c_ll, _lib.c_ll, c_int, c_int, c_float,
+              c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_void_p, _lib.c_ll, c_void_p, c_int, c_void_p, c_void_p]
+
+
+def _fused_head_ok(x2, w, w_t, cap, fp8):
+    K = x2.size(-1)
+    N = w.size(1) if w_t else w.size(0)
+    return (_head["fused"] and cap > 0 and N % 32 == 0 and K % (16 if fp8 else 8) == 0 and w.dtype == torch.bfloat16
+            and w.stride(-1) == 1 and x2.dtype == torch.bfloat16)
+
+
+def _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over_rows, fp8, want_grad):
+    """Runs sr_lmhead_ce_fwd. Returns (loss scalar, loss_rows, E', rscale, Xs); the last three are None when
+    `want_grad` is False (evaluation: nothing of size [tokens, vocab] is allocated at all)."""
+    M, K = x2.shape
+    N = w.size(1) if w_t else w.size(0)
+    dev = x2.device
+    tiles_n = (N + 255) // 256
+    partials = torch.empty((tiles_n, M), dtype=torch.float32, device=dev)
+    ztgt = torch.empty((M, 4), dtype=torch.float32, device=dev)
+    loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
+    scal = torch.empty(2, dtype=torch.float32, device=dev)      # [0] = scale, [1] = loss
+    E = rscale = Xs = None
+    if want_grad:
+        E = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        rscale = torch.empty(M, dtype=torch.float32, device=dev)
+        Xs = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    if fp8:
+        from .gemm import quantize_fp8
+        xa = quantize_fp8(x2, FP8_X_SCALE)
+        wa = quantize_fp8(w, FP8_W_SCALE, transpose=w_t)        # always [N, K]
+        alpha, b_mn, lda, ldb = FP8_X_SCALE * FP8_W_SCALE, 0, xa.stride(0), wa.stride(0)
+    else:
+        xa, wa, alpha, b_mn, lda, ldb = x2, w, 1.0, int(w_t), x2.stride(0), w.stride(0)
+    _call("sr_lmhead_ce_fwd", _HEAD_ARGS, xa.data_ptr(), wa.data_ptr(), _lib.ptr(E), N, M, N, K, lda, ldb, b_mn, int(fp8),
+          alpha, t.data_ptr(), _lib.ptr(weights), n_predict, vocab, cap, int(mean_over_rows), scal.data_ptr(),
+          partials.data_ptr(), ztgt.data_ptr(), loss_rows.data_ptr(), scal.data_ptr() + 4, _lib.ptr(rscale),
+          x2.data_ptr(), x2.stride(0), _lib.ptr(Xs), 0, _lib.status_buffer(dev).data_ptr(), _lib.stream_ptr())
+    return scal[1], loss_rows, E, rscale, Xs
+
+
+class _FusedLMHeadLossFn(Function):
+    """lm-head + soft-capped CE on the fused kernel: forward leaves E' (bf16, the logit gradient up to the per-row
+    factor `rscale`) and the pre-scaled activations; backward is dx = diag(rscale) E' W (row factor in the GEMM
+    epilogue) and dW += E'^T (rscale * x), both scaled by the upstream scalar on the device."""
+
+    @staticmethod
+    def forward(ctx, x, w, grad_acc, w_t, targets, cap, vocab, weights, n_predict, mean_over_rows, fp8):
+        K = x.size(-1)
+        x2 = _c(x.reshape(-1, K))
+        t = _c(targets.reshape(-1))
+        loss, _, E, rscale, Xs = _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over_rows, fp8, True)
+        ctx.save_for_backward(w, E, rscale, Xs)
+        ctx.grad_acc, ctx.w_t, ctx.xshape = grad_acc, w_t, x.shape
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        w, E, rscale, Xs = ctx.saved_tensors
+        w_t = ctx.w_t
+        g = _c(g.float())
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(E, w, b_mn=not w_t, alpha_t=g, row_scale=rscale).view(ctx.xshape)
+        acc = ctx.grad_acc
+        dw = None
+        if acc is not None:
+            if w_t:
+                gemm(Xs, E, out=acc, cin=acc, a_mn=True, b_mn=True, beta=1.0, alpha_t=g)
+            else:
+                gemm(E, Xs, out=acc, cin=acc, a_mn=True, b_mn=True, beta=1.0, alpha_t=g)
+        elif ctx.needs_input_grad[1]:
+            dw = (gemm(Xs, E, a_mn=True, b_mn=True, alpha_t=g) if w_t else gemm(E, Xs, a_mn=True, b_mn=True, alpha_t=g))
+        return (dx, dw) + (None,) * 9
+
+
+def lm_head_loss(x, w, targets, cap, vocab, grad_acc=None, w_t=False, weights=None, fp8=False):
     """Mean soft-capped CE of (x @ W^T)[..., :vocab] against targets (ignore_index -1).
     With `weights` (fp32 tensor of k entries) row i is scored against targets[i..i+k-1] of the flattened batch and the
-    mean runs over all rows (the tiny track's shared-head multi-token loss, tiny/train.py:682-696)."""
+    mean runs over all rows (the tiny track's shared-head multi-token loss, tiny/train.py:682-696).
+    `fp8`: forward product on e4m3 operands with the reference's static per-tensor scales (tiny/cuda_kernels.py:340-352);
+    the two backward products stay in bf16."""
     if x.is_cuda:
         npred = 1 if weights is None else int(weights.numel())
         wts = None if weights is None else _c(weights.float())
+        x2 = x.reshape(-1, x.size(-1))
+        if _fused_head_ok(x2, w, w_t, float(cap), fp8):
+            return _FusedLMHeadLossFn.apply(x, w, grad_acc, w_t, targets, float(cap), int(vocab), wts, npred,
+                                            weights is not None, bool(fp8))
         return _LMHeadLossFn.apply(x, w, grad_acc, w_t, targets, float(cap), int(vocab), wts, npred, weights is not None)
     logits = (x @ w.to(x.dtype)) if w_t else F.linear(x, w.to(x.dtype))
     return softcap_ce_ref(logits.reshape(-1, logits.size(-1)), targets.reshape(-1), cap, vocab, weights)
@@ -504,8 +599,10 @@ def lm_head_rows(x, w, targets, cap, vocab, w_t=False):
     if x.is_cuda:
         K = x.size(-1)
         x2 = _c(x.reshape(-1, K))
-        logits = gemm(x2, w, b_mn=w_t)
         t = _c(targets.reshape(-1))
+        if _fused_head_ok(x2, w, w_t, float(cap), False):
+            return _fused_head_forward(x2, w, w_t, t, float(cap), int(vocab), None, 1, False, False, False)[1]
+        logits = gemm(x2, w, b_mn=w_t)
         loss_rows = torch.empty(x2.size(0), dtype=torch.float32, device=x.device)
         _call("sr_softcap_ce", _CE_ARGS, logits.data_ptr(), t.data_ptr(), loss_rows.data_ptr(), 0, 1, 0, x2.size(0),
               logits.size(1), vocab, logits.stride(0), float(cap), 0, _lib.stream_ptr())

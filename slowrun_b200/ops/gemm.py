@@ -19,7 +19,8 @@ _ARGTYPES = [
     _lib.c_ll, _lib.c_ll, _lib.c_ll, _lib.c_ll,  # lda ldb ldc ldcin
     _lib.c_ll, _lib.c_ll, _lib.c_ll, _lib.c_ll,  # strides
     _lib.c_int, _lib.c_int, _lib.c_int, _lib.c_int,  # a_mn b_mn c_fp32 cin_fp32
-    _lib.c_float, _lib.c_float, _lib.c_void_p, _lib.c_int, _lib.c_int, _lib.c_int,  # alpha beta alpha_ptr sym bn max_ctas
+    _lib.c_float, _lib.c_float, _lib.c_void_p, _lib.c_void_p,  # alpha beta alpha_ptr row_scale
+    _lib.c_int, _lib.c_int, _lib.c_int,  # sym bn max_ctas
     _lib.c_void_p, _lib.c_void_p,  # status stream
 ]
 
@@ -39,7 +40,8 @@ def _check_operand(t: torch.Tensor, name: str):
         raise ValueError(f"{name} must have a contiguous last dimension")
 
 
-def gemm_reference(a, b, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, out_dtype=torch.bfloat16):
+def gemm_reference(a, b, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, out_dtype=torch.bfloat16,
+                   row_scale=None):
     """fp32 PyTorch statement of `gemm` (the numerics oracle; runs on CPU or GPU)."""
     A = _as3d(a).float()
     B = _as3d(b).float()
@@ -48,6 +50,8 @@ def gemm_reference(a, b, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.
     if b_mn:
         B = B.transpose(-1, -2)
     out = alpha * torch.matmul(A, B.transpose(-1, -2))
+    if row_scale is not None:
+        out = out * row_scale.float().reshape(out.shape[0], -1, 1)
     if cin is not None:
         out = out + beta * _as3d(cin).float()
     out = out.to(out_dtype)
@@ -55,12 +59,16 @@ def gemm_reference(a, b, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.
 
 
 def gemm(a, b, out=None, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.0, alpha_t=None, sym=False,
-         out_dtype=torch.bfloat16, bn=0, max_ctas=0):
+         out_dtype=torch.bfloat16, bn=0, max_ctas=0, row_scale=None):
     """Launch the tcgen05 GEMM on the current stream. See the module docstring for operand conventions.
 
-    `alpha_t` is an optional 0-dim fp32 CUDA tensor multiplied into alpha on the device (no host sync)."""
+    `alpha_t` is an optional 0-dim fp32 CUDA tensor multiplied into alpha on the device (no host sync);
+    `row_scale` an optional fp32 CUDA tensor [batch, M] (or [M]) that scales the rows of the product."""
     if alpha_t is not None and (alpha_t.dtype != torch.float32 or not alpha_t.is_cuda):
         raise TypeError("alpha_t must be a float32 CUDA tensor")
+    if row_scale is not None and (row_scale.dtype != torch.float32 or not row_scale.is_cuda
+                                  or not row_scale.is_contiguous()):
+        raise TypeError("row_scale must be a contiguous float32 CUDA tensor")
     _check_operand(a, "a")
     _check_operand(b, "b")
     A, B = _as3d(a), _as3d(b)
@@ -95,9 +103,62 @@ def gemm(a, b, out=None, cin=None, *, a_mn=False, b_mn=False, alpha=1.0, beta=0.
            A.stride(0), B.stride(0), O.stride(0), CI.stride(0) if CI is not None else 0,
            int(a_mn), int(b_mn), int(O.dtype == torch.float32),
            int(CI is not None and CI.dtype == torch.float32),
-           float(alpha), float(beta), _lib.ptr(alpha_t), int(sym), int(bn), int(max_ctas),
+           float(alpha), float(beta), _lib.ptr(alpha_t), _lib.ptr(row_scale), int(sym), int(bn), int(max_ctas),
            _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "sr_gemm_bf16")
+    return out
+
+
+FP8_DTYPES = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
+_ARGTYPES_FP8 = _ARGTYPES[:16] + [_lib.c_int] * 4 + [_lib.c_float, _lib.c_float, _lib.c_void_p, _lib.c_void_p,
+                                                     _lib.c_int, _lib.c_int, _lib.c_void_p, _lib.c_void_p]
+
+
+def quantize_fp8(x: torch.Tensor, scale: float, transpose: bool = False, dtype=torch.float8_e4m3fn) -> torch.Tensor:
+    """fp8(x / scale) of a bf16 matrix [R, C] (saturating); `transpose` returns the [C, R] layout. Per-tensor static
+    scales as in the reference's fp8 head (tiny/cuda_kernels.py:340-343)."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise TypeError("quantize_fp8 expects a 2-D bf16 tensor with a contiguous last dimension")
+    R, C = x.shape
+    out = torch.empty((C, R) if transpose else (R, C), dtype=dtype, device=x.device)
+    if not x.is_cuda:
+        src = (x.float() / scale).clamp(-torch.finfo(dtype).max, torch.finfo(dtype).max).to(dtype)
+        out.copy_(src.t() if transpose else src)
+        return out
+    rc = _lib.fn("sr_quant_fp8", [_lib.c_void_p, _lib.c_void_p, ctypes.c_long, _lib.c_int, ctypes.c_long, ctypes.c_long,
+                                  _lib.c_float, _lib.c_int, _lib.c_int, _lib.c_void_p])(
+        x.data_ptr(), out.data_ptr(), R, C, x.stride(0), out.stride(0), float(scale), int(transpose),
+        FP8_DTYPES[dtype], _lib.stream_ptr())
+    _lib.check_rc(rc, "sr_quant_fp8")
+    return out
+
+
+def gemm_fp8(a, b, out=None, cin=None, *, alpha=1.0, beta=0.0, alpha_t=None, row_scale=None, out_dtype=torch.bfloat16,
+             bn=0, max_ctas=0):
+    """alpha * a @ b.T with fp8 operands a [.., M, K], b [.., N, K] (K contiguous, K % 16 == 0) on the CTA-pair
+    tcgen05 kernel with kind::f8f6f4 MMAs and fp32 accumulation. The scales of a per-tensor quantisation go into
+    alpha. The reference calls torch._scaled_mm (cuBLASLt) for these products (tiny/cuda_kernels.py:345-352)."""
+    if a.dtype not in FP8_DTYPES or b.dtype not in FP8_DTYPES:
+        raise TypeError("gemm_fp8 operands must be float8_e4m3fn or float8_e5m2")
+    A, B = _as3d(a), _as3d(b)
+    batch, M, K = A.shape
+    N = B.shape[1]
+    if B.shape[0] != batch or B.shape[2] != K or A.stride(-1) != 1 or B.stride(-1) != 1:
+        raise ValueError(f"shape mismatch: {tuple(a.shape)} vs {tuple(b.shape)}")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+        if a.dim() == 2:
+            out = out[0]
+    O = _as3d(out)
+    CI = _as3d(cin) if cin is not None else None
+    f = _lib.fn("sr_gemm_fp8_pair", _ARGTYPES_FP8)
+    rc = f(A.data_ptr(), B.data_ptr(), O.data_ptr(), _lib.ptr(CI), M, N, K, batch,
+           A.stride(1), B.stride(1), O.stride(1), CI.stride(1) if CI is not None else 0,
+           A.stride(0), B.stride(0), O.stride(0), CI.stride(0) if CI is not None else 0,
+           FP8_DTYPES[a.dtype], FP8_DTYPES[b.dtype], int(O.dtype == torch.float32),
+           int(CI is not None and CI.dtype == torch.float32), float(alpha), float(beta), _lib.ptr(alpha_t),
+           _lib.ptr(row_scale), int(bn), int(max_ctas), _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "sr_gemm_fp8_pair")
     return out
 
 

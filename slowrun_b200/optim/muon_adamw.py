@@ -192,6 +192,11 @@ class ShardedMuonAdamW:
     def step(self):
         if self.fused:
             return self._step_fused_tuned()
+        return self._step_library()
+
+    @torch.no_grad()
+    def _step_library(self):
+        """The torch.distributed (NCCL / Gloo) formulation: reduce-scatter, owner update, all-gather of bf16 updates."""
         self.step_count += 1
         W, rank, comm = self.world, self.rank, self.comm
         gscale = 1.0 / W
@@ -202,6 +207,10 @@ class ShardedMuonAdamW:
             if g["kind"] == "muon":
                 st = self.state[g["name"]]
                 ga = st["arena"]
+                if W > 1 and st["grad_chunk"] is None:      # peer-memory job that runs this path (mode measurement)
+                    r_, c_ = ga.shape
+                    st["grad_chunk"] = torch.empty((ga.chunk, r_, c_), dtype=torch.float32, device=self.device)
+                    st["U_all"] = torch.empty((ga.n_pad, r_, c_), dtype=torch.bfloat16, device=self.device)
                 st["h"] = comm.reduce_scatter_sum(st["grad_chunk"], ga.G) if W > 1 else None
             else:
                 for p in g["params"]:
@@ -244,25 +253,38 @@ class ShardedMuonAdamW:
             out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
         return out
 
-    # ------------------------------------------------------------------ one-stream or two-stream order, measured
+    # ------------------------------------------------------------------ which formulation of the step: measured
+    TUNE_MODES = ("fused", "fused_two_streams", "library")
+
+    def _run_mode(self, mode):
+        if mode == "library":
+            return self._step_library()
+        self.overlap = mode == "fused_two_streams"
+        return self._step_fused()
+
     def _step_fused_tuned(self):
-        """`self.overlap` is True / False, or "auto" (default): steps 2 and 4 of the run are timed on the device in the
-        back-to-back and the two-stream order (steps 1 and 3 warm them up), the maximum over ranks is compared and
-        the faster order is kept. Both orders issue the same barriers in the same sequence and compute the same
-        update, so ranks may even disagree for a step without harm."""
-        mode = getattr(self, "overlap", "auto")
+        """`self.mode` is one of TUNE_MODES or "auto" (default). In "auto" the first six steps of the run try the three
+        formulations in turn (one warm-up step and one device-timed step each: peer-memory kernels back to back,
+        peer-memory kernels on two streams, the torch.distributed collectives), the maximum over ranks is compared
+        and the fastest is kept for the rest of the run. All three compute the same update from the same state, so
+        switching between steps is harmless. Setting `self.overlap` to True / False (older interface) pins the
+        two-stream / one-stream peer-memory order."""
+        mode = getattr(self, "mode", "auto")
+        ov = getattr(self, "overlap", "auto")
+        if mode == "auto" and ov != "auto":
+            mode = "fused_two_streams" if ov else "fused"
         if mode != "auto":
-            return self._step_fused()
-        k = len(self._tune) if hasattr(self, "_tune") else 0
+            return self._run_mode(mode)
         if not hasattr(self, "_tune"):
             self._tune = []
-        self.overlap = k >= 2          # calls 0,1 back to back; calls 2,3 on two streams
-        timed = k in (1, 3)
+        k = len(self._tune)
+        cand = self.TUNE_MODES[k // 2]
+        timed = k % 2 == 1
         if timed:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         try:
-            self._step_fused()
+            self._run_mode(cand)
         finally:
             self.overlap = "auto"
         ms = 0.0
@@ -272,9 +294,10 @@ class ShardedMuonAdamW:
             t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float32, device=self.device)
             ms = float(self.comm.all_reduce_max(t).item())
         self._tune.append(ms)
-        if k == 3:
-            self.overlap = bool(self._tune[3] < self._tune[1])
-            self.tuned = {"back_to_back_ms": self._tune[1], "two_stream_ms": self._tune[3], "overlap": self.overlap}
+        if len(self._tune) == 2 * len(self.TUNE_MODES):
+            times = {m: self._tune[2 * i + 1] for i, m in enumerate(self.TUNE_MODES)}
+            self.mode = min(times, key=times.get)
+            self.tuned = {"ms": times, "mode": self.mode}
 
     # ------------------------------------------------------------------ fused peer-memory step
     @torch.no_grad()
@@ -297,6 +320,7 @@ class ShardedMuonAdamW:
         gscale = 1.0 / W
         head = self.model.lm_head.weight
         cvp = ctypes.c_void_p
+        status_ptr = _lib.status_buffer(self.device).data_ptr()
         self._marks = []
         self._mark("start")
         main = torch.cuda.current_stream(self.device)
@@ -318,11 +342,11 @@ class ShardedMuonAdamW:
             r, c = ga.shape
             n_own = self.num_owned(ga)
             if n_own > 0:
-                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, c_int, cvp])(
+                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, c_int, cvp, cvp])(
                     ctypes.cast(comm.peer_ptrs(ga.G), cvp), comm.multicast_ptr(ga.G), W, rank, rank * ga.chunk * r * c,
                     st["momentum"].data_ptr(),
                     st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale,
-                    int(side is not main), _lib.stream_ptr())
+                    int(side is not main), status_ptr, _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_pre_multi")
             ev = torch.cuda.Event()
             ev.record(side)
@@ -402,9 +426,9 @@ class ShardedMuonAdamW:
                 side.wait_event(ev_post)
                 comm.device_barrier()                                                              # B_g
                 lr_b = _bf16(float(g["lr"]) * max(1.0, r / c) ** 0.5)
-                rc = _lib.fn("sr_muon_apply_multi", [cvp, cvp, c_int, c_long, cvp, c_long, c_float, c_float, cvp])(
+                rc = _lib.fn("sr_muon_apply_multi", [cvp, cvp, c_int, c_long, cvp, c_long, c_float, c_float, cvp, cvp])(
                     ga.P.data_ptr(), ctypes.cast(comm.peer_ptrs(st["U"]), cvp), W, ga.chunk * r * c, ga.W16.data_ptr(),
-                    ga.P.numel(), lr_b, _bf16(lr_b * _bf16(float(g["weight_decay"]))), _lib.stream_ptr())
+                    ga.P.numel(), lr_b, _bf16(lr_b * _bf16(float(g["weight_decay"]))), status_ptr, _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_apply_multi")
         # ---- side stream: shape groups without the kernel path (no bf16 shadow), then the AdamW slice gathers
         side.wait_stream(main)

@@ -39,6 +39,11 @@ class FusedComm(TorchComm):
         self._allocs = []          # (base address, bytes, handle)
         self._ptr_cache = {}
         self.epoch = 0
+        # How long a device-side barrier waits for each peer before it gives up and reports through the status word.
+        # Ranks may legitimately be seconds apart (one of them writes a checkpoint, evaluates, compiles), so the default
+        # is generous; tests set it to milliseconds to make a wait run out.
+        import os
+        self.wait_limit_s = float(os.environ.get("SLOWRUN_PEER_WAIT_S", "60"))
         self.flags = self.alloc((64,), torch.int32)
         self.flag_ptrs = self.peer_ptrs(self.flags)
         torch.cuda.synchronize()
@@ -94,22 +99,25 @@ class FusedComm(TorchComm):
     def device_barrier(self):
         """All ranks' preceding work on the current stream is complete and visible before any rank proceeds."""
         self.epoch += 1
-        rc = _lib.fn("sr_peer_barrier", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p])(
+        rc = _lib.fn("sr_peer_barrier", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p,
+                                         ctypes.c_ulonglong, ctypes.c_void_p])(
             ctypes.cast(self.flag_ptrs, ctypes.c_void_p), self.rank, self.world, self.epoch,
-            _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
+            _lib.status_buffer(self.device).data_ptr(), int(self.wait_limit_s * 1e9), _lib.stream_ptr())
         _lib.check_rc(rc, "sr_peer_barrier")
 
     # ------------------------------------------------------------------ fused primitives
     def reduce_from_peers(self, src: torch.Tensor, offset: int, out: torch.Tensor):
         """out[i] = sum_r src_r[offset + i], fp32 result; src is a symmetric fp32 or bf16 tensor."""
-        rc = _lib.fn("sr_reduce_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_long, ctypes.c_int, ctypes.c_void_p])(
+        rc = _lib.fn("sr_reduce_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_long, ctypes.c_int,
+                                         ctypes.c_void_p, ctypes.c_void_p])(
             ctypes.cast(self.peer_ptrs(src), ctypes.c_void_p), self.world, offset, out.data_ptr(), out.numel(),
-            int(src.dtype == torch.bfloat16), _lib.stream_ptr())
+            int(src.dtype == torch.bfloat16), _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check_rc(rc, "sr_reduce_multi")
 
     def gather_slices(self, buf: torch.Tensor):
         """Every rank owns slice `rank` of `buf` along dim 0; pull the other ranks' slices from their replicas."""
         slice_bytes = buf.numel() * buf.element_size() // self.world
-        rc = _lib.fn("sr_gather_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_long, ctypes.c_void_p])(
-            ctypes.cast(self.peer_ptrs(buf), ctypes.c_void_p), self.world, self.rank, slice_bytes, _lib.stream_ptr())
+        rc = _lib.fn("sr_gather_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_void_p])(
+            ctypes.cast(self.peer_ptrs(buf), ctypes.c_void_p), self.world, self.rank, slice_bytes,
+            _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check_rc(rc, "sr_gather_multi")

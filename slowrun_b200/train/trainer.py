@@ -152,6 +152,10 @@ class Trainer:
         self._pending_epoch = epoch
         self.sched.apply(self.param_groups, self.step)
         self.optimizer.step()
+        if getattr(self.optimizer, "fused", False):
+            # a device-side barrier that gave up leaves the status word set and every consumer kernel of the step
+            # returned without writing: stop here, before the gradients are cleared, instead of training on
+            _lib.check_status(self.device)
         model.zero_grad_arena()
         if self.ema is not None:
             self.ema.maybe_update(self.step)
@@ -288,6 +292,9 @@ class Trainer:
                 if keep > 0 and not stop:
                     path = ring.save(self.model, self.current_epoch)
                     print0(f"  Saved checkpoint {path} ({len(ring.paths)}/{keep})")
+                    # only rank 0 writes (seconds for a multi-GB model); the others wait here on the host, not inside
+                    # the next step's device-side barrier
+                    self.comm.barrier()
                 if stop:
                     break
                 st = window_stage_for_epoch(self.window_schedule, epoch)
@@ -306,6 +313,7 @@ class Trainer:
                 gc.disable()
         gc.enable()
         # ---------------------------------------------------------------- post-training averaging
+        self.comm.barrier()          # every checkpoint rank 0 wrote is complete before any rank reads it
         comm = self.comm if world > 1 else None
         if c.track in ("limited", "two_hour") and c.logit_avg > 0:
             paths = ring.paths
@@ -344,6 +352,7 @@ class Trainer:
                     min_loss, min_bpb = avg_loss, avg_bpb
             if self.master:
                 torch.save({n: p.data.float().cpu() for n, p in self.model.named_parameters()}, os.path.join(log.run_dir, "model.pt"))
+            self.comm.barrier()
         peak = torch.cuda.max_memory_allocated() / 1024 / 1024 if self.device.type == "cuda" else 0.0
         final_train = self.smooth_loss / (1 - 0.9 ** self.step) if self.step > 0 else float("inf")
         print0(f"Peak memory: {peak:.2f} MiB")

@@ -76,3 +76,26 @@ def test_noalloc_entry_point_rejects_oversized_problems():
     rc = lib.sr_muon_post_noalloc(X.data_ptr(), S.data_ptr(), U.data_ptr(), n, r, c, 0.95, torch.cuda.current_stream().cuda_stream)
     assert rc == -8
     torch.cuda.synchronize()
+
+
+def test_noalloc_entry_point_at_exactly_the_limit_and_with_a_bad_column_count():
+    lib = _lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    mx = lib.sr_muon_post_noalloc_max_elems()
+    torch.manual_seed(1)
+    n, r, c = 4, 64, mx // 4            # column mode, n * c == the limit exactly: accepted
+    X = (torch.randn(n, r, c, device="cuda") * 0.05).bfloat16()
+    S0 = torch.rand(n, c, device="cuda") * 1e-3
+    S_ref, S_new = S0.clone(), S0.clone()
+    U_ref = _reference(lib, X, S_ref, 0.94921875)
+    U_new = torch.empty_like(X)
+    assert lib.sr_muon_post_noalloc(X.data_ptr(), S_new.data_ptr(), U_new.data_ptr(), n, r, c, 0.94921875, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(S_new, S_ref, rtol=1e-4, atol=1e-9)
+    err = (U_new.float() - U_ref.float()).abs().max().item()
+    assert err <= 2e-2 * max(U_ref.float().abs().max().item(), 1e-6), err
+    # a column count that is not a multiple of four is refused before anything is launched
+    Xb = torch.zeros(1, 8, 6, dtype=torch.bfloat16, device="cuda")
+    Sb = torch.zeros(1, 8, device="cuda")
+    assert lib.sr_muon_post_noalloc(Xb.data_ptr(), Sb.data_ptr(), torch.empty_like(Xb).data_ptr(), 1, 8, 6, 0.95, stream) == -2
+    torch.cuda.synchronize()
