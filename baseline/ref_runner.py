@@ -11,6 +11,9 @@ the reference's files, is only what the scripts need to start offline on a B200:
     The limited and two-hour scripts only look for FlashAttention-3 when the device reports compute capability 9.x
     and refuse to run otherwise, so the capability query answers (9, 0) until that one lookup is done and is restored
     inside it;
+  * for the tiny track, whose loss kernel is compiled at import for compute capability 9.0 only
+    (tiny/cuda_kernels.py:305-312): the one `torch.cuda._compile_kernel` call is given this GPU's capability instead,
+    from here; the kernel source and the file are untouched;
   * a synthetic Zipf corpus in the reference's .pt format, passed through --input_bin / --input_val_bin.
 Timing uses torch's global optimizer-step hooks: a CUDA event and a host timestamp after every `optimizer.step()`;
 the period between consecutive steps is one full training step of the script (its micro-batches, H2D copies,
@@ -28,7 +31,7 @@ import types
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_ROOT = os.path.join(HERE, "_ref")
 
-SCRIPTS = {"limited": "train.py", "two_hour": os.path.join("two_hour", "train.py")}
+SCRIPTS = {"limited": "train.py", "two_hour": os.path.join("two_hour", "train.py"), "tiny": os.path.join("tiny", "train.py")}
 
 
 class _StopBench(BaseException):
@@ -118,7 +121,18 @@ def _install_stubs(state):
     kn.get_kernel = get_kernel
     sys.modules["kernels"] = kn
     torch.cuda.get_device_capability = lambda *a, **k: (9, 0)
-    state["restore_cap"] = lambda: setattr(torch.cuda, "get_device_capability", real_cap)
+    real_compile = getattr(torch.cuda, "_compile_kernel", None)
+    if real_compile is not None:
+        def compile_for_this_gpu(*a, **kw):
+            kw["compute_capability"] = "".join(str(v) for v in real_cap())
+            return real_compile(*a, **kw)
+        torch.cuda._compile_kernel = compile_for_this_gpu
+
+    def restore():
+        torch.cuda.get_device_capability = real_cap
+        if real_compile is not None:
+            torch.cuda._compile_kernel = real_compile
+    state["restore_cap"] = restore
 
 
 def run(track: str, steps: int, warmup: int, extra_args, data_dir: str, work_dir: str):
@@ -153,6 +167,7 @@ def run(track: str, steps: int, warmup: int, extra_args, data_dir: str, work_dir
             "--input_val_bin", os.path.join(data_dir, "fineweb_val.pt")] + list(extra_args)
     old_argv, old_cwd = sys.argv, os.getcwd()
     sys.argv = argv
+    sys.path.insert(0, os.path.dirname(script))       # the tiny script imports its kernel module from its own folder
     os.makedirs(work_dir, exist_ok=True)
     os.chdir(work_dir)
     try:
@@ -163,6 +178,7 @@ def run(track: str, steps: int, warmup: int, extra_args, data_dir: str, work_dir
     finally:
         handle.remove()
         sys.argv = old_argv
+        sys.path.remove(os.path.dirname(script))
         os.chdir(old_cwd)
         state["restore_cap"]()
     sys.stdout, sys.stderr = sys.__stdout__, sys.__stderr__

@@ -6,6 +6,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...     # the unmodified reference script through baseline/ref_runner.py
+    python bench.py --track tiny ...         # same measurement for the tiny track (16 layers, d_model 1024, 8 heads,
+                                             # recurrence, XSA, fp8 shared-head multi-token loss, device batch 32)
 
 One "step" is one optimizer step of the reference's loop (train.py:1156-1187): total_batch/(B*T*N) micro-batches of
 forward+backward with local gradient accumulation, then the sharded Muon/AdamW step with all its communication.
@@ -32,6 +34,7 @@ SIZES = {
     "2.7b": (30, 2560, 20),
     "1.4b": (30, 1792, 14),
     "smoke": (4, 256, 2),
+    "tiny": (16, 1024, 8),
 }
 
 
@@ -104,12 +107,18 @@ def parse_args():
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
-    p.add_argument("--size", type=str, default="2.7b", choices=list(SIZES))
-    p.add_argument("--device-batch-size", type=int, default=4)
+    p.add_argument("--track", type=str, default="limited", choices=["limited", "tiny"])
+    p.add_argument("--size", type=str, default=None, choices=list(SIZES))
+    p.add_argument("--device-batch-size", type=int, default=None)
     p.add_argument("--total-batch-size", type=int, default=524288)
     p.add_argument("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"])
     p.add_argument("--no-e2e", action="store_true")
-    return p.parse_args()
+    a = p.parse_args()
+    if a.size is None:
+        a.size = "tiny" if a.track == "tiny" else "2.7b"
+    if a.device_batch_size is None:
+        a.device_batch_size = 32 if a.track == "tiny" else 4
+    return a
 
 
 def ensure_corpus(args, rank, world, barrier):
@@ -131,8 +140,10 @@ def result_line(args, world, tok_per_s, ms_per_step, e2e, clocks, launches, extr
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic Zipf(s=1.1) tokens over 50257 ids in the reference .pt format; random-init weights",
-        "config": {"model": f"limited-track GPT {args.size}: n_layer={n_layer} n_embd={n_embd} n_head={n_head} head_dim=128 "
-                            f"swiglu IHA MTP dropout=0.1 stoch_depth=0.05 vocab=50257",
+        "config": {"model": (f"tiny-track GPT: n_layer={n_layer} n_embd={n_embd} n_head={n_head} head_dim=128 swiglu XSA "
+                             f"key-offset 2x-recurrence fp8 shared-head MTP dropout=0.1 vocab=50257" if args.track == "tiny" else
+                             f"limited-track GPT {args.size}: n_layer={n_layer} n_embd={n_embd} n_head={n_head} head_dim=128 "
+                             f"swiglu IHA MTP dropout=0.1 stoch_depth=0.05 vocab=50257"),
                    "global_batch": args.total_batch_size, "seq_len": 2048, "device_batch_size": args.device_batch_size,
                    "parallelism": f"dp{world} (optimizer-sharded)", "tokens_per_step": args.total_batch_size,
                    "l2": "working set (parameters + activations) is far larger than the 126 MB L2; no flush needed"},
@@ -164,7 +175,7 @@ def run_ours(args):
             dist.barrier()
 
     data_dir = ensure_corpus(args, rank, world, barrier)
-    cfg = track_defaults("limited")
+    cfg = track_defaults(args.track)
     cfg.model.n_layer, cfg.model.n_embd, cfg.model.n_head = SIZES[args.size]
     cfg.model.n_kv_head = cfg.model.n_head
     cfg.device_batch_size = args.device_batch_size
@@ -249,12 +260,12 @@ def run_reference(args):
         n_layer, n_embd, n_head = SIZES[args.size]
         extra = ["--n_layer", str(n_layer), "--n_embd", str(n_embd), "--n_head", str(n_head),
                  "--device-batch-size", str(args.device_batch_size), "--total-batch-size", str(args.total_batch_size),
-                 "--run-name", f"bench_ref_{os.getpid() if world == 1 else 'dist'}"]
+                 "--run-name", f"bench_ref_{args.track}_{os.getpid() if world == 1 else 'dist'}"]
         sampler = ClockSampler(0)
         if rank == 0:
             sampler.start()
         work = os.path.join(tempfile.gettempdir(), "slowrun_ref_work")
-        res = ref_runner.run("limited", args.steps, args.warmup, extra, data_dir, work)
+        res = ref_runner.run(args.track, args.steps, args.warmup, extra, data_dir, work)
         clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
             ms_per_step = res["device_ms"] / args.steps

@@ -4,6 +4,14 @@
 //
 //   qkv_prep fwd/bwd   split the fused [M, 3d] projection, add the gated value residual to v, apply RoPE and the
 //                      per-head RMSNorm to q and k; backward writes one dense dqkv buffer (train.py:296-306).
+//                      With `key_offset` the upper half of every key vector is the one computed for the previous token
+//                      of the same sequence (token 0 keeps its own): the tiny track's partial key offset on
+//                      long-window layers (tiny/train.py:447-449), done as a shifted store / shifted gradient load.
+//   attn_post fwd/bwd  what follows the attention kernel per (token, head): exclusive self-attention
+//                      y -= tanh(alpha_h) (y . v^) v^ with v^ the normalised value vector of the same token
+//                      (tiny/train.py:451-458), then the per-head sigmoid gate (train.py:308-309). The backward also
+//                      emits the attention backward's `delta` = rowsum(dO * O), the XSA contribution to dV and the
+//                      gradient of alpha.
 //   iha_mix fwd/bwd    Interleaved-head mixing of projection weights W'[h] = sum_m mix[h,m] W[m] on bf16 shadows and
 //                      its gradients (dW += mix^T dW', dmix = dW' W^T). The reference leaves the [H, d*D] x [d*D, H]
 //                      product to a library GEMM (train.py:277-280); with H <= 20 that is a long skinny reduction,
@@ -16,6 +24,16 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 constexpr int kThreads = kWarpsPerBlock * 32;
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -35,7 +53,7 @@ __global__ void qkv_prep_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
                                     const float* __restrict__ gate, const __nv_bfloat16* __restrict__ cosb,
                                     const __nv_bfloat16* __restrict__ sinb, __nv_bfloat16* __restrict__ q_out,
                                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, long tokens, int H,
-                                    int T, float eps) {
+                                    int T, float eps, int key_offset) {
   const long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (wid >= tokens * H) return;
   const int lane = threadIdx.x & 31;
@@ -59,7 +77,13 @@ __global__ void qkv_prep_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
     const float r = rsqrtf(ss * (1.f / 128.f) + eps);
     __nv_bfloat16* o = (which == 0 ? q_out : k_out) + wid * 128;
     st2(o + 2 * lane, o1.x * r, o1.y * r);
-    st2(o + 64 + 2 * lane, o2.x * r, o2.y * r);
+    if (which == 1 && key_offset) {
+      // upper half goes to the next token of the sequence (same head: H rows further); token 0 also keeps its own
+      if (t + 1 < T) st2(o + (long)H * 128 + 64 + 2 * lane, o2.x * r, o2.y * r);
+      if (t == 0) st2(o + 64 + 2 * lane, o2.x * r, o2.y * r);
+    } else {
+      st2(o + 64 + 2 * lane, o2.x * r, o2.y * r);
+    }
   }
   {
     const __nv_bfloat16* p = qkv + tok * 3 * d + 2 * d + h * 128 + lane * 4;
@@ -82,7 +106,8 @@ __global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
                                     const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ dv,
                                     __nv_bfloat16* __restrict__ dqkv, __nv_bfloat16* __restrict__ dve,
                                     float* __restrict__ dgate, long tokens, int H, int T, float eps,
-                                    const float* __restrict__ dq_f32) {
+                                    const float* __restrict__ dq_f32, int key_offset,
+                                    const __nv_bfloat16* __restrict__ dv_extra) {
   const long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (wid >= tokens * H) return;
   const int lane = threadIdx.x & 31;
@@ -109,7 +134,18 @@ __global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
     } else {
       const __nv_bfloat16* gp = (which == 0 ? dq : dk) + wid * 128;
       g1 = ld2(gp + 2 * lane);
-      g2 = ld2(gp + 64 + 2 * lane);
+      if (which == 1 && key_offset) {
+        // the upper half computed here was consumed by the next token (and by token 0 itself)
+        g2 = make_float2(0.f, 0.f);
+        if (t + 1 < T) g2 = ld2(gp + (long)H * 128 + 64 + 2 * lane);
+        if (t == 0) {
+          const float2 own = ld2(gp + 64 + 2 * lane);
+          g2.x += own.x;
+          g2.y += own.y;
+        }
+      } else {
+        g2 = ld2(gp + 64 + 2 * lane);
+      }
     }
     float ss = o1.x * o1.x + o1.y * o1.y + o2.x * o2.x + o2.y * o2.y;
     float dot = o1.x * g1.x + o1.y * g1.y + o2.x * g2.x + o2.y * g2.y;
@@ -128,7 +164,11 @@ __global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
   }
   {
     const __nv_bfloat16* gp = dv + wid * 128 + lane * 4;
-    const float2 g0 = ld2(gp), g1 = ld2(gp + 2);
+    float2 g0 = ld2(gp), g1 = ld2(gp + 2);
+    if (dv_extra != nullptr) {    // second consumer of v (exclusive self-attention)
+      const float2 x0 = ld2(dv_extra + wid * 128 + lane * 4), x1 = ld2(dv_extra + wid * 128 + lane * 4 + 2);
+      g0.x += x0.x; g0.y += x0.y; g1.x += x1.x; g1.y += x1.y;
+    }
     __nv_bfloat16* o = dqkv + tok * 3 * d + 2 * d + h * 128 + lane * 4;
     st2(o, g0.x, g0.y);
     st2(o + 2, g1.x, g1.y);
@@ -143,6 +183,107 @@ __global__ void qkv_prep_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const
       st2(de, g * g0.x, g * g0.y);
       st2(de + 2, g * g1.x, g * g1.y);
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- after attention
+// One warp per (token, head) row of 128; lane l owns elements 4l .. 4l+3. alpha: fp32 [H] (raw, tanh applied here) or
+// null = no exclusive self-attention.
+struct Row4 {
+  float v[4];
+};
+__device__ __forceinline__ Row4 ld4(const __nv_bfloat16* p) {
+  const float2 a = ld2(p), b = ld2(p + 2);
+  return Row4{{a.x, a.y, b.x, b.y}};
+}
+__device__ __forceinline__ float dot4(const Row4& a, const Row4& b) {
+  return a.v[0] * b.v[0] + a.v[1] * b.v[1] + a.v[2] * b.v[2] + a.v[3] * b.v[3];
+}
+
+__global__ void attn_post_fwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ v,
+                                     const float* __restrict__ gate, const float* __restrict__ alpha,
+                                     __nv_bfloat16* __restrict__ out, long rows, int H, float xsa_eps) {
+  const int lane = threadIdx.x & 31;
+  for (long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); wid < rows; wid += (long)gridDim.x * kWarpsPerBlock) {
+    Row4 yy = ld4(y + wid * 128 + lane * 4);
+    if (alpha != nullptr) {
+      const Row4 vv = ld4(v + wid * 128 + lane * 4);
+      const float n = fmaxf(sqrtf(warp_sum(dot4(vv, vv))), xsa_eps);
+      const float c = warp_sum(dot4(yy, vv)) / n;
+      const float k = tanhf(alpha[wid % H]) * c / n;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) yy.v[i] -= k * vv.v[i];
+    }
+    const float s = gate[wid];
+    __nv_bfloat16* o = out + wid * 128 + lane * 4;
+    st2(o, yy.v[0] * s, yy.v[1] * s);
+    st2(o + 2, yy.v[2] * s, yy.v[3] * s);
+  }
+}
+
+// g: gradient of the gated output. Writes dy (gradient of the attention output), dgate (w.r.t. the gate value),
+// delta[b, h, t] = sum_d dy * y, and with alpha: dv_x (this op's gradient of v) and dalpha[H] += (atomics, one per
+// block and head).
+__global__ void attn_post_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ y,
+                                     const __nv_bfloat16* __restrict__ v, const float* __restrict__ gate,
+                                     const float* __restrict__ alpha, __nv_bfloat16* __restrict__ dy,
+                                     float* __restrict__ dgate, float* __restrict__ delta,
+                                     __nv_bfloat16* __restrict__ dv_x, float* __restrict__ dalpha, long rows, int H, int T,
+                                     float xsa_eps) {
+  __shared__ float dal[64];
+  const int lane = threadIdx.x & 31;
+  if (alpha != nullptr) {
+    if (threadIdx.x < 64) dal[threadIdx.x] = 0.f;
+    __syncthreads();
+  }
+  for (long wid = (long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); wid < rows; wid += (long)gridDim.x * kWarpsPerBlock) {
+    const long tok = wid / H;
+    const int h = (int)(wid - tok * H);
+    const Row4 gg = ld4(g + wid * 128 + lane * 4);
+    const Row4 yy = ld4(y + wid * 128 + lane * 4);
+    const float s = gate[wid];
+    Row4 d;      // gradient of the attention output
+    float dg;    // sum_d g * (output before the gate)
+    if (alpha != nullptr) {
+      const Row4 vv = ld4(v + wid * 128 + lane * 4);
+      const float nrm = sqrtf(warp_sum(dot4(vv, vv)));
+      const float n = fmaxf(nrm, xsa_eps);
+      const float inv = 1.f / n;
+      const float c = warp_sum(dot4(yy, vv)) * inv;          // y . u,  u = v / n
+      const float a = tanhf(alpha[h]);
+      const float gy = warp_sum(dot4(gg, yy)), gu = warp_sum(dot4(gg, vv)) * inv;
+      dg = gy - a * c * gu;                                   // g . (y - a c u)
+      const float p = s * gu;                                 // (s g) . u
+      Row4 du;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float u = vv.v[i] * inv, dyp = s * gg.v[i];
+        d.v[i] = dyp - a * p * u;
+        du.v[i] = -a * (p * yy.v[i] + c * dyp);
+      }
+      // v -> u = v / max(|v|, eps): the projection term only where the norm is not clamped
+      const float duu = nrm > xsa_eps ? warp_sum(dot4(du, vv)) * inv : 0.f;
+      __nv_bfloat16* o = dv_x + wid * 128 + lane * 4;
+      st2(o, (du.v[0] - duu * vv.v[0] * inv) * inv, (du.v[1] - duu * vv.v[1] * inv) * inv);
+      st2(o + 2, (du.v[2] - duu * vv.v[2] * inv) * inv, (du.v[3] - duu * vv.v[3] * inv) * inv);
+      if (lane == 0) atomicAdd(&dal[h], -c * p * (1.f - a * a));
+    } else {
+      dg = warp_sum(dot4(gg, yy));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d.v[i] = s * gg.v[i];
+    }
+    const float dl = warp_sum(dot4(d, yy));
+    if (lane == 0) {
+      dgate[wid] = dg;
+      delta[((tok / T) * H + h) * T + (tok % T)] = dl;
+    }
+    __nv_bfloat16* o = dy + wid * 128 + lane * 4;
+    st2(o, d.v[0], d.v[1]);
+    st2(o + 2, d.v[2], d.v[3]);
+  }
+  if (alpha != nullptr) {
+    __syncthreads();
+    if (threadIdx.x < H && dal[threadIdx.x] != 0.f) atomicAdd(dalpha + threadIdx.x, dal[threadIdx.x]);
   }
 }
 
@@ -379,32 +520,63 @@ int iha_dispatch(int which, int H, const float* mix, const void* W, const void* 
 
 // qkv: [tokens, 3*H*128]; ve: [tokens, H*128] or null; gate: fp32 [tokens, H] (only read when ve != null)
 extern "C" int sr_qkv_prep_fwd(const void* qkv, const void* ve, const float* gate, const void* cosb, const void* sinb,
-                               void* q, void* k, void* v, long tokens, int H, int T, float eps, cudaStream_t s) {
+                               void* q, void* k, void* v, long tokens, int H, int T, float eps, int key_offset,
+                               cudaStream_t s) {
   const long n = tokens * H;
   if (n <= 0) return 0;
   qkv_prep_fwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
-      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BFM(q), BFM(k), BFM(v), tokens, H, T, eps);
+      BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BFM(q), BFM(k), BFM(v), tokens, H, T, eps, key_offset);
   return rc();
 }
 extern "C" int sr_qkv_prep_bwd(const void* qkv, const void* ve, const float* gate, const void* cosb, const void* sinb,
                                const void* dq, const void* dk, const void* dv, void* dqkv, void* dve, float* dgate,
-                               long tokens, int H, int T, float eps, cudaStream_t s) {
+                               long tokens, int H, int T, float eps, int key_offset, const void* dv_extra,
+                               cudaStream_t s) {
   const long n = tokens * H;
   if (n <= 0) return 0;
   qkv_prep_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
       BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), BF(dq), BF(dk), BF(dv), BFM(dqkv), BFM(dve), dgate, tokens, H, T, eps,
-      nullptr);
+      nullptr, key_offset, BF(dv_extra));
   return rc();
 }
 // Same with dQ given as the fp32 accumulator of the attention backward, (tokens, H, 128) contiguous.
 extern "C" int sr_qkv_prep_bwd_f32dq(const void* qkv, const void* ve, const float* gate, const void* cosb,
                                      const void* sinb, const float* dq_f32, const void* dk, const void* dv, void* dqkv,
-                                     void* dve, float* dgate, long tokens, int H, int T, float eps, cudaStream_t s) {
+                                     void* dve, float* dgate, long tokens, int H, int T, float eps, int key_offset,
+                                     const void* dv_extra, cudaStream_t s) {
   const long n = tokens * H;
   if (n <= 0) return 0;
   qkv_prep_bwd_kernel<<<(unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock), kThreads, 0, s>>>(
       BF(qkv), BF(ve), gate, BF(cosb), BF(sinb), nullptr, BF(dk), BF(dv), BFM(dqkv), BFM(dve), dgate, tokens, H, T, eps,
-      dq_f32);
+      dq_f32, key_offset, BF(dv_extra));
+  return rc();
+}
+
+// y, v, out: [tokens, H, 128] bf16 contiguous; gate: fp32 [tokens, H]; alpha: fp32 [H] or null (v is then unused).
+extern "C" int sr_attn_post_fwd(const void* y, const void* v, const float* gate, const float* alpha, void* out, long tokens,
+                                int H, float xsa_eps, cudaStream_t s) {
+  const long n = tokens * H;
+  if (n <= 0) return 0;
+  if (H > 64) return -2;
+  long blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const long cap = (long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  attn_post_fwd_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(BF(y), BF(v), gate, alpha, BFM(out), n, H, xsa_eps);
+  return rc();
+}
+// g: gradient of `out`. dy, dv_x: [tokens, H, 128] bf16; dgate: fp32 [tokens, H]; delta: fp32 [B, H, T] with tokens = B * T;
+// dalpha: fp32 [H], ADDED to (the caller passes the parameter's gradient buffer). dv_x / dalpha only with alpha.
+extern "C" int sr_attn_post_bwd(const void* g, const void* y, const void* v, const float* gate, const float* alpha, void* dy,
+                                float* dgate, float* delta, void* dv_x, float* dalpha, long tokens, int H, int T,
+                                float xsa_eps, cudaStream_t s) {
+  const long n = tokens * H;
+  if (n <= 0) return 0;
+  if (H > 64 || (alpha != nullptr && (dv_x == nullptr || dalpha == nullptr))) return -2;
+  long blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const long cap = (long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  attn_post_bwd_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(BF(g), BF(y), BF(v), gate, alpha, BFM(dy), dgate, delta,
+                                                             BFM(dv_x), dalpha, n, H, T, xsa_eps);
   return rc();
 }
 // out[p] = bf16(mix[p]) @ W[p] for P stacked projections, W viewed as [P, H, J]

@@ -82,7 +82,7 @@ __device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
 __global__ void __launch_bounds__(kThreads, 2)
 muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int rank, long base, float* __restrict__ Mom,
                       __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
-                      float gscale, const int* __restrict__ status) {
+                      float gscale, int row_norm, const int* __restrict__ status) {
   if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;   // a barrier gave up: touch nothing
   const int lane = threadIdx.x & 31;
   // at most one CTA per SM (the launcher caps the grid): the kernel is meant to share the SMs with the Newton-Schulz
@@ -145,7 +145,7 @@ muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int r
       }
     }
     ss = warp_sum(ss);
-    const float inv = 1.f / fmaxf(sqrtf(ss), 1e-7f);
+    const float inv = row_norm ? 1.f / fmaxf(sqrtf(ss), 1e-7f) : 1.f;
     float xs = 0.f;
     for (int j = lane * 4; j < c; j += 128) {
       const float4 nv = *reinterpret_cast<const float4*>(park + j);   // written by this same lane above
@@ -325,7 +325,7 @@ extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, in
 // 0 = two CTAs per SM (it has the GPU to itself).
 extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* mc, int world, int rank, long base,
                                  float* Mom, void* X,
-                                 float* sumsq, int n, int r, int c, float mu, float gscale, int shared_sms,
+                                 float* sumsq, int n, int r, int c, float mu, float gscale, int row_norm, int shared_sms,
                                  const int* status, cudaStream_t s) {
   if (n <= 0) return 0;
   if (c % 4 || rank < 0 || rank >= world) return -2;
@@ -337,7 +337,7 @@ extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* 
   const long cap = shared_sms ? sm_count() : 2L * sm_count();
   if (pull_grid > cap) pull_grid = cap;
   muon_pre_multi_kernel<<<(unsigned)pull_grid, kThreads, 0, s>>>(
-      t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, status);
+      t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, row_norm, status);
   const long total = rows * c;
   fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total, status);
   return rc();

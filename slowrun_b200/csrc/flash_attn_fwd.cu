@@ -322,16 +322,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+extern "C" void* sr_driver_encode_tiled(void);   // process-wide handle, gemm_tcgen05.cu
+
 EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  // a driver-API call: the device's context must be current on this thread (see gemm_common.cuh)
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
   }
-  return fn;
+  return reinterpret_cast<EncodeTiledFn>(sr_driver_encode_tiled());
 }
 
 // (B, T, H, 128) bf16 tensor with row stride `ld_t` elements between tokens (the head h slice starts at h*128);

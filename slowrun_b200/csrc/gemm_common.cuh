@@ -3,6 +3,7 @@
 // tensor-map encoder.
 #pragma once
 #include "sm100_common.cuh"
+#include <stdio.h>
 
 namespace {
 
@@ -259,16 +260,30 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+// The driver entry point is resolved once per process, by sr_runtime_init() (gemm_tcgen05.cu), which the Python
+// loader calls from the main thread right after it has opened the library: every translation unit and every thread
+// (autograd runs backward passes on its own) then shares the same pointer.
+extern "C" void* sr_driver_encode_tiled(void);
+
+// The encoder is a driver-API call and wants the device's context current on the calling thread. A thread whose first
+// CUDA activity is one of these launchers (autograd's worker, when the loss is the direct output of an op of this
+// library) has not bound it yet: one no-op runtime call per thread does.
+inline EncodeTiledFn get_encode_fn() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
   }
-  return fn;
+  return reinterpret_cast<EncodeTiledFn>(sr_driver_encode_tiled());
+}
+
+inline int report_encode_failure(CUresult r, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
+                                 const cuuint32_t* box) {
+  fprintf(stderr, "slowrun_b200: cuTensorMapEncodeTiled failed with CUresult %d (ptr %p, dims %llu x %llu x %llu, "
+                  "strides %llu %llu, box %u x %u)\n", (int)r, ptr, (unsigned long long)dims[0],
+          (unsigned long long)dims[1], (unsigned long long)dims[2], (unsigned long long)strides[0],
+          (unsigned long long)strides[1], box[0], box[1]);
+  return -3;
 }
 
 // 3-D bf16 tensor map {inner, rows, batch}, 128B swizzle, zero fill outside the tensor.
@@ -285,7 +300,7 @@ int encode_bf16_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t 
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  return r == CUDA_SUCCESS ? 0 : report_encode_failure(r, ptr, dims, strides, box);
 }
 
 // Same for 1-byte (fp8) elements: {inner, rows, batch} with the leading dimension given in elements (= bytes).
@@ -302,10 +317,10 @@ int encode_u8_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t ro
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  return r == CUDA_SUCCESS ? 0 : report_encode_failure(r, ptr, dims, strides, box);
 }
 
-int num_sms() {
+inline int num_sms() {
   static int n = 0;
   if (n == 0) {
     int dev = 0;

@@ -250,6 +250,28 @@ extern "C" int sr_gemm_bf16_pair(const void* A, const void* B, void* C, const vo
                                  const float* row_scale, int splitk, int bn, int max_ctas, int* status,
                                  cudaStream_t stream);
 
+// Process-wide handle of the driver's tensor-map encoder (see gemm_common.cuh). Resolved on first use and by
+// sr_runtime_init(); returns null when the driver does not export it.
+extern "C" void* sr_driver_encode_tiled(void) {
+  static void* fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = ptr;
+  }
+  return fn;
+}
+
+// Called once by the loader, from the thread that opened the library, with the device it will use current: creates
+// the runtime's context on that device and resolves the driver entry point there. Returns 0, or -1 when the tensor-map
+// encoder is not available.
+extern "C" int sr_runtime_init(void) {
+  cudaFree(nullptr);
+  return sr_driver_encode_tiled() != nullptr ? 0 : -1;
+}
+
 static int g_pair_mode = 1;
 // 1 (default): eligible problems run on the CTA-pair kernel (gemm_tcgen05_pair.cu); 0: single-CTA kernel only.
 extern "C" void sr_gemm_set_pair_mode(int on) { g_pair_mode = on; }

@@ -17,10 +17,13 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
-// Momentum + Nesterov + MuonEq-R row normalisation, one warp per row.
+// Momentum + Nesterov + (row_norm != 0) MuonEq-R row normalisation, one warp per row.
 //   G *= gscale (1/world for SUM-reduced gradients);  M <- M + (1-mu)(G - M);  g = G + mu(M - G);  g /= max(||g_row||, 1e-7);  X = bf16(g);  sumsq[b] += sum X^2
+// The limited, two-hour and unlimited tracks normalise rows (train.py:611-613); the tiny track does not
+// (tiny/train.py:770-778).
 __global__ void muon_pre_kernel(const float* __restrict__ G, float* __restrict__ Mom, __nv_bfloat16* __restrict__ X,
-                                float* __restrict__ sumsq, long rows_total, int r, int c, float mu, float gscale) {
+                                float* __restrict__ sumsq, long rows_total, int r, int c, float mu, float gscale,
+                                int row_norm) {
   const long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5);
   if (row >= rows_total) return;
   const int lane = threadIdx.x & 31;
@@ -39,7 +42,7 @@ __global__ void muon_pre_kernel(const float* __restrict__ G, float* __restrict__
     ss += a * a + b * b + cc * cc + d * d;
   }
   ss = warp_sum(ss);
-  const float inv = 1.f / fmaxf(sqrtf(ss), 1e-7f);
+  const float inv = row_norm ? 1.f / fmaxf(sqrtf(ss), 1e-7f) : 1.f;
   __nv_bfloat16* x = X + row * c;
   float xs = 0.f;
   for (int j = lane * 4; j < c; j += 128) {
@@ -244,12 +247,12 @@ inline int rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
 }  // namespace
 
 extern "C" int sr_muon_pre(const float* G, float* Mom, void* X, float* sumsq, int n, int r, int c, float mu,
-                           float gscale, cudaStream_t s) {
+                           float gscale, int row_norm, cudaStream_t s) {
   if (n <= 0) return 0;
   if (c % 4) return -2;
   const long rows = (long)n * r;
   cudaMemsetAsync(sumsq, 0, sizeof(float) * n, s);
-  muon_pre_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(G, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale);
+  muon_pre_kernel<<<(unsigned)((rows + kWarps - 1) / kWarps), kThreads, 0, s>>>(G, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, row_norm);
   const long total = rows * c;
   muon_fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total);
   return rc();

@@ -1,13 +1,14 @@
-"""Epoch-shuffling token loader with the reference's exact ordering.
+"""Epoch-shuffling token loader.
 
-Order of batches, per rank and per epoch, is the one `DataLoader` of the reference produces (train.py:765-840):
-documents are cumulatively re-permuted each epoch with seed = epoch, concatenated, cut into T+1 windows, the
-windows permuted with seed = epoch + 1000, the tail dropped, and step s of rank r is rows
-[s, r, :, :] of the [steps, world, B, T+1] view. With doc_shuffle off the stored numpy permutation is applied once
-and only the step order is reshuffled per epoch.
-
-What differs is the transport: the per-rank table is kept as int32 in pinned host memory and each batch is a
-single asynchronous H2D copy on a side stream, prefetched one step ahead, widened to int64 on the device.
+The batch order, per rank and per epoch, is bit-for-bit the one the reference's `DataLoader` yields
+(train.py:765-840; unlimited variant unlimited/train.py:765-964): that order is part of the training recipe.
+How it is produced is different. The corpus stays ONE int32 token tensor plus a table of document offsets; an
+epoch is described by a document order (an index vector that the per-epoch permutations act on) and a sequence
+permutation, and a rank materialises only ITS rows of the epoch: for every sequence it owns, the positions of the
+virtual concatenated stream are mapped back to corpus positions with one `searchsorted` over the cumulative document
+lengths and fetched with one gather. Nothing is concatenated, no per-document tensors exist, and a rank touches
+1/world of the tokens per epoch. The per-rank table lives in pinned host memory as int32; each batch is one
+asynchronous H2D copy on a side stream, issued one step ahead and widened to int64 on the device.
 """
 from __future__ import annotations
 
@@ -19,76 +20,117 @@ import torch
 from ..config import BOS_ID
 
 
-class TokenLoader:
-    def __init__(self, filepath, B, T, device="cuda", doc_shuffle=False, rank=0, world_size=1, prefetch=True,
-                 seed_fn=None):
+class Corpus:
+    """Tokens of a `.pt` corpus file (prepare_data.py format) and its document table."""
+
+    def __init__(self, filepath):
         data = torch.load(filepath, weights_only=True)
-        all_tokens = data["tokens"].long()
-        raw_doc_starts = data["doc_starts"].long()
         bos_id = int(data["bos_id"])
-        assert bos_id == BOS_ID, f"data bos_id {bos_id} != expected {BOS_ID}"
-        doc_ends = torch.cat([raw_doc_starts[1:], torch.tensor([all_tokens.numel()])])
-        self.doc_tokens = [all_tokens[s:e] for s, e in zip(raw_doc_starts.tolist(), doc_ends.tolist())]
-        self.default_shuffle_seed = data["seq_shuffle_seed"]
+        if bos_id != BOS_ID:
+            raise ValueError(f"corpus was tokenised with bos_id {bos_id}, this loader expects {BOS_ID}")
+        self.tokens = data["tokens"].to(torch.int32)
+        self.starts = data["doc_starts"].to(torch.int64)
+        ends = torch.cat([self.starts[1:], torch.tensor([self.tokens.numel()], dtype=torch.int64)])
+        self.lens = ends - self.starts
+        self.seq_shuffle_seed = data["seq_shuffle_seed"]
+
+    @property
+    def num_docs(self):
+        return self.starts.numel()
+
+
+class EpochStream:
+    """The virtual token stream "documents `order[0]`, `order[1]`, ... back to back" of one epoch."""
+
+    def __init__(self, corpus: Corpus, order: torch.Tensor):
+        self.corpus = corpus
+        lens = corpus.lens[order]
+        self.first = torch.cumsum(lens, 0) - lens                 # stream position where each document begins
+        self.src0 = corpus.starts[order]                          # corpus position where it begins
+        self.length = int(lens.sum())
+
+    def rows(self, seq_ids: torch.Tensor, seq_size: int) -> torch.Tensor:
+        """int32 [len(seq_ids), seq_size]: windows `seq_ids[i] * seq_size ...` of the stream, fetched from the corpus."""
+        pos = (seq_ids.to(torch.int64) * seq_size).unsqueeze(1) + torch.arange(seq_size, dtype=torch.int64)
+        doc = torch.searchsorted(self.first, pos.reshape(-1), right=True) - 1
+        src = self.src0[doc] + (pos.reshape(-1) - self.first[doc])
+        return self.corpus.tokens[src].view(len(seq_ids), seq_size)
+
+
+def _generator(seed: int) -> torch.Generator:
+    g = torch.Generator()
+    g.manual_seed(int(seed))
+    return g
+
+
+class TokenLoader:
+    """Infinite iterator of (x [B, T], y [B, T], epoch) for the limited, tiny and two-hour tracks.
+
+    doc_shuffle on: before every epoch after the first the document order is permuted again (seed = epoch, acting on
+    the previous order), the stream is cut into windows of T + 1 tokens, the windows are permuted (seed = epoch +
+    1000), the tail that does not fill a step of B * world windows is dropped and step s of rank r is windows
+    [s, r, :] of the [steps, world, B] arrangement. doc_shuffle off: file order, one fixed window permutation from
+    the seed stored in the file, and per epoch only the order of this rank's steps is re-permuted (seed = epoch)."""
+
+    def __init__(self, filepath, B, T, device="cuda", doc_shuffle=False, rank=0, world_size=1, prefetch=True):
+        self.corpus = Corpus(filepath)
         self.rank, self.world_size = rank, world_size
         self.device = torch.device(device)
         self.B, self.T, self.seq_size = B, T, T + 1
         self.doc_shuffle = doc_shuffle
         self.epoch = 1
+        self.order = torch.arange(self.corpus.num_docs)
         self._cuda = self.device.type == "cuda"
         self._stream = torch.cuda.Stream(device=self.device) if (self._cuda and prefetch) else None
         self._next = None
         self.h2d_bytes_per_batch = B * self.seq_size * 4
-        self._build_batches()
+        self._plan_epoch()
 
-    def _build_batches(self):
-        tokens = torch.cat(self.doc_tokens)
-        num_seqs = len(tokens) // self.seq_size
-        all_seqs = tokens[:num_seqs * self.seq_size].view(num_seqs, self.seq_size)
+    # ------------------------------------------------------------------ what this rank reads in the current epoch
+    def _window_permutation(self, num_seqs):
         if self.doc_shuffle:
-            g = torch.Generator()
-            g.manual_seed(self.epoch + 1000)
-            all_seqs = all_seqs[torch.randperm(num_seqs, generator=g)]
-        else:
-            perm = np.random.RandomState(self.default_shuffle_seed).permutation(num_seqs)
-            all_seqs = all_seqs[torch.from_numpy(perm)]
-        seqs_per_step = self.B * self.world_size
-        num_steps = len(all_seqs) // seqs_per_step
-        usable = num_steps * seqs_per_step
-        all_seqs = all_seqs[:usable].view(num_steps, self.world_size, self.B, self.seq_size)
-        self._set_rank_data(all_seqs[:, self.rank])
-        self.num_steps = num_steps
-        self.total_tokens = usable * self.T
+            return torch.randperm(num_seqs, generator=_generator(self.epoch + 1000))
+        return torch.from_numpy(np.random.RandomState(self.corpus.seq_shuffle_seed).permutation(num_seqs))
+
+    def _rank_share(self, perm):
+        """(window ids of this rank in step order, steps, windows used by all ranks)"""
+        per_step = self.B * self.world_size
+        steps = perm.numel() // per_step
+        mine = perm[:steps * per_step].view(steps, self.world_size, self.B)[:, self.rank]
+        return mine.reshape(-1), steps, steps * per_step
+
+    def _plan_epoch(self):
+        stream = EpochStream(self.corpus, self.order)
+        ids, steps, used = self._rank_share(self._window_permutation(stream.length // self.seq_size))
+        self._set_table(stream.rows(ids, self.seq_size).view(steps, self.B, self.seq_size))
+        self.num_steps = steps
+        self.total_tokens = used * self.T
         self.pos = 0
 
-    def _set_rank_data(self, t):
-        t = t.to(torch.int32).contiguous()
+    def _set_table(self, t):
+        t = t.contiguous()
         self.rank_data = t.pin_memory() if self._cuda else t
         self._next = None
 
-    def __iter__(self):
-        return self
-
-    def _next_epoch(self):
+    def _advance_epoch(self):
         self.epoch += 1
         if int(os.environ.get("RANK", 0)) == 0:
             print(f"Starting epoch {self.epoch}")
         if self.doc_shuffle:
-            g = torch.Generator()
-            g.manual_seed(self.epoch)
-            perm = torch.randperm(len(self.doc_tokens), generator=g)
-            self.doc_tokens = [self.doc_tokens[i] for i in perm.tolist()]
-            self._build_batches()
+            self.order = self.order[torch.randperm(self.order.numel(), generator=_generator(self.epoch))]
+            self._plan_epoch()
         else:
+            self._set_table(self.rank_data[torch.randperm(self.num_steps, generator=_generator(self.epoch))])
             self.pos = 0
-            g = torch.Generator()
-            g.manual_seed(self.epoch)
-            self._set_rank_data(self.rank_data[torch.randperm(self.num_steps, generator=g)])
+
+    # ------------------------------------------------------------------ transport
+    def __iter__(self):
+        return self
 
     def _issue(self):
-        """Start the copy of the batch at self.pos (rolling the epoch if needed); returns (device int32, epoch)."""
+        """Start the copy of the batch at self.pos (rolling the epoch if needed)."""
         if self.pos >= self.num_steps:
-            self._next_epoch()
+            self._advance_epoch()
         host = self.rank_data[self.pos]
         self.pos += 1
         if self._stream is not None:
@@ -107,74 +149,104 @@ class TokenLoader:
             torch.cuda.current_stream().wait_event(ev)
             dev.record_stream(torch.cuda.current_stream())
         batch = dev.long()
-        # prefetch the following batch while this one is consumed (does not roll the visible epoch early:
-        # the epoch returned with a batch is the loader's epoch after that batch was taken, as in the reference)
         x, y = batch[:, :-1].contiguous(), batch[:, 1:].contiguous()
+        # The next copy is issued now unless it would roll the epoch: the epoch reported with a batch is the loader's
+        # epoch at the moment that batch was taken.
         self._next = None
         if self._stream is not None and self.pos < self.num_steps:
             self._next = self._issue()
         return x, y, epoch
 
+    # ------------------------------------------------------------------ resume support
+    def state(self) -> dict:
+        """Position of the next batch the CONSUMER will see (a prefetched but unconsumed batch is counted as unread)."""
+        pos = self.pos - (1 if self._next is not None else 0)
+        return {"epoch": self.epoch, "pos": pos, "order": self.order.clone()}
+
+    def restore(self, st: dict):
+        """Re-create the table of the saved epoch and continue at the saved step. With doc_shuffle off the cumulative
+        step permutations of the elapsed epochs are replayed."""
+        target_epoch, pos = int(st["epoch"]), int(st["pos"])
+        self._next = None
+        if self.doc_shuffle:
+            self.epoch = target_epoch
+            self.order = st["order"].clone()
+            self._plan_epoch()
+        else:
+            self.epoch = 1
+            self._plan_epoch()
+            while self.epoch < target_epoch:
+                self.epoch += 1
+                self._set_table(self.rank_data[torch.randperm(self.num_steps, generator=_generator(self.epoch))])
+        self.pos = pos
+
 
 class EnsembleTokenLoader(TokenLoader):
-    """Loader of the unlimited track: per-model seed, step interleaving over data-parallel ranks, and a held-out
-    "fitness" slice carved from the front of the training file at document granularity
-    (unlimited/train.py:765-964). Ordering per epoch e of a model with seed s: documents permuted (cumulatively)
-    with seed s*1009 + e + 1000, windows permuted with seed s*1009 + e + 2000, the step list truncated to a multiple
-    of the data-parallel size and rank r takes steps r, r + world, ...
-    """
+    """Loader of the unlimited track (unlimited/train.py:765-964): a per-model seed, steps dealt round-robin to the
+    data-parallel ranks, and a held-out "fitness" slice taken from the front of the file at document granularity.
+    Epoch e of the model with seed s: the document order is permuted again with seed s * 1009 + e + 1000 (also
+    before the first epoch), windows with seed s * 1009 + e + 2000, the step list is cut to a multiple of the
+    data-parallel size and rank r takes steps r, r + world, ... With `fitness_only` the loader serves the held-out
+    documents instead, the way the reference's p(ground truth) cache reads them (unlimited/train.py:1002-1009): windows
+    of the held-out stream permuted with seed `seed + epoch`, step s of rank r = windows [s, r, :]."""
 
     def __init__(self, filepath, B, T, device="cuda", seed=0, rank=0, world_size=1, fitness_tokens=0,
                  fitness_only=False, prefetch=True):
         self.seed = int(seed)
         self.fitness_tokens = int(fitness_tokens)
         self.fitness_only = fitness_only
-        self._carved = False
+        self.fitness_order = None
+        self._keep_order = False
         super().__init__(filepath, B, T, device=device, doc_shuffle=True, rank=rank, world_size=world_size,
                          prefetch=prefetch)
 
     def _carve(self):
-        if self._carved:
+        """Split the document list once: the shortest prefix holding at least `fitness_tokens` tokens is held out."""
+        if self.fitness_order is not None:
             return
-        self._carved = True
-        if self.fitness_tokens <= 0:
-            self.fitness_docs = []
-            return
-        n, cut = 0, 0
-        for cut, d in enumerate(self.doc_tokens):
-            if n >= self.fitness_tokens:
-                break
-            n += len(d)
-        else:
-            cut = len(self.doc_tokens)
-        self.fitness_docs = self.doc_tokens[:cut]
-        self.doc_tokens = self.doc_tokens[cut:]
+        n = self.corpus.num_docs
+        cut = 0
+        if self.fitness_tokens > 0:
+            csum = torch.cumsum(self.corpus.lens, 0)
+            cut = min(int(torch.searchsorted(csum, self.fitness_tokens, right=False)) + 1, n)
+        self.fitness_order = torch.arange(cut)
+        self.order = torch.arange(cut, n)
 
-    def _build_batches(self):
+    def _plan_epoch(self):
         self._carve()
         if self.fitness_only:
-            tokens = torch.cat(self.fitness_docs) if self.fitness_docs else torch.zeros(0, dtype=torch.long)
-            num_seqs = len(tokens) // self.seq_size
-            all_seqs = tokens[:num_seqs * self.seq_size].view(num_seqs, self.seq_size)
+            stream = EpochStream(self.corpus, self.fitness_order)
+            perm = torch.randperm(stream.length // self.seq_size, generator=_generator(self.seed + self.epoch))
+            ids, steps, used = self._rank_share(perm)
+            self._set_table(stream.rows(ids, self.seq_size).view(steps, self.B, self.seq_size))
+            self.num_steps, self.total_tokens, self.pos = steps, used * self.T, 0
+            return
         else:
-            g = torch.Generator()
-            g.manual_seed(self.seed * 1009 + self.epoch + 1000)
-            perm = torch.randperm(len(self.doc_tokens), generator=g)
-            self.doc_tokens = [self.doc_tokens[i] for i in perm.tolist()]
-            tokens = torch.cat(self.doc_tokens)
-            num_seqs = len(tokens) // self.seq_size
-            all_seqs = tokens[:num_seqs * self.seq_size].view(num_seqs, self.seq_size)
-            g.manual_seed(self.seed * 1009 + self.epoch + 2000)
-            all_seqs = all_seqs[torch.randperm(num_seqs, generator=g)]
-        steps_total = len(all_seqs) // self.B
-        steps_total = (steps_total // self.world_size) * self.world_size
-        usable = steps_total * self.B
-        all_seqs = all_seqs[:usable].view(steps_total, self.B, self.seq_size)
-        self._set_rank_data(all_seqs[self.rank::self.world_size])
-        self.num_steps = steps_total // self.world_size
-        self.total_tokens = usable * self.T
+            base = self.seed * 1009 + self.epoch
+            if not self._keep_order:
+                self.order = self.order[torch.randperm(self.order.numel(), generator=_generator(base + 1000))]
+            stream = EpochStream(self.corpus, self.order)
+            perm = torch.randperm(stream.length // self.seq_size, generator=_generator(base + 2000))
+        steps_total = (perm.numel() // self.B // self.world_size) * self.world_size
+        used = steps_total * self.B
+        mine = perm[:used].view(steps_total, self.B)[self.rank::self.world_size]
+        steps = steps_total // self.world_size
+        self._set_table(stream.rows(mine.reshape(-1), self.seq_size).view(steps, self.B, self.seq_size))
+        self.num_steps = steps
+        self.total_tokens = used * self.T
         self.pos = 0
 
-    def _next_epoch(self):
+    def _advance_epoch(self):
         self.epoch += 1
-        self._build_batches()
+        self._plan_epoch()
+
+    def restore(self, st: dict):
+        """`st["order"]` is the document order of the saved epoch (already permuted for it)."""
+        self._carve()
+        self.epoch, self.order = int(st["epoch"]), st["order"].clone()
+        self._keep_order = True
+        try:
+            self._plan_epoch()
+        finally:
+            self._keep_order = False
+        self.pos = int(st["pos"])

@@ -28,50 +28,55 @@ def has_ve(layer_idx: int, n_layer: int) -> bool:
 
 
 class Rotary(nn.Module):
-    """RoPE tables [1, T, 1, D/2] in bf16 with the three variants of the reference: full (train.py:424-430),
-    half-truncated (tiny/train.py:557-567) and YaRN-rescalable with a softmax scale (two_hour/train.py:291-331)."""
+    """Rotary position tables, bf16 [1, T, 1, D/2], for the three RoPE flavours of the model family:
+    full (train.py:424-430), half-truncated where only the first D/4 frequency pairs rotate (tiny/train.py:557-567),
+    and YaRN-rescalable together with the attention softmax scale (two_hour/train.py:291-331).
+
+    State is the per-pair angular frequency vector `inv_freq`; the tables are a pure function of it
+    (`_tabulate`). Stretching the context from L to L' multiplies each frequency by
+    s + w (1 - s), s = L / L', where w ramps from 0 to 1 as the number of full turns the pair makes over L goes from
+    `slow` to `fast` (slowly rotating pairs are interpolated, fast ones kept), and the softmax scale by 0.2 ln(L'/L) + 1.
+    """
 
     def __init__(self, head_dim: int, max_seq_len: int, base: float = 10000.0, truncate: bool = False):
         super().__init__()
         self.head_dim, self.max_seq_len, self.base, self.truncate = head_dim, max_seq_len, base, truncate
-        self.register_buffer("inv_freq", torch.empty(head_dim // 2), persistent=False)
-        self.register_buffer("cos", torch.empty(1, max_seq_len, 1, head_dim // 2, dtype=torch.bfloat16), persistent=False)
-        self.register_buffer("sin", torch.empty(1, max_seq_len, 1, head_dim // 2, dtype=torch.bfloat16), persistent=False)
+        pairs = head_dim // 2
+        self.register_buffer("inv_freq", torch.empty(pairs), persistent=False)
+        self.register_buffer("cos", torch.empty(1, max_seq_len, 1, pairs, dtype=torch.bfloat16), persistent=False)
+        self.register_buffer("sin", torch.empty(1, max_seq_len, 1, pairs, dtype=torch.bfloat16), persistent=False)
         self.attn_scale = head_dim ** -0.5
         self.yarn_active = False
 
-    def _build_inv_freq(self, device):
-        D = self.head_dim
-        if self.truncate:
-            half = D // 4
-            f = 1.0 / (self.base ** (torch.arange(0, half * 2, 2, dtype=torch.float32, device=device) / (half * 2)))
-            return torch.cat([f, torch.zeros(D // 2 - half, dtype=torch.float32, device=device)])
-        return 1.0 / (self.base ** (torch.arange(0, D, 2, dtype=torch.float32, device=device) / D))
+    def _base_frequencies(self, device):
+        pairs = self.head_dim // 2
+        live = pairs // 2 if self.truncate else pairs          # pairs that actually rotate
+        k = torch.arange(live, dtype=torch.float32, device=device)
+        freq = 1.0 / (self.base ** (k / live))
+        return torch.cat([freq, freq.new_zeros(pairs - live)])
+
+    @torch.no_grad()
+    def _tabulate(self):
+        angle = torch.arange(self.max_seq_len, dtype=torch.float32, device=self.inv_freq.device)[:, None] * self.inv_freq
+        self.cos.copy_(angle.cos().bfloat16().view_as(self.cos))
+        self.sin.copy_(angle.sin().bfloat16().view_as(self.sin))
 
     @torch.no_grad()
     def reset(self):
-        dev = self.inv_freq.device
-        self.inv_freq.copy_(self._build_inv_freq(dev))
-        self._refresh()
+        self.inv_freq.copy_(self._base_frequencies(self.inv_freq.device))
+        self._tabulate()
         self.attn_scale = self.head_dim ** -0.5
         self.yarn_active = False
 
     @torch.no_grad()
-    def _refresh(self):
-        t = torch.arange(self.max_seq_len, dtype=torch.float32, device=self.inv_freq.device)
-        freqs = torch.outer(t, self.inv_freq)
-        self.cos.copy_(freqs.cos()[None, :, None, :].bfloat16())
-        self.sin.copy_(freqs.sin()[None, :, None, :].bfloat16())
-
-    @torch.no_grad()
-    def apply_yarn(self, old_window: int, new_window: int, alpha: int = 1, beta: int = 32):
+    def apply_yarn(self, old_window: int, new_window: int, slow: float = 1.0, fast: float = 32.0):
         if new_window <= old_window:
-            raise ValueError(f"YaRN window updates must expand context, got {old_window} -> {new_window}")
-        rotations = old_window * self.inv_freq / (2 * torch.pi)
-        s = old_window / new_window
-        w = torch.clamp((rotations - alpha) / (beta - alpha), 0, 1)
-        self.inv_freq.mul_(s + w * (1 - s))
-        self._refresh()
+            raise ValueError(f"the context can only be stretched: {old_window} -> {new_window} tokens is not an expansion")
+        shrink = old_window / new_window
+        turns = self.inv_freq * (old_window / (2 * math.pi))
+        keep = ((turns - slow) / (fast - slow)).clamp_(0, 1)
+        self.inv_freq.mul_(shrink + keep * (1 - shrink))
+        self._tabulate()
         self.attn_scale *= 0.2 * math.log(new_window / old_window) + 1
         self.yarn_active = True
 
@@ -196,30 +201,33 @@ class GPT(nn.Module):
 
     # ------------------------------------------------------------------ structure helpers
     def _compute_window_sizes(self, short_w, long_w):
-        char_to_w = {"L": (long_w, 0), "S": (short_w, 0)}
-        n = self.config.n_layer
-        sizes = [char_to_w[self.window_pattern[i % len(self.window_pattern)]] for i in range(n)]
-        sizes[-1] = (long_w, 0)
-        return sizes
+        """(left, right) attention window per layer: the pattern string is tiled over the layers ('S' = short, 'L' =
+        long) and the last layer always sees the long window (train.py:432-438)."""
+        n, pat = self.config.n_layer, self.window_pattern
+        return [((long_w if (pat[i % len(pat)] == "L" or i == n - 1) else short_w), 0) for i in range(n)]
 
     @torch.no_grad()
     def set_window_sizes(self, short_window: int, long_window: int, apply_yarn: bool = False):
-        """Window schedule of the two-hour track (two_hour/train.py:538-551)."""
+        """Switch the active attention windows (the two-hour track's window schedule, two_hour/train.py:538-551).
+        With `apply_yarn` a longer long window also rescales the rotary frequencies and the softmax scale; the long
+        window never shrinks once YaRN is in play, because the frequency rescaling is not undone."""
         short_window, long_window = int(short_window), int(long_window)
-        if short_window <= 0 or long_window <= 0 or short_window > long_window:
-            raise ValueError(f"Invalid active windows short={short_window}, long={long_window}")
-        if long_window > self.config.sequence_len:
-            raise ValueError(f"Long window must be <= sequence length ({self.config.sequence_len}), got {long_window}")
-        if apply_yarn and long_window != self.long_window:
-            if long_window < self.long_window:
-                raise ValueError(f"Window schedule cannot shrink long context after start, got {self.long_window} -> {long_window}")
+        if not 0 < short_window <= long_window <= self.config.sequence_len:
+            raise ValueError(f"windows must satisfy 0 < short <= long <= {self.config.sequence_len}, "
+                             f"got short={short_window}, long={long_window}")
+        if apply_yarn and long_window < self.long_window:
+            raise ValueError(f"the long window cannot shrink under YaRN: {self.long_window} -> {long_window}")
+        if apply_yarn and long_window > self.long_window:
             self.rotary.apply_yarn(self.long_window, long_window)
         self.short_window, self.long_window = short_window, long_window
         self.window_sizes = self._compute_window_sizes(short_window, long_window)
 
     def set_dupe_layers(self, start: int, end: int, loops: int = 2):
-        assert start >= self.encoder_layers, "dupe layers must be decoder-only"
-        assert end <= self.config.n_layer
+        """Replay decoder layers [start, end) `loops` extra times per forward (train.py:378-383). Only decoder layers
+        can be replayed: every replay re-adds the U-Net skip of the matching encoder layer."""
+        if not self.encoder_layers <= start < end <= self.config.n_layer:
+            raise ValueError(f"replayed layers [{start}, {end}) must lie in the decoder half "
+                             f"[{self.encoder_layers}, {self.config.n_layer})")
         self._dupe_layers = (start, end)
         self._dupe_loops = loops
 
@@ -296,30 +304,32 @@ class GPT(nn.Module):
             if block.attn.iha_mix_v:
                 torch.nn.init.eye_(block.attn.v_mix)
 
-    # ------------------------------------------------------------------ FLOPs (train.py:443-459, tiny/train.py:595-625)
+    # ------------------------------------------------------------------ FLOPs per token
     @staticmethod
-    def _avg_causal_attended_keys(window, seq_len):
-        if window < 0 or window >= seq_len - 1:
-            return (seq_len + 1) / 2
-        max_keys = min(window + 1, seq_len)
-        return max_keys - max_keys * (max_keys - 1) / (2 * seq_len)
+    def _mean_visible_keys(window: int, T: int) -> float:
+        """Average, over the T query positions of a sequence, of the number of keys a causal query with left window
+        `window` attends to: position i sees min(i, window) + 1 keys."""
+        if window < 0 or window >= T - 1:
+            return (T + 1) / 2
+        w = min(window + 1, T)
+        return w - w * (w - 1) / (2 * T)          # the first w positions see 1..w keys, the other T - w see w
 
     def estimate_flops(self, num_iterations: Optional[int] = None):
+        """Training FLOPs per token in the reference's accounting (train.py:443-459; recurrent form
+        tiny/train.py:595-625): 6 per matmul parameter (embedding table and per-layer scalars excluded) plus
+        12 * heads * head_dim * mean visible keys per layer for attention. For the recurrent (tiny) model the layer
+        stack and the value projections count once per pass."""
         c = self.config
-        nparams = sum(p.numel() for p in self.parameters())
-        exclude = (self.transformer.wte.weight.numel() + self.resid_lambdas.numel() + self.x0_lambdas.numel()
-                   + self.skip_weights.numel())
-        if hasattr(self, "xsa_alphas"):
-            exclude += self.xsa_alphas.numel()
-        h, q, t = c.n_head, c.head_dim, c.sequence_len
-        attn = sum(12 * h * q * self._avg_causal_attended_keys(w[0], t) for w in self.window_sizes)
-        if c.num_iterations > 1 or num_iterations is not None:
-            it = c.num_iterations if num_iterations is None else num_iterations
-            shared = (sum(p.numel() for p in self.transformer.h.parameters())
-                      + sum(p.numel() for p in self.ve_projs.parameters()))
-            extra = nparams - exclude - shared
-            return 6 * (extra + it * shared) + it * attn
-        return 6 * (nparams - exclude) + attn
+        total = sum(p.numel() for p in self.parameters())
+        scalars = [self.resid_lambdas, self.x0_lambdas, self.skip_weights] + ([self.xsa_alphas] if hasattr(self, "xsa_alphas") else [])
+        dense = total - self.transformer.wte.weight.numel() - sum(p.numel() for p in scalars)
+        attn = sum(12 * c.n_head * c.head_dim * self._mean_visible_keys(w[0], c.sequence_len) for w in self.window_sizes)
+        recurrent = c.num_iterations > 1 or num_iterations is not None
+        if not recurrent:
+            return 6 * dense + attn
+        passes = c.num_iterations if num_iterations is None else num_iterations
+        per_pass = sum(p.numel() for p in self.transformer.h.parameters()) + sum(p.numel() for p in self.ve_projs.parameters())
+        return 6 * (dense - per_pass + passes * per_pass) + passes * attn
 
     # ------------------------------------------------------------------ CUDA preparation
     def finalize(self, world_size: int = 1, alloc=None):

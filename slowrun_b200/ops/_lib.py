@@ -44,6 +44,12 @@ def lib() -> ctypes.CDLL:
                 from ..csrc import build as _build
                 _build.build()
             _lib = ctypes.CDLL(_SO)
+            if torch.cuda.is_available():
+                # resolve the driver's tensor-map encoder here, on the loading thread, for every later caller
+                # (backward passes call the GEMMs from autograd's worker thread)
+                _lib.sr_runtime_init.restype = ctypes.c_int
+                if _lib.sr_runtime_init() != 0:
+                    raise RuntimeError("the CUDA driver does not export cuTensorMapEncodeTiled; the sm_100a kernels cannot run")
             if os.environ.get("SR_GEMM_PAIR", "1") == "0":
                 _lib.sr_gemm_set_pair_mode(0)
     return _lib

@@ -163,12 +163,14 @@ class _BlockFn(Function):
         cos2, sin2 = cos.view(-1, cos.size(-1)), sin.view(-1, sin.size(-1))
         q = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=x.device)
         k, v = torch.empty_like(q), torch.empty_like(q)
-        _call("sr_qkv_prep_fwd", [P] * 8 + [L, I, I, F32, P], qkv.data_ptr(), _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(),
-              sin2.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), M, H, T, eps, _sp())
+        koff = int(bool(attn.use_key_offset) and T > 1)
+        _call("sr_qkv_prep_fwd", [P] * 8 + [L, I, I, F32, I, P], qkv.data_ptr(), _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(),
+              sin2.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), M, H, T, eps, koff, _sp())
         y, attn_saved = impl.fwd(q, k, v, window, scale)
         y2 = torch.empty_like(y)
-        _call("sr_head_gate_fwd", [P] * 4 + [L, I, L, L, L, I, P], y.data_ptr(), 0, agate.data_ptr(), y2.data_ptr(), M, H,
-              H * D, 0, H * D, 1, _sp())
+        xsa = model.xsa_alphas if (do_mix and model._xsa_enabled(i)) else None     # [n_layer, H] fp32, row i
+        _call("sr_attn_post_fwd", [P] * 5 + [L, I, F32, P], y.data_ptr(), v.data_ptr(), agate.data_ptr(),
+              xsa.data_ptr() + 4 * i * H if xsa is not None else 0, y2.data_ptr(), M, H, float(attn.xsa_eps), _sp())
         o = gemm(y2.view(M, C), fz["proj_w16"])
         # ---- residual, MLP
         p_attn = float(attn.dropout) if training else 0.0
@@ -191,7 +193,7 @@ class _BlockFn(Function):
         else:
             out = _dropout_add_fwd(x_mid, mo, p_mlp, seed2)
         ctx.save_for_backward(xp, x0_2 if x0_2 is not None else xp.new_empty(0), sk if sk is not None else xp.new_empty(0))
-        ctx.t = (x, a, ve, mixes, w_qkv, qkv, agate, ve_gate, attn_saved, y, y2, x_mid, n, gf, hdn, keep)
+        ctx.t = (x, a, ve, mixes, w_qkv, qkv, agate, ve_gate, attn_saved, y, y2, x_mid, n, gf, hdn, keep, v, xsa, koff)
         ctx.meta = (model, block, i, j, do_mix, ve_lin, p_attn, p_mlp, seed1, seed2, eps, impl, (B, T, C, H, D),
                     x0 is not None, skip is not None)
         return out.view(B, T, C)
@@ -199,7 +201,7 @@ class _BlockFn(Function):
     @staticmethod
     def backward(ctx, g_out):
         xp, x0_2, sk = ctx.saved_tensors
-        x, a, ve, mixes, w_qkv, qkv, agate, ve_gate, attn_saved, y, y2, x_mid, n, gf, hdn, keep = ctx.t
+        x, a, ve, mixes, w_qkv, qkv, agate, ve_gate, attn_saved, y, y2, x_mid, n, gf, hdn, keep, v, xsa, koff = ctx.t
         model, block, i, j, do_mix, ve_lin, p_attn, p_mlp, seed1, seed2, eps, impl, dims, has_x0, has_skip = ctx.meta
         ctx.t = None
         B, T, C, H, D = dims
@@ -227,24 +229,25 @@ class _BlockFn(Function):
         dy = torch.empty_like(y)
         dagate = torch.empty((M, H), dtype=torch.float32, device=g.device)
         fused_attn_bwd = getattr(impl, "has_bwd", False) and hasattr(impl, "bwd_fused")
+        # gate (and exclusive self-attention) backward; it already forms delta = rowsum(dy * y) for the attention
+        # backward, which in turn leaves dQ in fp32 for qkv_prep_bwd
+        delta = torch.empty((B, H, T), dtype=torch.float32, device=g.device)
+        dv_x = torch.empty_like(y) if xsa is not None else None
+        _call("sr_attn_post_bwd", [P] * 10 + [L, I, I, F32, P], dy2.data_ptr(), y.data_ptr(), v.data_ptr(), agate.data_ptr(),
+              xsa.data_ptr() + 4 * i * H if xsa is not None else 0, dy.data_ptr(), dagate.data_ptr(), delta.data_ptr(),
+              _lib.ptr(dv_x), xsa.grad.data_ptr() + 4 * i * H if xsa is not None else 0, M, H, T, float(attn.xsa_eps), _sp())
         if fused_attn_bwd:
-            # the gate backward already forms rowsum(dy * y); the attention backward leaves dQ in fp32 for qkv_prep_bwd
-            delta = torch.empty((B, H, T), dtype=torch.float32, device=g.device)
-            _call("sr_head_gate_bwd_delta", [P] * 6 + [L, I, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), agate.data_ptr(),
-                  dy.data_ptr(), dagate.data_ptr(), delta.data_ptr(), M, H, T, H * D, H * D, H * D, _sp())
             dq, dk, dv = impl.bwd_fused(attn_saved, dy, delta)
         else:
-            _call("sr_head_gate_bwd", [P] * 5 + [L, I, L, L, L, P], dy2.data_ptr(), y.data_ptr(), agate.data_ptr(), dy.data_ptr(),
-                  dagate.data_ptr(), M, H, H * D, H * D, H * D, _sp())
             dq, dk, dv = impl.bwd(attn_saved, dy)
         dqkv = torch.empty_like(qkv)
         dve = torch.empty((M, C), dtype=torch.bfloat16, device=g.device) if ve is not None else None
         dvegate = torch.empty((M, H), dtype=torch.float32, device=g.device) if ve is not None else None
         cos, sin = model.rotary.cos, model.rotary.sin
         cos2, sin2 = cos.view(-1, cos.size(-1)), sin.view(-1, sin.size(-1))
-        _call("sr_qkv_prep_bwd_f32dq" if fused_attn_bwd else "sr_qkv_prep_bwd", [P] * 11 + [L, I, I, F32, P], qkv.data_ptr(),
+        _call("sr_qkv_prep_bwd_f32dq" if fused_attn_bwd else "sr_qkv_prep_bwd", [P] * 11 + [L, I, I, F32, I, P, P], qkv.data_ptr(),
               _lib.ptr(ve), _lib.ptr(ve_gate), cos2.data_ptr(), sin2.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-              dqkv.data_ptr(), _lib.ptr(dve), _lib.ptr(dvegate), M, H, T, eps, _sp())
+              dqkv.data_ptr(), _lib.ptr(dve), _lib.ptr(dvegate), M, H, T, eps, koff, _lib.ptr(dv_x), _sp())
         da = gemm(dqkv, w_qkv, b_mn=True)
         if mixes is not None:
             dwp = gemm(dqkv, a, a_mn=True, b_mn=True)
@@ -290,8 +293,7 @@ def block_forward(model, block, x_prev, x0, skip, i, j, do_mix, ve_lin, window, 
 
 
 def block_supported(model, block) -> bool:
-    """The fused node covers the limited / two-hour / unlimited feature set; XSA and the key offset of the tiny track
-    go through the op-by-op path."""
+    """The fused node covers every block of the four tracks (head_dim 128, weights large enough to have bf16 shadows);
+    anything else goes through the op-by-op path of `GPT._block_forward`."""
     a = block.attn
-    return (not a.use_key_offset) and model.config.xsa_mode == "off" and a.head_dim == 128 and a.fused is not None \
-        and a.fused["qkv_w16"] is not None
+    return a.head_dim == 128 and a.n_head <= 64 and a.fused is not None and a.fused["qkv_w16"] is not None

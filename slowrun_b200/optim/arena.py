@@ -141,6 +141,9 @@ class ParamArena:
         for g in self.groups.values():
             g.G.zero_()
         self.head_grad.zero_()
+        head = self.model.lm_head.weight
+        if head.grad is not None and head.grad.data_ptr() != self.head_grad.data_ptr():
+            head.grad = None          # autograd-made gradient of a bf16 head on the plain-PyTorch path
         self.small_grads.zero_()
         for p in self.other_params:
             p.grad.zero_()

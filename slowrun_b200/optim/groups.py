@@ -64,9 +64,11 @@ def build_param_groups(model, cfg: TrainConfig):
     # learnable XSA strengths (tiny/train.py:653-655); available to every track when xsa_mode is on
     if model.config.xsa_mode != "off" and hasattr(model, "xsa_alphas"):
         groups.append(dict(A, name="xsa", params=[model.xsa_alphas], lr=lrs["scalar"], betas=(0.9, 0.95), weight_decay=0.0))
+    # MuonEq-R row normalisation of the Nesterov gradient: every track but tiny (train.py:611-613 vs tiny/train.py:770-778)
+    row_norm = cfg.track != "tiny"
     for shape, ps in muon_shape_groups(model):
         groups.append(dict(kind="muon", name=f"muon{tuple(shape)}", params=ps, lr=lrs["matrix"], momentum=cfg.muon_momentum,
-                           ns_steps=cfg.ns_steps, beta2=0.95, weight_decay=wd))
+                           ns_steps=cfg.ns_steps, beta2=0.95, weight_decay=wd, row_norm=row_norm))
     for g in groups:
         g["initial_lr"] = g["lr"]
         g["initial_wd"] = g["weight_decay"]

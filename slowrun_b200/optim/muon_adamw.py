@@ -54,13 +54,18 @@ def newton_schulz_ref(X: torch.Tensor, ns_steps: int) -> torch.Tensor:
     return X
 
 
-def muon_update_ref(G, M, S, momentum, beta2, ns_steps):
+def muon_update_ref(G, M, S, momentum, beta2, ns_steps, row_norm=True):
     """Reference math of train.py:603-634 up to the variance-reduced update U (bf16). Updates M and S in place.
-    G: [n, r, c] fp32 averaged gradient (consumed), M: momentum, S: second moment ([n,r,1] or [n,1,c])."""
+    G: [n, r, c] fp32 averaged gradient (consumed), M: momentum, S: second moment ([n,r,1] or [n,1,c]).
+    `row_norm=False` is the tiny track's variant, which skips the MuonEq-R row normalisation (tiny/train.py:770-778).
+    Matrices that received no gradient in a step (the reference's `active_mask`, tiny/train.py:773-809) are simply
+    not passed in: with a zero mask that code leaves momentum, second moment and parameter of such a matrix
+    untouched, which is what skipping it does."""
     mu = torch.tensor(momentum, dtype=G.dtype)     # the reference forms 1 - mu in the gradient dtype
     M.lerp_(G, (1 - mu).to(G.device))
     g = G.lerp_(M, mu.to(G.device))
-    g /= g.float().norm(dim=-1, keepdim=True).clamp_min(1e-7).to(g.dtype)
+    if row_norm:
+        g /= g.float().norm(dim=-1, keepdim=True).clamp_min(1e-7).to(g.dtype)
     X = g.bfloat16()
     X = X / (X.norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6)
     X = newton_schulz_ref(X, ns_steps)
@@ -143,6 +148,7 @@ class ShardedMuonAdamW:
         self.state = {}
         self.step_count = 0
         self.fused = bool(getattr(comm, "fused", False)) and self.world > 1 and self.cuda and self.arena.symmetric
+        self._inactive = set()      # ids of parameters that receive no gradient in the coming steps
         if self.arena.world_size != self.world:
             raise ValueError(f"arena was laid out for world size {self.arena.world_size}, comm has {self.world}")
         self._init_state()
@@ -181,16 +187,42 @@ class ShardedMuonAdamW:
     def num_owned(self, ga) -> int:
         return min(ga.chunk, max(0, ga.n - self.rank * ga.chunk))
 
+    def set_inactive(self, params):
+        """Declare parameters that get no gradient until further notice (layers a growing model does not run yet,
+        research/universal_transformer/train.py:659-755; the `active_mask` of tiny/train.py:773-809). The step leaves
+        their values and their optimizer state untouched. Pass an empty list to make everything active again."""
+        self._inactive = {id(p) for p in params}
+
+    def _active_runs(self, ga, first, count):
+        """Maximal runs [a, b) of active matrices among stack slots first .. first + count - 1, as offsets from `first`."""
+        if not self._inactive:
+            return [(0, count)] if count > 0 else []
+        runs, start = [], None
+        for j in range(count):
+            on = id(ga.params[first + j]) not in self._inactive
+            if on and start is None:
+                start = j
+            if not on and start is not None:
+                runs.append((start, j))
+                start = None
+        if start is not None:
+            runs.append((start, count))
+        return runs
+
     # ------------------------------------------------------------------ gradient source for AdamW params
     def _grad_of(self, p):
         if p is self.model.lm_head.weight:
+            # CUDA ops accumulate the head gradient into the fp32 arena buffer; the plain-PyTorch path (CPU) leaves an
+            # autograd-made .grad on a bf16 head instead
+            if p.grad is not None and p.grad.data_ptr() != self.arena.head_grad.data_ptr():
+                return p.grad
             return self.arena.head_grad
         return p.grad
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self):
-        if self.fused:
+        if self.fused and not self._inactive:
             return self._step_fused_tuned()
         return self._step_library()
 
@@ -342,11 +374,11 @@ class ShardedMuonAdamW:
             r, c = ga.shape
             n_own = self.num_owned(ga)
             if n_own > 0:
-                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, c_int, cvp, cvp])(
+                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, c_int, c_int, cvp, cvp])(
                     ctypes.cast(comm.peer_ptrs(ga.G), cvp), comm.multicast_ptr(ga.G), W, rank, rank * ga.chunk * r * c,
                     st["momentum"].data_ptr(),
                     st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale,
-                    int(side is not main), status_ptr, _lib.stream_ptr())
+                    int(bool(g.get("row_norm", True))), int(side is not main), status_ptr, _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_pre_multi")
             ev = torch.cuda.Event()
             ev.record(side)
@@ -442,7 +474,8 @@ class ShardedMuonAdamW:
                     comm.reduce_from_peers(ga.G, rank * ga.chunk * r * c, tmp)
                     tmp.mul_(gscale)
                     st["U"][:n_own].copy_(muon_update_ref(tmp, st["momentum"][:n_own], st["second"][:n_own],
-                                                          float(g["momentum"]), float(g["beta2"]), int(g["ns_steps"])))
+                                                          float(g["momentum"]), float(g["beta2"]), int(g["ns_steps"]),
+                                                          bool(g.get("row_norm", True))))
             comm.device_barrier()                                                                  # last
             for g, st in slow:
                 ga = st["arena"]
@@ -495,12 +528,16 @@ class ShardedMuonAdamW:
         W, rank = self.world, self.rank
         arena = self.arena
         head = self.model.lm_head.weight
-        smalls = [p for p in grp["params"] if self.state[id(p)]["small"]]
+        smalls = [p for p in grp["params"] if self.state[id(p)]["small"] and id(p) not in self._inactive]
         if smalls:
             self._adamw_small(grp, smalls, arena.small_grads, gscale)
         for p in grp["params"]:
             st = self.state[id(p)]
             if st["small"]:
+                continue
+            if id(p) in self._inactive:
+                if st.get("h") is not None:
+                    st["h"].wait()
                 continue
             if st.get("h") is not None:
                 st["h"].wait()
@@ -531,22 +568,29 @@ class ShardedMuonAdamW:
         G = st["grad_chunk"] if W > 1 else ga.G
         U = st["U"]
         mu, beta2, ns = float(grp["momentum"]), float(grp["beta2"]), int(grp["ns_steps"])
-        if n_own > 0:
+        row_norm = bool(grp.get("row_norm", True))
+        first = rank * ga.chunk
+        for a0, a1 in self._active_runs(ga, first, n_own):
+            k = a1 - a0
             if self.cuda and "X" in st:
-                X = st["X"][:n_own]
+                X = st["X"][a0:a1]
                 sc = st["scratch"]
-                rc = _lib.fn("sr_muon_pre", [c_void_p] * 4 + [c_int, c_int, c_int, c_float, c_float, c_void_p])(
-                    G.data_ptr(), st["momentum"].data_ptr(), X.data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, mu, gscale,
-                    _lib.stream_ptr())
+                rc = _lib.fn("sr_muon_pre", [c_void_p] * 4 + [c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])(
+                    G[a0:a1].data_ptr(), st["momentum"][a0:a1].data_ptr(), X.data_ptr(), st["sumsq"].data_ptr(), k, r, c, mu,
+                    gscale, int(row_norm), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_pre")
                 Xo = newton_schulz_cuda(X, ns, st["ws"])
                 rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
-                    Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), U.data_ptr(), n_own, r, c,
+                    Xo.data_ptr(), sc[0].data_ptr(), st["second"][a0:a1].data_ptr(), sc[1].data_ptr(), U[a0:a1].data_ptr(), k, r, c,
                     _bf16(beta2), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_post")
             else:
-                g_own = G[:n_own].mul(gscale) if gscale != 1.0 else G[:n_own].clone()
-                U[:n_own].copy_(muon_update_ref(g_own, st["momentum"][:n_own], st["second"][:n_own], mu, beta2, ns))
+                g_own = G[a0:a1].mul(gscale) if gscale != 1.0 else G[a0:a1].clone()
+                U[a0:a1].copy_(muon_update_ref(g_own, st["momentum"][a0:a1], st["second"][a0:a1], mu, beta2, ns, row_norm))
+        if self._inactive and n_own > 0:
+            for j in range(n_own):                       # an inactive matrix contributes a zero update
+                if id(ga.params[first + j]) in self._inactive:
+                    U[j].zero_()
         lr_eff = float(grp["lr"]) * max(1.0, r / c) ** 0.5
         wd = float(grp["weight_decay"])
         if W > 1:
@@ -558,16 +602,18 @@ class ShardedMuonAdamW:
             if h is not None:
                 h.wait()
             Uall = st["U_all"][:ga.n] if W > 1 else U[:ga.n]
-            if self.cuda and ga.W16 is not None:
-                lr_b = _bf16(lr_eff)
-                lrwd_b = _bf16(lr_b * _bf16(wd))
-                rc = _lib.fn("sr_muon_apply", [c_void_p] * 3 + [c_long, c_float, c_float, c_void_p])(
-                    ga.P.data_ptr(), Uall.data_ptr(), ga.W16.data_ptr(), ga.P.numel(), lr_b, lrwd_b, _lib.stream_ptr())
-                _lib.check_rc(rc, "sr_muon_apply")
-            else:
-                muon_apply_ref(ga.P, Uall, lr_eff, wd)
-                if ga.W16 is not None:
-                    ga.W16.copy_(ga.P)
+            for a0, a1 in self._active_runs(ga, 0, ga.n):     # one run (everything) unless parameters were declared inactive
+                Pr, Ur = ga.P[a0:a1], Uall[a0:a1]
+                if self.cuda and ga.W16 is not None:
+                    lr_b = _bf16(lr_eff)
+                    lrwd_b = _bf16(lr_b * _bf16(wd))
+                    rc = _lib.fn("sr_muon_apply", [c_void_p] * 3 + [c_long, c_float, c_float, c_void_p])(
+                        Pr.data_ptr(), Ur.data_ptr(), ga.W16[a0:a1].data_ptr(), Pr.numel(), lr_b, lrwd_b, _lib.stream_ptr())
+                    _lib.check_rc(rc, "sr_muon_apply")
+                else:
+                    muon_apply_ref(Pr, Ur, lr_eff, wd)
+                    if ga.W16 is not None:
+                        ga.W16[a0:a1].copy_(Pr)
         pending.append(fin)
 
     # ------------------------------------------------------------------ (de)serialisation of the owned state

@@ -7,6 +7,7 @@ Formulas follow the reference scripts (limited: train.py:1083-1111, 1166-1182; t
 from __future__ import annotations
 
 import math
+import re
 from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
@@ -25,33 +26,26 @@ class WindowStage:
     long_window: int
 
 
+_STAGE_RE = re.compile(r"^\s*(\d+)\s*(?:-\s*(\d+)\s*)?:\s*(\d+)\s*,\s*(\d+)\s*$")
+
+
 def parse_window_schedule(spec: str, max_seq_len: int) -> Tuple[WindowStage, ...]:
-    """'1-6:256,768;7-13:768,1792;...' -> contiguous stages starting at epoch 1."""
-    if not spec:
-        return ()
-    stages, prev_end = [], 0
-    for raw in spec.split(";"):
-        raw = raw.strip()
-        if not raw:
-            continue
-        if ":" not in raw:
-            raise ValueError(f"Invalid --window-schedule stage '{raw}': expected 'start-end:short,long'")
-        ep, win = (s.strip() for s in raw.split(":", 1))
-        a, b = ep.split("-", 1) if "-" in ep else (ep, ep)
-        if "," not in win:
-            raise ValueError(f"Invalid --window-schedule stage '{raw}': expected 'short,long'")
-        sw, lw = (int(v) for v in win.split(",", 1))
-        a, b = int(a), int(b)
-        if a <= 0 or b < a:
-            raise ValueError(f"Invalid epoch range '{ep}' in --window-schedule")
-        if sw <= 0 or lw <= 0 or sw > lw:
-            raise ValueError(f"Invalid windows {sw},{lw} in --window-schedule")
-        if lw > max_seq_len:
-            raise ValueError(f"Long window must be <= sequence length ({max_seq_len}), got {lw}")
-        if a != prev_end + 1:
-            raise ValueError("--window-schedule stages must be contiguous and start at epoch 1")
-        stages.append(WindowStage(a, b, sw, lw))
-        prev_end = b
+    """Attention-window stages of the two-hour track (two_hour/train.py:143-199). `spec` is a ';'-separated list of
+    `first[-last]:short,long` entries, e.g. "1-6:256,768;7-13:768,1792;14-22:1280,2048"; epochs are 1-based and the
+    stages must tile the epoch axis from 1 without gaps. Windows are in tokens, short <= long <= max_seq_len."""
+    stages = []
+    for entry in filter(None, (e.strip() for e in (spec or "").split(";"))):
+        m = _STAGE_RE.match(entry)
+        if m is None:
+            raise ValueError(f"window schedule entry {entry!r} is not of the form first[-last]:short,long")
+        first, last, short, long_ = int(m[1]), int(m[2] or m[1]), int(m[3]), int(m[4])
+        expected = stages[-1].end_epoch + 1 if stages else 1
+        if first != expected or last < first:
+            raise ValueError(f"window schedule entry {entry!r}: stages must cover epochs {expected}, {expected + 1}, ... "
+                             "in order without gaps")
+        if not 0 < short <= long_ <= max_seq_len:
+            raise ValueError(f"window schedule entry {entry!r}: need 0 < short <= long <= {max_seq_len}")
+        stages.append(WindowStage(first, last, short, long_))
     return tuple(stages)
 
 

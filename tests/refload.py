@@ -2,8 +2,8 @@
 
 The reference scripts run their whole training at import, so tests cut out the self-contained sections (model,
 optimizer math, loader, schedules) by their banner comments and exec them with the few globals they read. The
-source tree is looked up at baseline/_ref (the copy that travels with the repo), then at the directory named by
-SLOWRUN_REFERENCE_DIR; tests that need it are skipped when neither exists.
+source tree is looked up at baseline/_ref (the copy that travels with the repo), then at the directory named by the
+environment variable SLOWRUN_REFERENCE_DIR; tests that need it are skipped when neither exists.
 """
 import math
 import os
@@ -21,8 +21,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def ref_root():
-    for p in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("SLOWRUN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))):
-        if os.path.isfile(os.path.join(p, "train.py")):
+    for p in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("SLOWRUN_REFERENCE_DIR")):
+        if p and os.path.isfile(os.path.join(p, "train.py")):
             return p
     return None
 
@@ -68,4 +68,31 @@ def load_limited(n_layer=4, n_embd=128, n_head=4, seq_len=64, mtp_weight=0.3, ih
     exec(model_src, ns)
     exec(opt_src, ns)
     exec(loader_src, ns)
+    return SimpleNamespace(**ns)
+
+
+def load_unlimited_loaders():
+    """The data-loading section of the reference's unlimited script (unlimited/train.py:758-965): DataLoader,
+    DDPValLoader and the fitness carve, on CPU."""
+    root = ref_root()
+    if root is None:
+        return None
+    src = open(os.path.join(root, "unlimited", "train.py")).read()
+    sec = _section(src, "# Data loading (flat tokens + doc_starts format", "# =============================================================================\n# Evaluation helpers")
+    ns = dict(torch=torch, np=np, math=math)
+    exec(sec, ns)
+    return SimpleNamespace(**ns)
+
+
+def load_tiny_optimizer():
+    """The optimizer section of the reference's tiny script (tiny/train.py:748-946): its Muon step without row
+    normalisation and with the active mask, run eagerly on CPU."""
+    root = ref_root()
+    if root is None:
+        return None
+    src = open(os.path.join(root, "tiny", "train.py")).read()
+    sec = _section(src, "# Polar Express coefficients for orthogonalization", "# =============================================================================\n# Dataloader")
+    sec = sec.replace("@torch.compile(dynamic=False, fullgraph=True)\n", "")
+    ns = dict(torch=torch, dist=torch.distributed, Tensor=torch.Tensor)
+    exec(sec, ns)
     return SimpleNamespace(**ns)

@@ -254,8 +254,8 @@ def test_muon_cuda_path_matches_oracle(shape):
     sc = torch.empty(3, n, ln, device="cuda")
     sumsq = torch.empty(n, device="cuda")
     cv, ci, cf = _lib.c_void_p, _lib.c_int, _lib.c_float
-    _lib.check_rc(_lib.fn("sr_muon_pre", [cv] * 4 + [ci, ci, ci, cf, cf, cv])(
-        G.data_ptr(), Mo.data_ptr(), X.data_ptr(), sumsq.data_ptr(), n, r, c, 0.9, 1.0, _lib.stream_ptr()), "pre")
+    _lib.check_rc(_lib.fn("sr_muon_pre", [cv] * 4 + [ci, ci, ci, cf, cf, ci, cv])(
+        G.data_ptr(), Mo.data_ptr(), X.data_ptr(), sumsq.data_ptr(), n, r, c, 0.9, 1.0, 1, _lib.stream_ptr()), "pre")
     Xo = newton_schulz_cuda(X, 5, ws)
     from slowrun_b200.optim.muon_adamw import _bf16
     _lib.check_rc(_lib.fn("sr_muon_post", [cv] * 5 + [ci, ci, ci, cf, cv])(
@@ -347,12 +347,14 @@ def test_graft_smoke():
     g.smoke()
 
 
-def test_fused_block_node_matches_op_by_op_path():
-    """Same CUDA model, block run as one autograd node vs. op by op: loss and every gradient must agree."""
+@pytest.mark.parametrize("track", ["limited", "tiny"])
+def test_fused_block_node_matches_op_by_op_path(track):
+    """Same CUDA model, block run as one autograd node vs. op by op: loss and every gradient must agree. The tiny
+    configuration adds the key offset (layer 3 is a long-window layer) and exclusive self-attention on every layer."""
     from slowrun_b200.config import track_defaults
     from slowrun_b200.models.gpt import build_model
     from slowrun_b200.ops import _lib
-    cfg = track_defaults("limited")
+    cfg = track_defaults(track)
     m = cfg.model
     m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 4, 256, 2, 2, 256
     m.dropout, m.stoch_depth = 0.0, 0.0
@@ -360,17 +362,24 @@ def test_fused_block_node_matches_op_by_op_path():
     torch.manual_seed(1)
     with torch.no_grad():
         for n, p in model.named_parameters():
-            if any(s in n for s in ("gate", "mix", "lambdas", "skip")):
+            if any(s in n for s in ("gate", "mix", "lambdas", "skip", "xsa")):
                 p.add_(0.05 * torch.randn_like(p))
+            if track == "tiny" and "c_proj" in n:       # zero-initialised in this track: nothing would flow back
+                p.add_(0.02 * torch.randn_like(p))
+        if track == "tiny":
+            model.xsa_alphas.add_(0.5)
     model.arena.refresh_shadows()
-    model.set_dupe_layers(2, 3, 1)
+    if track == "limited":
+        model.set_dupe_layers(2, 3, 1)
     idx = torch.randint(0, 50257, (2, 256), device="cuda")
     tgt = torch.randint(0, 50257, (2, 256), device="cuda")
+    kw = dict(num_iterations=2, mtp_weights=torch.tensor([1.0, 0.5, 0.25], device="cuda")) if track == "tiny" else {}
     res = {}
     for fused in (True, False):
         model.use_fused_blocks = fused
         model.zero_grad_arena()
-        loss, _ = model(idx, tgt)
+        out = model(idx, tgt, **kw)
+        loss = out[0] if isinstance(out, tuple) else out
         loss.backward()
         torch.cuda.synchronize(); _lib.check_status()
         res[fused] = (loss.item(), {n: (model.arena.head_grad if n == "lm_head.weight" else p.grad).clone()

@@ -4,7 +4,7 @@ import os
 import pytest
 import torch
 
-from slowrun_b200.data.loader import TokenLoader
+from slowrun_b200.data.loader import EnsembleTokenLoader, TokenLoader
 from slowrun_b200.data.synthetic import write_synthetic_corpus
 from tests import refload
 
@@ -40,3 +40,45 @@ def test_batches_equal_reference(corpus, doc_shuffle, world, rank):
         mx, my, me = next(m)
         assert re == me, i
         assert torch.equal(rx, mx) and torch.equal(ry, my), i
+
+
+@pytest.mark.parametrize("world,rank", [(1, 0), (2, 1)])
+def test_ensemble_loader_equals_reference_unlimited_loader(corpus, world, rank):
+    ref = refload.load_unlimited_loaders()
+    if ref is None:
+        pytest.skip("reference source not available")
+    B, T, seed, fit = 2, 256, 3, 20_000
+    docs, dseed = ref._load_new_format_file(corpus[0])
+    fit_docs, train_docs, _ = ref._carve_fitness_docs(docs, fit)
+    r = ref.DataLoader(None, B, T, device="cpu", seed=seed, dp_rank=rank, dp_world_size=world, doc_shuffle=True,
+                       doc_tokens=train_docs, default_shuffle_seed=dseed)
+    m = EnsembleTokenLoader(corpus[0], B, T, device="cpu", seed=seed, rank=rank, world_size=world, fitness_tokens=fit)
+    assert r.num_steps == m.num_steps and r.total_tokens == m.total_tokens
+    for i in range(2 * r.num_steps + 3):
+        rx, ry, re = next(r)
+        mx, my, me = next(m)
+        assert re == me, i
+        assert torch.equal(rx, mx) and torch.equal(ry, my), i
+    # the held-out slice, read the way the reference's p(ground truth) cache reads it
+    fseqs = ref._build_seqs_from_docs(fit_docs, T + 1)
+    rv = ref.DDPValLoader(None, 4, T, rank=rank, world_size=world, device="cpu", seed=0, seqs=fseqs)
+    mv = EnsembleTokenLoader(corpus[0], 4, T, device="cpu", seed=0, rank=rank, world_size=world, fitness_tokens=fit,
+                             fitness_only=True)
+    assert rv.num_steps == mv.num_steps
+    for i in range(rv.num_steps):
+        rx, ry, _ = next(rv)
+        mx, my, _ = next(mv)
+        assert torch.equal(rx, mx) and torch.equal(ry, my), i
+
+
+def test_loader_state_round_trip(corpus):
+    a = TokenLoader(corpus[0], 2, 256, device="cpu", doc_shuffle=True)
+    for _ in range(a.num_steps + 5):
+        next(a)
+    st = a.state()
+    b = TokenLoader(corpus[0], 2, 256, device="cpu", doc_shuffle=True)
+    b.restore(st)
+    for _ in range(a.num_steps):
+        xa, ya, ea = next(a)
+        xb, yb, eb = next(b)
+        assert ea == eb and torch.equal(xa, xb) and torch.equal(ya, yb)

@@ -119,3 +119,63 @@ def test_tiny_groups():
     assert names == ["lm_head", "wte", "resid", "x0", "skip", "attn_gate", "xsa"]
     muon_shapes = [tuple(g["params"][0].shape) for g in groups if g["kind"] == "muon"]
     assert (4, 12) not in muon_shapes and (4, 32) in muon_shapes
+
+
+@pytest.mark.parametrize("shape", [(3, 64, 32), (2, 32, 96)])
+def test_tiny_muon_math_matches_reference_including_the_active_mask(shape):
+    """tiny/train.py:770-809: no row normalisation before Newton-Schulz, and a matrix whose mask is off keeps its
+    parameter, momentum and second moment."""
+    ref = refload.load_tiny_optimizer()
+    if ref is None:
+        pytest.skip("reference source not available")
+    torch.manual_seed(0)
+    n, r, c = shape
+    G = torch.randn(n, r, c) * 0.02
+    P = torch.randn(n, r, c) * 0.05
+    M = torch.randn(n, r, c) * 0.01
+    S = torch.rand(n, r, 1) * 1e-3 if r >= c else torch.rand(n, 1, c) * 1e-3
+    lr, wd, mu, b2 = 0.02, 0.8, 0.9, 0.95
+    active = torch.ones(n, 1, 1, dtype=torch.bool)
+    active[1] = False
+    rG, rP, rM, rS = G.clone(), P.clone(), M.clone(), S.clone()
+    rG[1].zero_()
+    red_dim = -1 if r >= c else -2
+    ref.muon_step_fused(rG, rP, rM, rS, torch.tensor(mu), torch.tensor(lr), torch.tensor(wd), torch.tensor(b2), active, 5, red_dim)
+    # ours: the inactive matrix is left out of the call
+    mP, mM, mS = P.clone(), M.clone(), S.clone()
+    for i in (0,) + tuple(range(2, n)):
+        U = muon_update_ref(G[i:i + 1].clone(), mM[i:i + 1], mS[i:i + 1], mu, b2, 5, row_norm=False)
+        muon_apply_ref(mP[i:i + 1], U, lr, wd)
+    assert torch.equal(rP[1], P[1]) and torch.equal(rM[1], M[1]) and torch.equal(rS[1], S[1])
+    assert torch.equal(mP[1], P[1])
+    assert torch.allclose(rM, mM, rtol=1e-6, atol=1e-8)
+    assert torch.allclose(rS, mS, rtol=2e-2, atol=1e-7)
+    rel = (rP - mP).norm() / (rP - P).norm()
+    assert rel < 0.03, rel.item()
+    # and the row-normalised variant is measurably different, so the switch is not a no-op
+    U_rn = muon_update_ref(G[:1].clone(), M[:1].clone(), S[:1].clone(), mu, b2, 5, row_norm=True)
+    U_no = muon_update_ref(G[:1].clone(), M[:1].clone(), S[:1].clone(), mu, b2, 5, row_norm=False)
+    assert (U_rn.float() - U_no.float()).norm() / U_no.float().norm() > 0.02
+
+
+def test_tiny_track_groups_skip_row_norm_and_inactive_parameters_are_left_alone():
+    cfg = _small_cfg("tiny")
+    torch.manual_seed(0)
+    model = build_model(cfg.model, "cpu")
+    groups = build_param_groups(model, cfg)
+    assert all(g["row_norm"] is False for g in groups if g["kind"] == "muon")
+    assert all(g["row_norm"] is True for g in build_param_groups(build_model(_small_cfg().model, "cpu"), _small_cfg()) if g["kind"] == "muon")
+    opt = ShardedMuonAdamW(model, groups, TorchComm())
+    frozen = [model.transformer.h[1].mlp.c_fc.weight, model.transformer.h[2].attn.c_q.weight, model.x0_lambdas]
+    opt.set_inactive(frozen)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    idx = torch.randint(0, 50257, (2, 64)); tgt = torch.randint(0, 50257, (2, 64))
+    for _ in range(2):
+        loss = model(idx, tgt, num_iterations=1, mtp_weights=torch.tensor([1.0, 0.5, 0.25]))
+        loss.backward()
+        opt.step()
+        model.zero_grad_arena()
+    frozen_ids = {id(p) for p in frozen}
+    for n, p in model.named_parameters():
+        same = torch.equal(before[n], p.detach())
+        assert same == (id(p) in frozen_ids), n
