@@ -260,6 +260,48 @@ __global__ void quant_fp8_t_kernel(const __nv_bfloat16* __restrict__ x, uint8_t*
   }
 }
 
+// out[r, c] = fp8(x[r, c] * f_r) and out_t[c, r] = the same value, f_r = row_scale[r] * mult / *div_ptr: the logit
+// gradient of the fused head in both operand layouts its two fp8 backward products need (K-major for each). 64 x 64
+// tiles through shared memory so that both outputs are written in 64-byte row pieces.
+__global__ void quant_fp8_dual_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ row_scale,
+                                      const float* __restrict__ div_ptr, float mult, uint8_t* __restrict__ out,
+                                      uint8_t* __restrict__ out_t, int rows, int cols, long ldx, long ldo, long ldt,
+                                      int e5m2) {
+  __shared__ uint8_t tile[64][65];
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const float m = mult / (div_ptr ? *div_ptr : 1.f);
+  for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) {
+    const int rr = i / 32, cc = (i % 32) * 2;
+    float a = 0.f, b = 0.f;
+    if (r0 + rr < rows) {
+      const float f = (row_scale ? row_scale[r0 + rr] : 1.f) * m;
+      if (c0 + cc < cols) a = f * __bfloat162float(x[(size_t)(r0 + rr) * ldx + c0 + cc]);
+      if (c0 + cc + 1 < cols) b = f * __bfloat162float(x[(size_t)(r0 + rr) * ldx + c0 + cc + 1]);
+    }
+    const uint16_t q = cvt_fp8x2(a, b, e5m2);
+    tile[rr][cc] = (uint8_t)(q & 0xff);
+    tile[rr][cc + 1] = (uint8_t)(q >> 8);
+    if (r0 + rr < rows && c0 + cc + 1 < cols) {
+      *reinterpret_cast<uint16_t*>(out + (size_t)(r0 + rr) * ldo + c0 + cc) = q;
+    } else if (r0 + rr < rows && c0 + cc < cols) {
+      out[(size_t)(r0 + rr) * ldo + c0 + cc] = (uint8_t)(q & 0xff);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
+    const int cc = i / 16, rr = (i % 16) * 4;
+    if (c0 + cc >= cols) continue;
+    uint8_t* dst = out_t + (size_t)(c0 + cc) * ldt + r0 + rr;
+    if (r0 + rr + 3 < rows) {
+      *reinterpret_cast<uint32_t*>(dst) = (uint32_t)tile[rr][cc] | ((uint32_t)tile[rr + 1][cc] << 8) |
+                                          ((uint32_t)tile[rr + 2][cc] << 16) | ((uint32_t)tile[rr + 3][cc] << 24);
+    } else {
+      for (int j = 0; j < 4; ++j)
+        if (r0 + rr + j < rows) dst[j] = tile[rr + j][cc];
+    }
+  }
+}
+
 inline int last_rc() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
 
 }  // namespace
@@ -339,5 +381,19 @@ extern "C" int sr_quant_fp8(const void* x, void* out, long rows, int cols, long 
     quant_fp8_t_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(out),
                                                  (int)rows, cols, ldx, ldo, inv, e5m2);
   }
+  return last_rc();
+}
+
+// out [rows, ldo] and out_t [cols, ldt] (both fp8) = x[r, c] * row_scale[r] * mult / (*div_ptr), row_scale and div_ptr
+// optional. ldo and ldt must be multiples of 4 (16 for use as GEMM operands), cols even.
+extern "C" int sr_quant_fp8_dual(const void* x, const float* row_scale, const float* div_ptr, float mult, void* out,
+                                 void* out_t, long rows, int cols, long ldx, long ldo, long ldt, int e5m2,
+                                 cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 2 || ldo % 2 || ldt % 4) return -2;
+  dim3 grid((cols + 63) / 64, (unsigned)((rows + 63) / 64));
+  quant_fp8_dual_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), row_scale, div_ptr, mult,
+                                                  reinterpret_cast<uint8_t*>(out), reinterpret_cast<uint8_t*>(out_t),
+                                                  (int)rows, cols, ldx, ldo, ldt, e5m2);
   return last_rc();
 }

@@ -511,9 +511,15 @@ def _fused_head_ok(x2, w, w_t, cap, fp8):
             and w.stride(-1) == 1 and x2.dtype == torch.bfloat16)
 
 
+FP8_GRAD_MULT = 256.0           # the logit gradient (in probability units, |.| <= sum of target weights) is stored as
+                                # e5m2(256 * value): probabilities down to 6e-8 stay representable
+
+
 def _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over_rows, fp8, want_grad):
-    """Runs sr_lmhead_ce_fwd. Returns (loss scalar, loss_rows, E', rscale, Xs); the last three are None when
-    `want_grad` is False (evaluation: nothing of size [tokens, vocab] is allocated at all)."""
+    """Runs sr_lmhead_ce_fwd. Returns (loss scalar, loss_rows, saved) where `saved` holds what the backward needs
+    (None when `want_grad` is False: evaluation allocates nothing of size [tokens, vocab] at all).
+      bf16: saved = (E', rscale, Xs)                         dx = diag(rscale) E' W,  dW += E'^T Xs
+      fp8 : saved = (G8, G8^T, X8^T, W8 as [d, V], scale)    both backward products on fp8 operands as well"""
     M, K = x2.shape
     N = w.size(1) if w_t else w.size(0)
     dev = x2.device
@@ -526,11 +532,12 @@ def _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over
     if want_grad:
         E = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
         rscale = torch.empty(M, dtype=torch.float32, device=dev)
-        Xs = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+        if not fp8:
+            Xs = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
     if fp8:
         from .gemm import quantize_fp8
         xa = quantize_fp8(x2, FP8_X_SCALE)
-        wa = quantize_fp8(w, FP8_W_SCALE, transpose=w_t)        # always [N, K]
+        wa = quantize_fp8(w, FP8_W_SCALE, transpose=w_t)        # [N, K]
         alpha, b_mn, lda, ldb = FP8_X_SCALE * FP8_W_SCALE, 0, xa.stride(0), wa.stride(0)
     else:
         xa, wa, alpha, b_mn, lda, ldb = x2, w, 1.0, int(w_t), x2.stride(0), w.stride(0)
@@ -538,34 +545,65 @@ def _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over
           alpha, t.data_ptr(), _lib.ptr(weights), n_predict, vocab, cap, int(mean_over_rows), scal.data_ptr(),
           partials.data_ptr(), ztgt.data_ptr(), loss_rows.data_ptr(), scal.data_ptr() + 4, _lib.ptr(rscale),
           x2.data_ptr(), x2.stride(0), _lib.ptr(Xs), 0, _lib.status_buffer(dev).data_ptr(), _lib.stream_ptr())
-    return scal[1], loss_rows, E, rscale, Xs
+    if not want_grad:
+        return scal[1], loss_rows, None
+    if not fp8:
+        return scal[1], loss_rows, (E, rscale, Xs)
+    # fp8 backward operands, every one K-major: the gradient in both layouts (one pass over E'), x^T, and W as [d, V]
+    from .gemm import fp8_empty
+    G8 = fp8_empty((M, N), torch.float8_e5m2, dev)
+    G8T = fp8_empty((N, M), torch.float8_e5m2, dev)
+    _call("sr_quant_fp8_dual", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_long, c_int, c_long, c_long, c_long,
+                                c_int, c_void_p],
+          E.data_ptr(), rscale.data_ptr(), scal.data_ptr(), FP8_GRAD_MULT, G8.data_ptr(), G8T.data_ptr(), M, N, E.stride(0),
+          G8.stride(0), G8T.stride(0), 1, _lib.stream_ptr())
+    del E
+    X8T = quantize_fp8(x2, FP8_X_SCALE, transpose=True)         # [K, M]
+    Wd = quantize_fp8(w, FP8_W_SCALE, transpose=not w_t)        # [K, N]: the B operand of dx = G W
+    return scal[1], loss_rows, (G8, G8T, X8T, Wd, scal[0:1])
 
 
 class _FusedLMHeadLossFn(Function):
     """lm-head + soft-capped CE on the fused kernel: forward leaves E' (bf16, the logit gradient up to the per-row
     factor `rscale`) and the pre-scaled activations; backward is dx = diag(rscale) E' W (row factor in the GEMM
-    epilogue) and dW += E'^T (rscale * x), both scaled by the upstream scalar on the device."""
+    epilogue) and dW += E'^T (rscale * x), both scaled by the upstream scalar on the device. With `fp8` the forward
+    product runs on e4m3 operands and the two backward products on the e5m2 gradient and e4m3 x / W (the precision
+    recipe of the reference's tiny track, tiny/cuda_kernels.py:338-414), each with fp32 accumulation."""
 
     @staticmethod
     def forward(ctx, x, w, grad_acc, w_t, targets, cap, vocab, weights, n_predict, mean_over_rows, fp8):
         K = x.size(-1)
         x2 = _c(x.reshape(-1, K))
         t = _c(targets.reshape(-1))
-        loss, _, E, rscale, Xs = _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over_rows, fp8, True)
-        ctx.save_for_backward(w, E, rscale, Xs)
-        ctx.grad_acc, ctx.w_t, ctx.xshape = grad_acc, w_t, x.shape
+        loss, _, saved = _fused_head_forward(x2, w, w_t, t, cap, vocab, weights, n_predict, mean_over_rows, fp8, True)
+        ctx.save_for_backward(*saved)
+        ctx.grad_acc, ctx.w_t, ctx.xshape, ctx.fp8, ctx.w = grad_acc, w_t, x.shape, fp8, (None if fp8 else w)
         return loss
 
     @staticmethod
     def backward(ctx, g):
-        w, E, rscale, Xs = ctx.saved_tensors
-        w_t = ctx.w_t
+        w_t, acc = ctx.w_t, ctx.grad_acc
         g = _c(g.float())
-        dx = None
+        dx = dw = None
+        if ctx.fp8:
+            from .gemm import gemm_fp8
+            G8, G8T, X8T, Wd, scale = ctx.saved_tensors
+            gs = (g * scale).reshape(())                        # upstream scalar times 1 / #tokens, on the device
+            if ctx.needs_input_grad[0]:
+                dx = gemm_fp8(G8, Wd, alpha=FP8_W_SCALE / FP8_GRAD_MULT, alpha_t=gs).view(ctx.xshape)
+            a = FP8_X_SCALE / FP8_GRAD_MULT
+            if acc is not None:
+                if w_t:
+                    gemm_fp8(X8T, G8T, out=acc, cin=acc, alpha=a, beta=1.0, alpha_t=gs)
+                else:
+                    gemm_fp8(G8T, X8T, out=acc, cin=acc, alpha=a, beta=1.0, alpha_t=gs)
+            elif ctx.needs_input_grad[1]:
+                dw = gemm_fp8(X8T, G8T, alpha=a, alpha_t=gs) if w_t else gemm_fp8(G8T, X8T, alpha=a, alpha_t=gs)
+            return (dx, dw) + (None,) * 9
+        E, rscale, Xs = ctx.saved_tensors
+        w = ctx.w
         if ctx.needs_input_grad[0]:
             dx = gemm(E, w, b_mn=not w_t, alpha_t=g, row_scale=rscale).view(ctx.xshape)
-        acc = ctx.grad_acc
-        dw = None
         if acc is not None:
             if w_t:
                 gemm(Xs, E, out=acc, cin=acc, a_mn=True, b_mn=True, beta=1.0, alpha_t=g)
@@ -580,8 +618,8 @@ def lm_head_loss(x, w, targets, cap, vocab, grad_acc=None, w_t=False, weights=No
     """Mean soft-capped CE of (x @ W^T)[..., :vocab] against targets (ignore_index -1).
     With `weights` (fp32 tensor of k entries) row i is scored against targets[i..i+k-1] of the flattened batch and the
     mean runs over all rows (the tiny track's shared-head multi-token loss, tiny/train.py:682-696).
-    `fp8`: forward product on e4m3 operands with the reference's static per-tensor scales (tiny/cuda_kernels.py:340-352);
-    the two backward products stay in bf16."""
+    `fp8`: all three products on fp8 operands (e4m3 x and W with the reference's static per-tensor scales, e5m2 logit
+    gradient; tiny/cuda_kernels.py:340-412), fp32 accumulation."""
     if x.is_cuda:
         npred = 1 if weights is None else int(weights.numel())
         wts = None if weights is None else _c(weights.float())

@@ -114,13 +114,21 @@ _ARGTYPES_FP8 = _ARGTYPES[:16] + [_lib.c_int] * 4 + [_lib.c_float, _lib.c_float,
                                                      _lib.c_int, _lib.c_int, _lib.c_void_p, _lib.c_void_p]
 
 
+def fp8_empty(shape, dtype, device) -> torch.Tensor:
+    """Uninitialised 2-D fp8 tensor whose row stride is a multiple of 16 bytes (what a TMA operand needs); the view
+    returned has exactly `shape`."""
+    rows, cols = shape
+    ld = (cols + 15) // 16 * 16
+    return torch.empty((rows, ld), dtype=dtype, device=device)[:, :cols]
+
+
 def quantize_fp8(x: torch.Tensor, scale: float, transpose: bool = False, dtype=torch.float8_e4m3fn) -> torch.Tensor:
     """fp8(x / scale) of a bf16 matrix [R, C] (saturating); `transpose` returns the [C, R] layout. Per-tensor static
     scales as in the reference's fp8 head (tiny/cuda_kernels.py:340-343)."""
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
         raise TypeError("quantize_fp8 expects a 2-D bf16 tensor with a contiguous last dimension")
     R, C = x.shape
-    out = torch.empty((C, R) if transpose else (R, C), dtype=dtype, device=x.device)
+    out = fp8_empty((C, R) if transpose else (R, C), dtype, x.device)
     if not x.is_cuda:
         src = (x.float() / scale).clamp(-torch.finfo(dtype).max, torch.finfo(dtype).max).to(dtype)
         out.copy_(src.t() if transpose else src)

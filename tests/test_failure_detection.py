@@ -3,7 +3,9 @@
 * a rank that leaves between steps: the surviving rank's next collective ends with an error inside the process-group
   timeout instead of hanging (Gloo ranks on CPU);
 * a failing launcher return code and a non-zero kernel status word are turned into exceptions by the loader
-  (`ops/_lib.check_rc`, `check_status` semantics exercised on a fake status buffer).
+  (`ops/_lib.check_rc`, `check_status` semantics exercised on a fake status buffer);
+* on a GPU, a device-side bounded wait is made to run out (a flag that nothing sets, a limit of milliseconds): the
+  kernel returns, the status word names the wait, the kernels that depend on it skip their work.
 The reference has no failure handling at all (its collectives use the default 10-minute NCCL timeout, train.py:956).
 """
 import os
@@ -93,3 +95,45 @@ def test_reference_arm_reports_unavailable_without_a_gpu():
     assert r.returncode == 0
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+@pytest.mark.gpu
+def test_device_side_peer_wait_runs_out_and_the_step_is_skipped():
+    """A peer that never arrives, on ONE GPU and without any fault: the barrier is launched for a world of two whose
+    second flag word nobody writes, with a wait limit of a few milliseconds. The kernel must return by itself, the
+    status word must say which wait gave up (code 2 = peer wait, site 900, detail = the missing peer), a consumer
+    kernel launched after it must not touch its output, and once the word is cleared the next launches work."""
+    import ctypes
+    from slowrun_b200.ops import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    flags0 = torch.zeros(64, dtype=torch.int32, device=dev)     # "rank 0" (this process)
+    flags1 = torch.zeros(64, dtype=torch.int32, device=dev)     # stands in for a peer that is never launched
+    ptrs = (ctypes.c_ulonglong * 2)(flags0.data_ptr(), flags1.data_ptr())
+    status = _lib.status_buffer(dev)
+    barrier = _lib.fn("sr_peer_barrier", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p,
+                                          ctypes.c_ulonglong, ctypes.c_void_p])
+    t0 = time.time()
+    assert barrier(ctypes.cast(ptrs, ctypes.c_void_p), 0, 2, 1, status.data_ptr(), 5_000_000, _lib.stream_ptr()) == 0
+    # a consumer of the "collective": sums two sources into `out`; it must see the failed barrier and leave `out` alone
+    src = torch.ones(1024, device=dev)
+    out = torch.full((1024,), -7.0, device=dev)
+    sptrs = (ctypes.c_ulonglong * 2)(src.data_ptr(), src.data_ptr())
+    reduce = _lib.fn("sr_reduce_multi", [ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_long,
+                                         ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p])
+    assert reduce(ctypes.cast(sptrs, ctypes.c_void_p), 2, 0, out.data_ptr(), 1024, 0, status.data_ptr(), _lib.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0, "the wait limit was not honoured"
+    assert int(flags1[0]) == 1, "this rank did announce itself to the peer"
+    assert float(out[0]) == -7.0 and float(out[-1]) == -7.0, "a consumer ran after a failed barrier"
+    with pytest.raises(_lib.KernelStatusError, match="code=2 site=900") as ei:
+        _lib.check_status(dev)
+    assert "detail=1" in str(ei.value)
+    # cleared: the same launches now go through (the peer's flag is written by hand, as its barrier kernel would)
+    flags0[1] = 2
+    assert barrier(ctypes.cast(ptrs, ctypes.c_void_p), 0, 2, 2, status.data_ptr(), 5_000_000, _lib.stream_ptr()) == 0
+    assert reduce(ctypes.cast(sptrs, ctypes.c_void_p), 2, 0, out.data_ptr(), 1024, 0, status.data_ptr(), _lib.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    assert float(out[0]) == 2.0

@@ -104,25 +104,28 @@ def test_fused_head_matches_oracle_and_the_unfused_path(M, d, V, Vpad, weights, 
     assert abs(loss - lref.item()) <= abs(res[False][0] - lref.item()) + 1e-3 * abs(lref.item())
 
 
-def test_fused_head_fp8_forward_tracks_the_quantised_oracle():
+@pytest.mark.parametrize("M,w_t", [(700, True), (1024, False)])
+def test_fused_head_fp8_tracks_the_quantised_oracle(M, w_t):
+    """Forward against the oracle evaluated on the operands as the kernel sees them (e4m3 values times the static
+    scales); backward (e5m2 gradient, e4m3 x and W, fp32 accumulation) against the fp32 gradients to fp8 accuracy."""
     from slowrun_b200.ops import functional as ops
-    M, d, Vpad = 700, 512, 1536
+    d, Vpad = 512, 1536
     x = _bf(M, d, seed=21)
-    w = _bf(d, Vpad, scale=0.004, seed=22)      # stored [d, V] as in the tiny track
+    w = _bf(d, Vpad, scale=0.004, seed=22) if w_t else _bf(Vpad, d, scale=0.004, seed=22)   # [d, V] as in the tiny track
     tgt = torch.randint(0, Vpad, (M,), device="cuda")
     wt = torch.tensor([1.0, 0.5, 0.25], device="cuda")
     xa = x.clone().requires_grad_(True)
     acc = torch.zeros(w.shape, dtype=torch.float32, device="cuda")
-    loss = ops.lm_head_loss(xa, w, tgt, 15.0, Vpad, grad_acc=acc, w_t=True, weights=wt, fp8=True)
-    loss.backward()
+    loss = ops.lm_head_loss(xa, w, tgt, 15.0, Vpad, grad_acc=acc, w_t=w_t, weights=wt, fp8=True)
+    (loss * 0.5).backward()
     # oracle on the operands as the kernel sees them: e4m3 values times the static scales
     xq = (x.float() / ops.FP8_X_SCALE).clamp(-448, 448).to(torch.float8_e4m3fn).float() * ops.FP8_X_SCALE
     wq = (w.float() / ops.FP8_W_SCALE).clamp(-448, 448).to(torch.float8_e4m3fn).float() * ops.FP8_W_SCALE
-    lq = ops.softcap_ce_ref(xq @ wq, tgt, 15.0, Vpad, wt)
-    xb, wb, _, lref = _oracle(x, w, True, tgt, 15.0, Vpad, wt)
-    lref.backward()
+    lq = ops.softcap_ce_ref((xq @ wq) if w_t else (xq @ wq.t()), tgt, 15.0, Vpad, wt)
+    xb, wb, _, lref = _oracle(x, w, w_t, tgt, 15.0, Vpad, wt)
+    (lref * 0.5).backward()
     _status_ok()
     assert abs(loss.item() - lq.item()) < 2e-3 * abs(lq.item()), (loss.item(), lq.item())
     assert abs(loss.item() - lref.item()) < 2e-2 * abs(lref.item())
-    assert _rel(xa.grad, xb.grad) < 0.1
-    assert _rel(acc, wb.grad) < 0.1
+    assert _rel(xa.grad, xb.grad) < 0.15, _rel(xa.grad, xb.grad)
+    assert _rel(acc, wb.grad) < 0.15, _rel(acc, wb.grad)

@@ -193,7 +193,7 @@ def test_attn_post_forward_and_backward(B, T, H, xsa):
     D, M = 128, B * T
     y, v = _bf(B, T, H, D, seed=30), _bf(B, T, H, D, scale=0.5, seed=31)
     if xsa:
-        v[0, 1, 0] = 0           # a clamped norm: v^ = v / eps there
+        v[0, 1, 0] *= 1e-5       # a norm below the clamp: v^ = v / eps there
     gate = torch.rand(M, H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(32))
     alpha = torch.tensor([0.3 * (i - H / 2) for i in range(H)], device="cuda") if xsa else None
     eps_x = 1e-4
