@@ -158,7 +158,28 @@ class _IHAFuse(torch.autograd.Function):
         return dmix, None, None, None
 
 
-class GPT(nn.Module):
+class ArenaModelMixin:
+    """What the sharded optimizer needs from a model: parameters and gradients laid out in stacked arenas."""
+
+    def finalize(self, world_size: int = 1, alloc=None):
+        """Move parameters and gradients into stacked arenas (plus bf16 shadows and fused operand views on CUDA)."""
+        from ..optim.arena import ParamArena
+        self.arena = ParamArena(self, world_size, alloc)
+        return self
+
+    def zero_grad_arena(self):
+        if self.arena is not None:
+            self.arena.zero_grads()
+        else:
+            for p in self.parameters():
+                if p.grad is not None:
+                    p.grad.zero_()
+
+    def get_device(self):
+        return self.transformer.wte.weight.device
+
+
+class GPT(ArenaModelMixin, nn.Module):
     def __init__(self, config: ModelConfig, pad_vocab_size_to: int = 64):
         super().__init__()
         self.config = config
@@ -234,9 +255,6 @@ class GPT(nn.Module):
     def clear_dupe_layers(self):
         self._dupe_layers = None
 
-    def get_device(self):
-        return self.transformer.wte.weight.device
-
     def all_blocks(self):
         blocks = list(self.transformer.h)
         if self.mtp_weight > 0:
@@ -264,13 +282,16 @@ class GPT(nn.Module):
         if self.mtp_weight > 0:
             torch.nn.init.uniform_(self.mtp_proj.weight, -s, s)
         for block in self.all_blocks():
-            torch.nn.init.uniform_(block.attn.c_q.weight, -s, s)
-            torch.nn.init.uniform_(block.attn.c_k.weight, -s, s)
-            torch.nn.init.uniform_(block.attn.c_v.weight, -s, s)
-            if c.cproj_zero_init:
-                torch.nn.init.zeros_(block.attn.c_proj.weight)
+            if getattr(block.attn, "is_linear_attention", False):
+                block.attn.reset_parameters(s)            # token mixers of the hybrid fork bring their own initialisation
             else:
-                torch.nn.init.normal_(block.attn.c_proj.weight, mean=0.0, std=normal_std)
+                torch.nn.init.uniform_(block.attn.c_q.weight, -s, s)
+                torch.nn.init.uniform_(block.attn.c_k.weight, -s, s)
+                torch.nn.init.uniform_(block.attn.c_v.weight, -s, s)
+                if c.cproj_zero_init:
+                    torch.nn.init.zeros_(block.attn.c_proj.weight)
+                else:
+                    torch.nn.init.normal_(block.attn.c_proj.weight, mean=0.0, std=normal_std)
             torch.nn.init.uniform_(block.mlp.c_gate.weight, -s, s)
             torch.nn.init.uniform_(block.mlp.c_fc.weight, -s, s)
             if c.cproj_zero_init:
@@ -295,6 +316,8 @@ class GPT(nn.Module):
 
     @staticmethod
     def _init_gates(block):
+        if getattr(block.attn, "is_linear_attention", False):
+            return
         if block.attn.ve_gate is not None:
             torch.nn.init.zeros_(block.attn.ve_gate.weight)
         torch.nn.init.zeros_(block.attn.attn_gate.weight)
@@ -330,21 +353,6 @@ class GPT(nn.Module):
         passes = c.num_iterations if num_iterations is None else num_iterations
         per_pass = sum(p.numel() for p in self.transformer.h.parameters()) + sum(p.numel() for p in self.ve_projs.parameters())
         return 6 * (dense - per_pass + passes * per_pass) + passes * attn
-
-    # ------------------------------------------------------------------ CUDA preparation
-    def finalize(self, world_size: int = 1, alloc=None):
-        """Move parameters and gradients into stacked arenas (plus bf16 shadows and fused operand views on CUDA)."""
-        from ..optim.arena import ParamArena
-        self.arena = ParamArena(self, world_size, alloc)
-        return self
-
-    def zero_grad_arena(self):
-        if self.arena is not None:
-            self.arena.zero_grads()
-        else:
-            for p in self.parameters():
-                if p.grad is not None:
-                    p.grad.zero_()
 
     # ------------------------------------------------------------------ block forward
     def _eps(self, x):
@@ -409,7 +417,10 @@ class GPT(nn.Module):
         sd = training and block.drop_prob > 0
         x_in = x
         a = ops.rms_norm(x, self.norm_eps)
-        attn_out = self._attn_forward(block.attn, a, ve, cos_sin, window, scale, xsa_alpha)
+        if getattr(block.attn, "is_linear_attention", False):
+            attn_out = block.attn(a)
+        else:
+            attn_out = self._attn_forward(block.attn, a, ve, cos_sin, window, scale, xsa_alpha)
         x = ops.dropout_add(x, attn_out, block.attn.dropout, training)
         n = ops.rms_norm(x, self.norm_eps)
         mlp_out = self._mlp_forward(block.mlp, n)
@@ -551,8 +562,9 @@ class GPT(nn.Module):
         return lm_loss + self.mtp_weight * mtp_loss, {"lm_loss": lm_loss, "mtp_loss": mtp_loss}
 
 
-def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_size: int = 1, alloc=None) -> GPT:
-    """Construct on `device`, initialise with the reference's RNG call order, and lay out the arenas."""
+def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_size: int = 1, alloc=None, factory=None) -> GPT:
+    """Construct on `device`, initialise with the reference's RNG call order, and lay out the arenas. `factory(config)`
+    builds a GPT subclass instead (the research forks)."""
     device = torch.device(device)
     if seed is not None:
         torch.manual_seed(seed)
@@ -562,7 +574,7 @@ def build_model(config: ModelConfig, device, seed: Optional[int] = 42, world_siz
     # constructors then draw nothing from the generator, so init_weights() starts from the freshly seeded state and
     # the same seed gives the reference's parameters on the GPU as well.
     with torch.device("meta"):
-        model = GPT(config)
+        model = GPT(config) if factory is None else factory(config)
     model.to_empty(device=device)
     model.init_weights()
     if device.type == "cuda":

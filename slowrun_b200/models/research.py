@@ -5,13 +5,12 @@
   layers; what is per-layer are learnable RMSNorms (weight + bias) for the attention inputs, q, k and the MLP input,
   the value / attention gates, lambdas and value projections. The number of active layers grows during training
   (`--depth-schedule "0:10,1533:20"`), new layers being inserted towards the middle of the U-Net.
-* `GatedDeltaNetAttention` — the linear-attention block of the hybrid fork (research/hybrid_attn/train.py:375-635):
-  gated delta rule S_t = a_t S_{t-1} (I - b_t k_t k_t^T) + b_t v_t k_t^T, o_t = S_t q_t, with optional short
-  depth-wise convolutions on q/k/v and an output gate. The reference calls flash-linear-attention's Triton kernels;
-  this is the recurrence itself (chunk-free), the numerics oracle for a future kernel.
+  The unlimited variant (research/universal_transformer/train_unlimited.py:367-369, 598-604) adds a separate
+  `mtp_head` that predicts the token after next from the same final hidden state.
 
-These models reuse the GEMM-backed `ops.linear` path only through `torch.nn.functional.linear`; they are capability
-surface, not the tuned flagship.
+The hybrid softmax / linear-attention fork lives in `models/hybrid.py`. These models run on plain PyTorch ops
+(bf16 autocast on a GPU) and on the package's sharded Muon/AdamW optimizer; they are capability surface, not the
+tuned flagship.
 """
 from __future__ import annotations
 
@@ -23,7 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as ops
-from .gpt import Rotary, has_ve
+from .gpt import ArenaModelMixin, Rotary, has_ve
 
 
 # =============================================================================== universal transformer
@@ -39,6 +38,12 @@ class UniversalConfig:
     stoch_depth: float = 0.05
     logit_cap: float = 10.0
     depth_schedule: str = "0:10,1533:20"
+    use_iha: bool = True
+    iha_mix_v: bool = True
+    mtp_weight: float = 0.0          # > 0: separate mtp_head on the final hidden state (the unlimited variant)
+    # switches the shared parameter-grouping code reads
+    attn_gate_adamw: bool = False
+    xsa_mode: str = "off"
 
 
 def parse_depth_schedule(spec: str) -> List[Tuple[int, int]]:
@@ -67,6 +72,12 @@ class LearnedRMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
         self.bias = nn.Parameter(torch.zeros(dim))
 
+    adamw_kind = "norm"
+
+    def adamw_scalar_params(self):
+        """Stepped by AdamW at the scalar rate, not by Muon (research/universal_transformer/train.py:487-511)."""
+        return [self.weight, self.bias]
+
     def forward(self, x):
         return F.rms_norm(x, (x.size(-1),), self.weight.to(x.dtype)) + self.bias.to(x.dtype)
 
@@ -81,13 +92,25 @@ class SharedAttention(nn.Module):
         self.c_q, self.c_k, self.c_v = (nn.Linear(d, d, bias=False) for _ in range(3))
         self.c_proj = nn.Linear(d, d, bias=False)
         self.dropout = c.dropout
+        self.use_iha, self.iha_mix_v = c.use_iha, c.iha_mix_v
+        if self.use_iha:          # head mixing of the projection weights, as in the limited track (train.py:266-298)
+            self.q_mix = nn.Parameter(torch.eye(self.n_head))
+            self.k_mix = nn.Parameter(torch.eye(self.n_head))
+            if self.iha_mix_v:
+                self.v_mix = nn.Parameter(torch.eye(self.n_head))
+
+    def _proj(self, x, lin, mix):
+        w = lin.weight
+        if mix is not None:
+            w = (mix @ w.view(self.n_head, -1)).view_as(w)
+        return F.linear(x, w.to(x.dtype))
 
     def forward(self, x, ve, cos_sin, window, q_norm, k_norm, ve_gate, attn_gate):
         B, T, _ = x.shape
         H, D = self.n_head, self.head_dim
-        q = self.c_q(x).view(B, T, H, D)
-        k = self.c_k(x).view(B, T, H, D)
-        v = self.c_v(x).view(B, T, H, D)
+        q = self._proj(x, self.c_q, self.q_mix if self.use_iha else None).view(B, T, H, D)
+        k = self._proj(x, self.c_k, self.k_mix if self.use_iha else None).view(B, T, H, D)
+        v = self._proj(x, self.c_v, self.v_mix if (self.use_iha and self.iha_mix_v) else None).view(B, T, H, D)
         if ve is not None and ve_gate is not None:
             v = v + (2 * torch.sigmoid(ve_gate)).unsqueeze(-1) * ve.view(B, T, H, D)
         cos, sin = cos_sin
@@ -131,10 +154,14 @@ class LayerParams(nn.Module):
         self.drop_prob = c.stoch_depth * (layer_idx / max(c.n_layer - 1, 1))
 
 
-class UniversalGPT(nn.Module):
+class UniversalGPT(ArenaModelMixin, nn.Module):
+    wire_fused = False            # forward runs on plain PyTorch ops; the arena only serves the optimizer
+
     def __init__(self, c: UniversalConfig):
         super().__init__()
         self.config = c
+        self.arena = None
+        self.mtp_weight = c.mtp_weight
         L = c.n_layer
         assert L % 2 == 0
         pv = ((c.vocab_size + 63) // 64) * 64
@@ -144,6 +171,8 @@ class UniversalGPT(nn.Module):
         self.decoder_attns = nn.ModuleList([SharedAttention(c) for _ in range(2)])
         self.encoder_mlp, self.decoder_mlp = SharedMLP(c), SharedMLP(c)
         self.lm_head = nn.Linear(c.n_embd, pv, bias=False)
+        if c.mtp_weight > 0:
+            self.mtp_head = nn.Linear(c.n_embd, pv, bias=False)
         self.resid_lambdas = nn.Parameter(torch.ones(L))
         self.x0_lambdas = nn.Parameter(torch.full((L,), 0.1))
         self.ve_projs = nn.ModuleDict({str(i): nn.Linear(c.n_embd, c.n_embd, bias=False) for i in range(L) if has_ve(i, L)})
@@ -164,10 +193,15 @@ class UniversalGPT(nn.Module):
         s = 3 ** 0.5 * c.n_embd ** -0.5
         nn.init.normal_(self.transformer.wte.weight, std=1.0)
         nn.init.normal_(self.lm_head.weight, std=0.001)
+        if c.mtp_weight > 0:
+            nn.init.normal_(self.mtp_head.weight, std=0.001)
         for m in list(self.encoder_attns) + list(self.decoder_attns):
             for lin in (m.c_q, m.c_k, m.c_v):
                 nn.init.uniform_(lin.weight, -s, s)
             nn.init.zeros_(m.c_proj.weight)
+            if m.use_iha:
+                for mix in (m.q_mix, m.k_mix) + ((m.v_mix,) if m.iha_mix_v else ()):
+                    nn.init.eye_(mix)
         for m in (self.encoder_mlp, self.decoder_mlp):
             nn.init.uniform_(m.c_gate.weight, -s, s)
             nn.init.uniform_(m.c_fc.weight, -s, s)
@@ -178,7 +212,59 @@ class UniversalGPT(nn.Module):
             for g in list(blk.ve_gates) + list(blk.attn_gates):
                 if isinstance(g, nn.Linear):
                     nn.init.zeros_(g.weight)
+            for nrm in list(blk.attn_norms) + [blk.mlp_norm] + list(blk.q_norms) + list(blk.k_norms):
+                nn.init.ones_(nrm.weight)
+                nn.init.zeros_(nrm.bias)
+        self.resid_lambdas.fill_(1.0)
+        self.x0_lambdas.fill_(0.1)
+        self.skip_weights.fill_(1.0)
         self.rotary.reset()
+
+    # ------------------------------------------------------------------ what the shared optimizer code asks of a model
+    def all_blocks(self):
+        return []
+
+    def iha_params(self):
+        out = []
+        for m in list(self.encoder_attns) + list(self.decoder_attns):
+            if m.use_iha:
+                out += [m.q_mix, m.k_mix] + ([m.v_mix] if m.iha_mix_v else [])
+        return out
+
+    def muon_matrix_params(self):
+        """Shared projections and MLPs, per-layer gate linears, value projections
+        (research/universal_transformer/train.py:470-503)."""
+        iha = {id(p) for p in self.iha_params()}
+        shared = [p for mod in (self.encoder_attns, self.decoder_attns, self.encoder_mlp, self.decoder_mlp)
+                  for p in mod.parameters() if id(p) not in iha]
+        per_layer = []
+        for blk in self.transformer.h:
+            per_layer += [g.weight for g in blk.attn_gates]
+            per_layer += [g.weight for g in blk.ve_gates if isinstance(g, nn.Linear)]
+        return shared + per_layer + list(self.ve_projs.parameters())
+
+    def layer_parameters(self, i):
+        """Parameters that only layer i touches (norms, gates, its value projection): what goes idle while the layer is
+        not part of the active depth."""
+        ps = list(self.transformer.h[i].parameters())
+        if str(i) in self.ve_projs:
+            ps += list(self.ve_projs[str(i)].parameters())
+        return ps
+
+    def inactive_parameters(self):
+        idle = [i for i in range(self.max_n_layer) if self.active_encoder_layers <= i < self.active_decoder_start]
+        return [p for i in idle for p in self.layer_parameters(i)]
+
+    def estimate_flops(self):
+        """6 FLOPs per matmul parameter per use (shared modules count once per active layer) plus attention."""
+        c = self.config
+        per_layer_shared = sum(p.numel() for p in self.encoder_attns.parameters()) + sum(p.numel() for p in self.encoder_mlp.parameters())
+        active = list(range(self.active_encoder_layers)) + list(range(self.active_decoder_start, self.max_n_layer))
+        own = sum(p.numel() for i in active for p in self.layer_parameters(i))
+        heads = self.lm_head.weight.numel() + (self.mtp_head.weight.numel() if c.mtp_weight > 0 else 0)
+        D, T = c.n_embd // c.n_head, c.sequence_len
+        attn = sum(2 * 12 * c.n_head * D * min(self.window_sizes[i][0], T) for i in active)     # two attention modules per layer
+        return 6 * (len(active) * per_layer_shared + own + heads) + attn
 
     def set_active_layers(self, n_layer: int):
         """Run only `n_layer` layers: the first n/2 encoder layers and the last n/2 decoder layers, so growth adds
@@ -226,71 +312,16 @@ class UniversalGPT(nn.Module):
                 x = x + self.skip_weights[i - self.max_encoder_layers] * enc[j]
             x = self._run_layer(x, x0, cos_sin, i, self.decoder_attns, self.decoder_mlp)
         x = F.rms_norm(x, (c.n_embd,))
-        logits = self.lm_head(x)[..., :c.vocab_size].float()
-        if c.logit_cap > 0:
-            logits = c.logit_cap * torch.tanh(logits / c.logit_cap)
+
+        def capped(head, h):
+            z = F.linear(h, head.weight.to(h.dtype))[..., :c.vocab_size].float()
+            return c.logit_cap * torch.tanh(z / c.logit_cap) if c.logit_cap > 0 else z
+        logits = capped(self.lm_head, x)
         if targets is None:
             return logits
-        return F.cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1), ignore_index=-1, reduction=loss_reduction)
-
-
-# =============================================================================== gated delta net attention
-def gated_delta_rule(q, k, v, alpha, beta):
-    """Recurrent statement of the gated delta rule. q, k: (B, T, H, Dk) (k L2-normalised by the caller), v: (B, T, H, Dv),
-    alpha, beta: (B, T, H) with alpha in (0, 1] the decay and beta in (0, 1) the write strength.
-        S_t = alpha_t * S_{t-1} (I - beta_t k_t k_t^T) + beta_t v_t k_t^T ;  o_t = S_t q_t
-    Returns o: (B, T, H, Dv). O(T Dk Dv) time, state kept in fp32."""
-    B, T, H, Dk = q.shape
-    Dv = v.size(-1)
-    S = torch.zeros(B, H, Dv, Dk, dtype=torch.float32, device=q.device)
-    out = []
-    qf, kf, vf = q.float(), k.float(), v.float()
-    for t in range(T):
-        kt, vt, qt = kf[:, t], vf[:, t], qf[:, t]
-        a, b = alpha[:, t].float()[..., None, None], beta[:, t].float()[..., None, None]
-        Sk = torch.einsum("bhvk,bhk->bhv", S, kt)                       # S k_t
-        S = a * (S - b * Sk.unsqueeze(-1) * kt.unsqueeze(-2)) + b * vt.unsqueeze(-1) * kt.unsqueeze(-2)
-        out.append(torch.einsum("bhvk,bhk->bhv", S, qt))
-    return torch.stack(out, dim=1).to(v.dtype)
-
-
-class GatedDeltaNetAttention(nn.Module):
-    """Drop-in replacement for softmax attention on selected layers of the hybrid model: projections, optional
-    depth-wise causal convolutions (kernel 4) on q/k/v, SiLU, L2-normalised q/k, data-dependent decay and write
-    gates, gated RMSNorm on the output."""
-
-    def __init__(self, n_embd: int, n_head: int, head_dim: Optional[int] = None, use_conv: bool = True, conv_size: int = 4):
-        super().__init__()
-        self.n_head = n_head
-        self.head_dim = head_dim or n_embd // n_head
-        inner = self.n_head * self.head_dim
-        self.c_q, self.c_k, self.c_v = (nn.Linear(n_embd, inner, bias=False) for _ in range(3))
-        self.a_proj = nn.Linear(n_embd, n_head, bias=False)      # decay logits
-        self.b_proj = nn.Linear(n_embd, n_head, bias=False)      # write-strength logits
-        self.g_proj = nn.Linear(n_embd, inner, bias=False)       # output gate
-        self.c_proj = nn.Linear(inner, n_embd, bias=False)
-        self.A_log = nn.Parameter(torch.zeros(n_head))
-        self.dt_bias = nn.Parameter(torch.zeros(n_head))
-        self.use_conv = use_conv
-        if use_conv:
-            self.convs = nn.ModuleList([nn.Conv1d(inner, inner, conv_size, groups=inner, padding=conv_size - 1, bias=False)
-                                        for _ in range(3)])
-
-    def _conv(self, x, conv):
-        T = x.size(1)
-        return conv(x.transpose(1, 2))[..., :T].transpose(1, 2)
-
-    def forward(self, x):
-        B, T, _ = x.shape
-        H, D = self.n_head, self.head_dim
-        q, k, v = self.c_q(x), self.c_k(x), self.c_v(x)
-        if self.use_conv:
-            q, k, v = (self._conv(t, c) for t, c in zip((q, k, v), self.convs))
-        q, k, v = (F.silu(t).view(B, T, H, D) for t in (q, k, v))
-        q = F.normalize(q.float(), dim=-1).to(x.dtype) * D ** -0.5
-        k = F.normalize(k.float(), dim=-1).to(x.dtype)
-        alpha = torch.exp(-torch.exp(self.A_log.float()) * F.softplus(self.a_proj(x).float() + self.dt_bias.float()))
-        beta = torch.sigmoid(self.b_proj(x).float())
-        o = gated_delta_rule(q, k, v, alpha, beta)
-        o = F.rms_norm(o, (D,)) * F.silu(self.g_proj(x).view(B, T, H, D))
-        return self.c_proj(o.reshape(B, T, H * D))
+        lm_loss = F.cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1), ignore_index=-1, reduction=loss_reduction)
+        if loss_reduction != "mean" or c.mtp_weight <= 0:
+            return lm_loss
+        mtp_logits = capped(self.mtp_head, x[:, :-1])
+        mtp_loss = F.cross_entropy(mtp_logits.reshape(-1, mtp_logits.size(-1)), targets[:, 1:].reshape(-1), ignore_index=-1)
+        return lm_loss + c.mtp_weight * mtp_loss

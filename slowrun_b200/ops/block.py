@@ -296,4 +296,6 @@ def block_supported(model, block) -> bool:
     """The fused node covers every block of the four tracks (head_dim 128, weights large enough to have bf16 shadows);
     anything else goes through the op-by-op path of `GPT._block_forward`."""
     a = block.attn
+    if getattr(a, "is_linear_attention", False):
+        return False
     return a.head_dim == 128 and a.n_head <= 64 and a.fused is not None and a.fused["qkv_w16"] is not None

@@ -104,7 +104,7 @@ class ParamArena:
         for p in self.other_params:
             repoint(p)
             p.grad = zeros(p.shape, p.dtype)
-        if cuda:
+        if cuda and getattr(model, "wire_fused", True):
             self._wire_fused_views()
 
     # ------------------------------------------------------------------ fused operand views for the model
@@ -116,25 +116,30 @@ class ParamArena:
         m = self.model
         for block in m.all_blocks():
             a = block.attn
+            if getattr(a, "is_linear_attention", False):
+                self._wire_mlp(block.mlp)
+                continue
             g, iq = self._slot(a.c_q.weight)
             assert g.params[iq + 1] is a.c_k.weight and g.params[iq + 2] is a.c_v.weight, "q,k,v must be adjacent"
             d_out, d_in = g.shape
             g2, ip = self._slot(a.c_proj.weight)
             a.fused = dict(qkv_w16=g.W16[iq:iq + 3].view(3 * d_out, d_in), qkv_grad=g.G[iq:iq + 3].view(3 * d_out, d_in),
                            proj_w16=g2.W16[ip], proj_grad=g2.G[ip])
-            mlp = block.mlp
-            gg, ig = self._slot(mlp.c_gate.weight)
-            assert gg.params[ig + 1] is mlp.c_fc.weight, "c_gate, c_fc must be adjacent"
-            h, d = gg.shape
-            g3, i3 = self._slot(mlp.c_proj.weight)
-            mlp.fused = dict(gf_w16=gg.W16[ig:ig + 2].view(2 * h, d), gf_grad=gg.G[ig:ig + 2].view(2 * h, d),
-                             proj_w16=g3.W16[i3], proj_grad=g3.G[i3])
+            self._wire_mlp(block.mlp)
         for lin in m.ve_projs.values():
             g, i = self._slot(lin.weight)
             lin.fused = dict(w16=g.W16[i], grad=g.G[i])
         if m.mtp_weight > 0:
             g, i = self._slot(m.mtp_proj.weight)
             m.mtp_proj.fused = dict(w16=g.W16[i], grad=g.G[i])
+
+    def _wire_mlp(self, mlp):
+        gg, ig = self._slot(mlp.c_gate.weight)
+        assert gg.params[ig + 1] is mlp.c_fc.weight, "c_gate, c_fc must be adjacent"
+        h, d = gg.shape
+        g3, i3 = self._slot(mlp.c_proj.weight)
+        mlp.fused = dict(gf_w16=gg.W16[ig:ig + 2].view(2 * h, d), gf_grad=gg.G[ig:ig + 2].view(2 * h, d),
+                         proj_w16=g3.W16[i3], proj_grad=g3.G[i3])
 
     # ------------------------------------------------------------------ maintenance
     def zero_grads(self):

@@ -33,6 +33,11 @@ POLAR_EXPRESS_COEFFS = [
     (2.3465413258596377, -1.7097828382687081, 0.42323551169305323),
 ]
 
+# Second coefficient table of the hybrid research fork: eight identical steps and two finishing ones
+# (research/hybrid_attn/train.py:932-940)
+DEEPSEEK_V4_COEFFS = [(3.4445, -4.7750, 2.0315)] * 8 + [(2.0, -1.5, 0.5)] * 2
+NS_SCHEDULES = {"polar-express": POLAR_EXPRESS_COEFFS, "deepseek-v4": DEEPSEEK_V4_COEFFS}
+
 c_void_p, c_int, c_long, c_float = _lib.c_void_p, _lib.c_int, _lib.ctypes.c_long, _lib.c_float
 
 
@@ -41,20 +46,21 @@ def _bf16(x: float) -> float:
 
 
 # ----------------------------------------------------------------------------- plain-PyTorch statements (oracle / CPU path)
-def newton_schulz_ref(X: torch.Tensor, ns_steps: int) -> torch.Tensor:
+def newton_schulz_ref(X: torch.Tensor, ns_steps: int, schedule: str = "polar-express") -> torch.Tensor:
     """X: [n, r, c] bf16 (already Frobenius-normalised). Returns the orthogonalised stack in bf16."""
+    coeffs = NS_SCHEDULES[schedule]
     if X.size(-2) > X.size(-1):
-        for a, b, c in POLAR_EXPRESS_COEFFS[:ns_steps]:
+        for a, b, c in coeffs[:ns_steps]:
             A = X.mT @ X
             X = a * X + X @ (b * A + c * (A @ A))
     else:
-        for a, b, c in POLAR_EXPRESS_COEFFS[:ns_steps]:
+        for a, b, c in coeffs[:ns_steps]:
             A = X @ X.mT
             X = a * X + (b * A + c * (A @ A)) @ X
     return X
 
 
-def muon_update_ref(G, M, S, momentum, beta2, ns_steps, row_norm=True):
+def muon_update_ref(G, M, S, momentum, beta2, ns_steps, row_norm=True, schedule="polar-express"):
     """Reference math of train.py:603-634 up to the variance-reduced update U (bf16). Updates M and S in place.
     G: [n, r, c] fp32 averaged gradient (consumed), M: momentum, S: second moment ([n,r,1] or [n,1,c]).
     `row_norm=False` is the tiny track's variant, which skips the MuonEq-R row normalisation (tiny/train.py:770-778).
@@ -68,7 +74,7 @@ def muon_update_ref(G, M, S, momentum, beta2, ns_steps, row_norm=True):
         g /= g.float().norm(dim=-1, keepdim=True).clamp_min(1e-7).to(g.dtype)
     X = g.bfloat16()
     X = X / (X.norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6)
-    X = newton_schulz_ref(X, ns_steps)
+    X = newton_schulz_ref(X, ns_steps, schedule)
     red_dim = -1 if G.size(-2) >= G.size(-1) else -2
     v_mean = X.float().square().mean(dim=red_dim, keepdim=True)
     red = X.size(red_dim)
@@ -111,14 +117,15 @@ class _NSWorkspace:
         self.B = torch.empty((n, g, g), dtype=torch.bfloat16, device=device)
 
 
-def newton_schulz_cuda(X: torch.Tensor, ns_steps: int, ws: _NSWorkspace, sym: bool = True) -> torch.Tensor:
+def newton_schulz_cuda(X: torch.Tensor, ns_steps: int, ws: _NSWorkspace, sym: bool = True,
+                       schedule: str = "polar-express") -> torch.Tensor:
     """In: X [n, r, c] bf16. Three GEMMs per iteration; the gram and polynomial products are symmetric and only
     their upper-triangular tiles are computed; `aX + ...` and `bA + ...` ride in the epilogues."""
     n, r, c = X.shape
     tall = r > c
     src, dst = X, ws.X2[:n]
     A, B = ws.A[:n], ws.B[:n]
-    for a_, b_, c_ in POLAR_EXPRESS_COEFFS[:ns_steps]:
+    for a_, b_, c_ in NS_SCHEDULES[schedule][:ns_steps]:
         if tall:
             gemm(src, src, out=A, a_mn=True, b_mn=True, sym=sym)                    # A = X^T X
             gemm(A, A, out=B, cin=A, alpha=c_, beta=b_, sym=sym)                    # B = bA + cA^2
@@ -445,7 +452,8 @@ class ShardedMuonAdamW:
             self._mark("wait_pull")
             if n_own > 0:
                 sc = st["scratch"]
-                Xo = newton_schulz_cuda(st["X"][:n_own], int(g["ns_steps"]), st["ws"])
+                Xo = newton_schulz_cuda(st["X"][:n_own], int(g["ns_steps"]), st["ws"],
+                                        schedule=g.get("ns_schedule", "polar-express"))
                 self._mark("newton_schulz")
                 rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
                     Xo.data_ptr(), sc[0].data_ptr(), st["second"].data_ptr(), sc[1].data_ptr(), st["U"].data_ptr(),
@@ -475,7 +483,7 @@ class ShardedMuonAdamW:
                     tmp.mul_(gscale)
                     st["U"][:n_own].copy_(muon_update_ref(tmp, st["momentum"][:n_own], st["second"][:n_own],
                                                           float(g["momentum"]), float(g["beta2"]), int(g["ns_steps"]),
-                                                          bool(g.get("row_norm", True))))
+                                                          bool(g.get("row_norm", True)), g.get("ns_schedule", "polar-express")))
             comm.device_barrier()                                                                  # last
             for g, st in slow:
                 ga = st["arena"]
@@ -579,14 +587,15 @@ class ShardedMuonAdamW:
                     G[a0:a1].data_ptr(), st["momentum"][a0:a1].data_ptr(), X.data_ptr(), st["sumsq"].data_ptr(), k, r, c, mu,
                     gscale, int(row_norm), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_pre")
-                Xo = newton_schulz_cuda(X, ns, st["ws"])
+                Xo = newton_schulz_cuda(X, ns, st["ws"], schedule=grp.get("ns_schedule", "polar-express"))
                 rc = _lib.fn("sr_muon_post", [c_void_p] * 5 + [c_int, c_int, c_int, c_float, c_void_p])(
                     Xo.data_ptr(), sc[0].data_ptr(), st["second"][a0:a1].data_ptr(), sc[1].data_ptr(), U[a0:a1].data_ptr(), k, r, c,
                     _bf16(beta2), _lib.stream_ptr())
                 _lib.check_rc(rc, "sr_muon_post")
             else:
                 g_own = G[a0:a1].mul(gscale) if gscale != 1.0 else G[a0:a1].clone()
-                U[a0:a1].copy_(muon_update_ref(g_own, st["momentum"][a0:a1], st["second"][a0:a1], mu, beta2, ns, row_norm))
+                U[a0:a1].copy_(muon_update_ref(g_own, st["momentum"][a0:a1], st["second"][a0:a1], mu, beta2, ns, row_norm,
+                                               grp.get("ns_schedule", "polar-express")))
         if self._inactive and n_own > 0:
             for j in range(n_own):                       # an inactive matrix contributes a zero update
                 if id(ga.params[first + j]) in self._inactive:

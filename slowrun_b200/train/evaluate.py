@@ -57,9 +57,10 @@ def evaluate_bpb(model, batches, steps, token_bytes, comm=None, num_iterations=N
     """(bits per byte, mean loss) over `steps` batches of `batches` (train.py:846-873)."""
     tally = _Tally(model.get_device(), token_bytes)
     it = iter(batches)
+    kw = {} if num_iterations is None else {"num_iterations": num_iterations}
     for _ in range(steps):
         x, y, _ = next(it)
-        tally.add(model(x, y, loss_reduction="none", num_iterations=num_iterations).float(), y)
+        tally.add(model(x, y, loss_reduction="none", **kw).float(), y)
     return tally.result(comm)
 
 

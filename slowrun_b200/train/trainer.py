@@ -46,6 +46,33 @@ def make_comm(cfg: TrainConfig, info: DistInfo):
 
 
 class Trainer:
+    # tracks whose post-training step is the probability average over the last epoch checkpoints on disk
+    LOGIT_AVG_TRACKS = ("limited", "two_hour", "universal")
+    # tracks that replay decoder layers from `dupe_start_epoch` on
+    DUPE_TRACKS = ("limited", "two_hour", "hybrid")
+
+    def model_factory(self):
+        """Constructor of the model (`factory(model_config) -> GPT-like module`), or None for the package's GPT."""
+        return None
+
+    def forward_context(self):
+        """Context the forward pass runs in (research models on plain PyTorch ops use bf16 autocast on a GPU)."""
+        import contextlib
+        return contextlib.nullcontext()
+
+    def before_optimizer_step(self):
+        """Hook: gradients of the step are complete (local, not yet reduced across ranks)."""
+
+    def after_optimizer_step(self):
+        """Hook: parameters were updated; `self.step` still holds the index of the step just taken."""
+
+    def on_epoch_end(self, epoch, val_bpb, val_loss):
+        """Hook: `epoch` was just evaluated (called on every rank)."""
+
+    def post_training(self, log, best):
+        """Hook after the last step: `best` = (min_bpb, min_loss); returns the possibly improved pair."""
+        return best
+
     def __init__(self, cfg: TrainConfig, info: Optional[DistInfo] = None, quiet: bool = False):
         self.cfg = cfg
         self.info = info or init_distributed()
@@ -65,7 +92,8 @@ class Trainer:
             torch.cuda.set_stream(self.stream)
         self.comm = make_comm(c, info)
         self.model = build_model(c.model, self.device, seed=seed, world_size=info.world_size,
-                                 alloc=self.comm.alloc if getattr(self.comm, "fused", False) else None)
+                                 alloc=self.comm.alloc if getattr(self.comm, "fused", False) else None,
+                                 factory=self.model_factory())
         self.param_groups = build_param_groups(self.model, c)
         self.optimizer = ShardedMuonAdamW(self.model, self.param_groups, self.comm)
         train_path = c.input_bin or os.path.join(c.data_dir, "fineweb_train.pt")
@@ -105,7 +133,7 @@ class Trainer:
     # ------------------------------------------------------------------ one optimizer step
     def _maybe_switch_structure(self):
         c = self.cfg
-        if c.track in ("limited", "two_hour") and not self.dupe_active and self.current_epoch >= c.dupe_start_epoch:
+        if c.track in self.DUPE_TRACKS and not self.dupe_active and self.current_epoch >= c.dupe_start_epoch:
             self.model.set_dupe_layers(c.dupe_layers_start, c.dupe_layers_end, c.dupe_loops)
             self.dupe_active = True
             self.flops_per_token = self.model.estimate_flops()
@@ -141,15 +169,15 @@ class Trainer:
                 _lib.launch_count += graph["launches"]      # kernels replayed from the graph
                 loss_t, metrics = graph["loss"], graph["metrics"]
             else:
-                if tiny:
-                    loss = model(self.x, self.y, num_iterations=n_iter, mtp_weights=mtp_w)
-                else:
-                    loss, metrics = model(self.x, self.y)
+                with self.forward_context():
+                    out = model(self.x, self.y, num_iterations=n_iter, mtp_weights=mtp_w) if tiny else model(self.x, self.y)
+                loss, metrics = out if isinstance(out, tuple) else (out, {})
                 loss_t = loss.detach()
                 (loss / self.grad_accum).backward()
                 self._eager_micro += 1
             self.x, self.y, epoch = next(self.train_loader)
         self._pending_epoch = epoch
+        self.before_optimizer_step()
         self.sched.apply(self.param_groups, self.step)
         self.optimizer.step()
         if getattr(self.optimizer, "fused", False):
@@ -159,6 +187,7 @@ class Trainer:
         model.zero_grad_arena()
         if self.ema is not None:
             self.ema.maybe_update(self.step)
+        self.after_optimizer_step()
         self.step += 1
         out = {"loss_tensor": loss_t, "metrics": metrics, "epoch": epoch, "num_iterations": n_iter}
         if sync:
@@ -212,8 +241,9 @@ class Trainer:
             self.token_bytes = default_token_bytes(self.device, c.model.vocab_size)
         steps = max(1, c.eval_tokens // (c.device_batch_size * c.model.sequence_len * self.info.world_size))
         self.model.eval()
-        bpb, loss = evaluate_bpb(self.model, self.build_val_loader(), steps, self.token_bytes,
-                                 self.comm if self.info.world_size > 1 else None, num_iterations=num_iterations)
+        with self.forward_context():
+            bpb, loss = evaluate_bpb(self.model, self.build_val_loader(), steps, self.token_bytes,
+                                     self.comm if self.info.world_size > 1 else None, num_iterations=num_iterations)
         self.model.train()
         return bpb, loss
 
@@ -240,8 +270,8 @@ class Trainer:
         val_bpb = val_loss = float("inf")
         bad_epochs = 0
         total_time, timed_steps, timing_start = 0.0, 0, 4
-        keep = c.logit_avg if c.track in ("limited", "two_hour") else c.swa_last_epochs
-        ring_dir = c.logit_avg_dir if c.track in ("limited", "two_hour") else os.path.join(log.run_dir, "checkpoints")
+        keep = c.logit_avg if c.track in self.LOGIT_AVG_TRACKS else (c.swa_last_epochs if c.track == "tiny" else 0)
+        ring_dir = c.logit_avg_dir if c.track in self.LOGIT_AVG_TRACKS else os.path.join(log.run_dir, "checkpoints")
         ring = CheckpointRing(ring_dir, keep, self.master)
         max_iters = c.model.num_iterations if c.track == "tiny" else None
         if not c.eval_logit_avg:
@@ -281,6 +311,7 @@ class Trainer:
                 val_bpb, val_loss = self.evaluate(max_iters)
                 print0(f"Step {step:05d} | Epoch {self.current_epoch} | Val BPB: {val_bpb:.6f} | Val Loss: {val_loss:.6f}")
                 log.metrics({"step": step, "epoch": self.current_epoch, "val/bpb": val_bpb, "val/loss": val_loss})
+                self.on_epoch_end(self.current_epoch, val_bpb, val_loss)
                 stop = False
                 if val_bpb < min_bpb:
                     min_bpb, min_loss, bad_epochs = val_bpb, val_loss, 0
@@ -315,7 +346,7 @@ class Trainer:
         # ---------------------------------------------------------------- post-training averaging
         self.comm.barrier()          # every checkpoint rank 0 wrote is complete before any rank reads it
         comm = self.comm if world > 1 else None
-        if c.track in ("limited", "two_hour") and c.logit_avg > 0:
+        if c.track in self.LOGIT_AVG_TRACKS and c.logit_avg > 0:
             paths = ring.paths
             if c.eval_logit_avg:
                 import glob
@@ -330,7 +361,8 @@ class Trainer:
                 for label in (("equal", "weighted") if c.logit_avg_mode == "both" else (c.logit_avg_mode,)):
                     w = recency_weights(n, label)
                     print0(f"  [{label}] weights: {[f'{x:.3f}' for x in w]}")
-                    bpb, loss = evaluate_prob_avg(self.model, self.build_val_loader, paths, w, steps, self.token_bytes, comm)
+                    with self.forward_context():
+                        bpb, loss = evaluate_prob_avg(self.model, self.build_val_loader, paths, w, steps, self.token_bytes, comm)
                     print0(f"  [{label}] Val BPB: {bpb:.6f} | Val Loss: {loss:.6f}")
                     log.metrics({f"logit_avg_{label}/bpb": bpb, f"logit_avg_{label}/loss": loss})
                     if loss < min_loss:
@@ -353,6 +385,7 @@ class Trainer:
             if self.master:
                 torch.save({n: p.data.float().cpu() for n, p in self.model.named_parameters()}, os.path.join(log.run_dir, "model.pt"))
             self.comm.barrier()
+        min_bpb, min_loss = self.post_training(log, (min_bpb, min_loss))
         peak = torch.cuda.max_memory_allocated() / 1024 / 1024 if self.device.type == "cuda" else 0.0
         final_train = self.smooth_loss / (1 - 0.9 ** self.step) if self.step > 0 else float("inf")
         print0(f"Peak memory: {peak:.2f} MiB")

@@ -1,8 +1,8 @@
-"""Research variants: universal transformer (shared modules, depth schedule) and the gated-delta-rule layer."""
+"""Research variants: universal transformer (shared modules, depth schedule) and the gated delta rule."""
 import torch
 
-from slowrun_b200.models.research import (GatedDeltaNetAttention, UniversalConfig, UniversalGPT, depth_at_step,
-                                           gated_delta_rule, parse_depth_schedule)
+from slowrun_b200.models.research import UniversalConfig, UniversalGPT, depth_at_step, parse_depth_schedule
+from slowrun_b200.ops.linear_attention import gated_delta_rule_recurrent
 
 
 def test_depth_schedule_parsing_and_growth():
@@ -32,21 +32,16 @@ def test_universal_gpt_shares_weights_and_trains():
     assert m.encoder_attns[0].c_q.weight.grad.abs().sum() > 0
 
 
-def test_gated_delta_rule_matches_explicit_recurrence_and_is_causal():
+def test_gated_delta_rule_definition_matches_an_explicit_matrix_recurrence():
+    """S_t = diag(a_t) S_{t-1} (then) S_t += b_t k_t (v_t - S_t^T k_t)^T ; o_t = S_t^T q_t, written with plain matrices."""
     torch.manual_seed(0)
-    B, T, H, D = 1, 6, 2, 4
-    q, k, v = torch.randn(B, T, H, D), torch.nn.functional.normalize(torch.randn(B, T, H, D), dim=-1), torch.randn(B, T, H, D)
-    alpha, beta = torch.rand(B, T, H) * 0.5 + 0.5, torch.rand(B, T, H)
-    o = gated_delta_rule(q, k, v, alpha, beta)
-    S = torch.zeros(H, D, D)
-    for t in range(T):
-        for h in range(H):
-            kk = k[0, t, h]
-            S[h] = alpha[0, t, h] * S[h] @ (torch.eye(D) - beta[0, t, h] * torch.outer(kk, kk)) + beta[0, t, h] * torch.outer(v[0, t, h], kk)
-            assert torch.allclose(o[0, t, h], S[h] @ q[0, t, h], atol=1e-5)
-    layer = GatedDeltaNetAttention(32, 2)
-    x = torch.randn(1, 8, 32)
-    y1 = layer(x)
-    x2 = x.clone()
-    x2[:, 5:] += 1.0
-    assert torch.allclose(layer(x2)[:, :5], y1[:, :5], atol=1e-5)   # later tokens cannot influence earlier outputs
+    B, T, H, Dk, Dv = 1, 6, 2, 4, 3
+    q, k, v = torch.randn(B, T, H, Dk), torch.nn.functional.normalize(torch.randn(B, T, H, Dk), dim=-1), torch.randn(B, T, H, Dv)
+    g, beta = -torch.rand(B, T, H), torch.rand(B, T, H) * 2
+    o = gated_delta_rule_recurrent(q, k, v, g, beta)
+    for h in range(H):
+        S = torch.zeros(Dk, Dv)
+        for t in range(T):
+            S = torch.exp(g[0, t, h]) * S
+            S = S + beta[0, t, h] * torch.outer(k[0, t, h], v[0, t, h] - S.t() @ k[0, t, h])
+            assert torch.allclose(o[0, t, h], S.t() @ q[0, t, h], atol=1e-5)
