@@ -261,43 +261,62 @@ __global__ void quant_fp8_t_kernel(const __nv_bfloat16* __restrict__ x, uint8_t*
 }
 
 // out[r, c] = fp8(x[r, c] * f_r) and out_t[c, r] = the same value, f_r = row_scale[r] * mult / *div_ptr: the logit
-// gradient of the fused head in both operand layouts its two fp8 backward products need (K-major for each). 64 x 64
-// tiles through shared memory so that both outputs are written in 64-byte row pieces.
-__global__ void quant_fp8_dual_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ row_scale,
-                                      const float* __restrict__ div_ptr, float mult, uint8_t* __restrict__ out,
-                                      uint8_t* __restrict__ out_t, int rows, int cols, long ldx, long ldo, long ldt,
-                                      int e5m2) {
-  __shared__ uint8_t tile[64][65];
-  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+// gradient of the fused head in both operand layouts its two fp8 backward products need (K-major for each).
+// One CTA converts a 64-row x 128-column tile: 16-byte loads, 8-byte stores of the row-major copy, and the transposed
+// copy through shared memory (bytes stored column-major with a per-column rotation that keeps the 16 lanes of a row on
+// 16 different banks) written back as 16-byte pieces of 16 consecutive rows. cols % 8 == 0.
+constexpr int kQR = 64, kQC = 128;
+__global__ void __launch_bounds__(256)
+quant_fp8_dual_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ row_scale,
+                      const float* __restrict__ div_ptr, float mult, uint8_t* __restrict__ out,
+                      uint8_t* __restrict__ out_t, int rows, int cols, long ldx, long ldo, long ldt, int e5m2) {
+  __shared__ __align__(16) uint8_t T[kQC * kQR];       // [column][row], row index rotated by 4 * ((column >> 3) & 15)
+  const int r0 = blockIdx.y * kQR, c0 = blockIdx.x * kQC;
   const float m = mult / (div_ptr ? *div_ptr : 1.f);
-  for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) {
-    const int rr = i / 32, cc = (i % 32) * 2;
-    float a = 0.f, b = 0.f;
-    if (r0 + rr < rows) {
-      const float f = (row_scale ? row_scale[r0 + rr] : 1.f) * m;
-      if (c0 + cc < cols) a = f * __bfloat162float(x[(size_t)(r0 + rr) * ldx + c0 + cc]);
-      if (c0 + cc + 1 < cols) b = f * __bfloat162float(x[(size_t)(r0 + rr) * ldx + c0 + cc + 1]);
+#pragma unroll
+  for (int it = 0; it < (kQR * kQC / 8) / 256; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const int rr = idx >> 4, cg = idx & 15;
+    const int r = r0 + rr, c = c0 + cg * 8;
+    uint32_t lo = 0, hi = 0;
+    if (r < rows && c < cols) {
+      const float f = (row_scale ? row_scale[r] : 1.f) * m;
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)r * ldx + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      uint16_t q[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 v = __bfloat1622float2(h[e]);
+        q[e] = cvt_fp8x2(v.x * f, v.y * f, e5m2);
+      }
+      lo = (uint32_t)q[0] | ((uint32_t)q[1] << 16);
+      hi = (uint32_t)q[2] | ((uint32_t)q[3] << 16);
+      *reinterpret_cast<uint2*>(out + (size_t)r * ldo + c) = make_uint2(lo, hi);
     }
-    const uint16_t q = cvt_fp8x2(a, b, e5m2);
-    tile[rr][cc] = (uint8_t)(q & 0xff);
-    tile[rr][cc + 1] = (uint8_t)(q >> 8);
-    if (r0 + rr < rows && c0 + cc + 1 < cols) {
-      *reinterpret_cast<uint16_t*>(out + (size_t)(r0 + rr) * ldo + c0 + cc) = q;
-    } else if (r0 + rr < rows && c0 + cc < cols) {
-      out[(size_t)(r0 + rr) * ldo + c0 + cc] = (uint8_t)(q & 0xff);
+    const int rot = 4 * (cg & 15);
+#pragma unroll
+    for (int jb = 0; jb < 8; ++jb) {
+      const uint32_t w = jb < 4 ? lo : hi;
+      T[(cg * 8 + jb) * kQR + ((rr + rot) & (kQR - 1))] = (uint8_t)(w >> (8 * (jb & 3)));
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
-    const int cc = i / 16, rr = (i % 16) * 4;
-    if (c0 + cc >= cols) continue;
-    uint8_t* dst = out_t + (size_t)(c0 + cc) * ldt + r0 + rr;
-    if (r0 + rr + 3 < rows) {
-      *reinterpret_cast<uint32_t*>(dst) = (uint32_t)tile[rr][cc] | ((uint32_t)tile[rr + 1][cc] << 8) |
-                                          ((uint32_t)tile[rr + 2][cc] << 16) | ((uint32_t)tile[rr + 3][cc] << 24);
+#pragma unroll
+  for (int it = 0; it < (kQR * kQC / 16) / 256; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const int cc = idx >> 2, seg = idx & 3;
+    const int c = c0 + cc, r = r0 + seg * 16;
+    if (c >= cols || r >= rows) continue;
+    const int rot = 4 * ((cc >> 3) & 15);
+    uint32_t w[4];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4)
+      w[q4] = *reinterpret_cast<const uint32_t*>(&T[cc * kQR + ((seg * 16 + q4 * 4 + rot) & (kQR - 1))]);
+    uint8_t* dst = out_t + (size_t)c * ldt + r;
+    if (r + 16 <= rows) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
-      for (int j = 0; j < 4; ++j)
-        if (r0 + rr + j < rows) dst[j] = tile[rr + j][cc];
+      for (int b = 0; b < 16 && r + b < rows; ++b) dst[b] = (uint8_t)(w[b >> 2] >> (8 * (b & 3)));
     }
   }
 }
@@ -385,13 +404,13 @@ extern "C" int sr_quant_fp8(const void* x, void* out, long rows, int cols, long 
 }
 
 // out [rows, ldo] and out_t [cols, ldt] (both fp8) = x[r, c] * row_scale[r] * mult / (*div_ptr), row_scale and div_ptr
-// optional. ldo and ldt must be multiples of 4 (16 for use as GEMM operands), cols even.
+// optional. cols, ldx and ldo must be multiples of 8, ldt a multiple of 16, all base pointers 16-byte aligned.
 extern "C" int sr_quant_fp8_dual(const void* x, const float* row_scale, const float* div_ptr, float mult, void* out,
                                  void* out_t, long rows, int cols, long ldx, long ldo, long ldt, int e5m2,
                                  cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
-  if (cols % 2 || ldo % 2 || ldt % 4) return -2;
-  dim3 grid((cols + 63) / 64, (unsigned)((rows + 63) / 64));
+  if (cols % 8 || ldx % 8 || ldo % 8 || ldt % 16) return -2;
+  dim3 grid((cols + kQC - 1) / kQC, (unsigned)((rows + kQR - 1) / kQR));
   quant_fp8_dual_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), row_scale, div_ptr, mult,
                                                   reinterpret_cast<uint8_t*>(out), reinterpret_cast<uint8_t*>(out_t),
                                                   (int)rows, cols, ldx, ldo, ldt, e5m2);

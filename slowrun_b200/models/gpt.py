@@ -217,6 +217,12 @@ class GPT(ArenaModelMixin, nn.Module):
             self.mtp_proj = nn.Linear(2 * c.n_embd, c.n_embd, bias=False)
             self.mtp_block = Block(c, c.n_layer)
         self.use_fused_blocks = True   # CUDA: run each block as one autograd node (ops/block.py)
+        # Optional callable(layer_index): called during backward once the gradient flowing INTO layer `layer_index`
+        # (first time it ran in the forward pass) is complete, i.e. when every weight gradient of that layer and of all
+        # later layers has been written. Index n_layer stands for the extra multi-token-prediction block. Used to start
+        # gradient reductions while the rest of the backward pass still runs.
+        self.layer_done_hook = None
+        self._hooked_layers = set()
         self.arena = None          # set by finalize()
         self.norm_eps: Optional[float] = None   # None = torch default for the activation dtype
 
@@ -438,9 +444,16 @@ class GPT(ArenaModelMixin, nn.Module):
             return ops.linear(x0, lin.fused["w16"], lin.fused["grad"])
         return F.linear(x0, lin.weight.to(x0.dtype))
 
+    def _watch_layer_input(self, i, x):
+        hook = self.layer_done_hook
+        if hook is not None and i not in self._hooked_layers and torch.is_grad_enabled() and x.requires_grad:
+            self._hooked_layers.add(i)
+            x.register_hook(lambda g, i=i: hook(i))
+
     def _layer(self, i, x, x0, skip, cos_sin, scale):
         j = i - self.encoder_layers
         block = self.transformer.h[i]
+        self._watch_layer_input(i, x)
         if x.is_cuda and self.use_fused_blocks and block_supported(self, block):
             ve_lin = self.ve_projs[str(i)] if str(i) in self.ve_projs else None
             return block_forward(self, block, x, x0, skip, i, max(j, 0), True, ve_lin, self.window_sizes[i], scale)
@@ -494,6 +507,7 @@ class GPT(ArenaModelMixin, nn.Module):
         scale = self.rotary.attn_scale if self.rotary.yarn_active else None
         if self.training and idx.is_cuda:
             ops.advance_dropout_state(idx.device)
+        self._hooked_layers = set()
         x = self._embed(idx)
         x_emb = x
         if c.num_iterations > 1 or num_iterations is not None:
@@ -521,6 +535,7 @@ class GPT(ArenaModelMixin, nn.Module):
             combined = ops.linear(cat, self.mtp_proj.fused["w16"], self.mtp_proj.fused["grad"])
         else:
             combined = F.linear(cat, self.mtp_proj.weight.to(cat.dtype))
+        self._watch_layer_input(c.n_layer, combined)
         mT = combined.size(1)
         cs = (self.rotary.cos[:, :mT], self.rotary.sin[:, :mT])
         scale = self.rotary.attn_scale if self.rotary.yarn_active else None

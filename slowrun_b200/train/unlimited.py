@@ -22,6 +22,9 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
+import copy
+import dataclasses
+
 from ..config import TrainConfig
 from ..data.loader import EnsembleTokenLoader, TokenLoader
 from ..models.gpt import build_model
@@ -31,6 +34,116 @@ from ..parallel.comm import DistInfo, TorchComm, init_distributed, print0
 from .checkpoint import load_named_params
 from .evaluate import default_token_bytes, evaluate_bpb
 from .selection import select_members
+
+
+# Per-node hyper-parameter overrides for ensemble diversity, keyed by node rank (unlimited/train.py:62-68, 1325-1330,
+# 2046). Any field of TrainConfig may be overridden (the reference uses lr_multiplier, weight_decay, label_smoothing,
+# lr_floor, warmup_frac, warmdown_frac and documents distill_alpha / distill_temperature). Filled from the
+# `node_overrides` argument of UnlimitedTrainer or from the JSON in $SLOWRUN_NODE_OVERRIDES; empty = every node alike.
+NODE_OVERRIDES: Dict[int, dict] = {}
+
+
+def config_for_node(cfg: TrainConfig, node_rank: int, overrides: Optional[Dict[int, dict]] = None) -> TrainConfig:
+    """Copy of `cfg` with this node's overrides applied; unknown keys are an error."""
+    table = dict(NODE_OVERRIDES)
+    env = os.environ.get("SLOWRUN_NODE_OVERRIDES")
+    if env:
+        table.update({int(k): v for k, v in json.loads(env).items()})
+    if overrides:
+        table.update({int(k): v for k, v in overrides.items()})
+    mine = table.get(node_rank, {})
+    out = copy.deepcopy(cfg)
+    alias = {"warmup_frac": "warmup_ratio", "warmdown_frac": "cycle_warmdown_frac"}
+    fields = {f.name for f in dataclasses.fields(out)}
+    for k, v in mine.items():
+        k = alias.get(k, k)
+        if k == "label_smoothing":
+            out.model.label_smoothing = v
+        elif k == "cycle_warmdown_frac":
+            out.cycle_warmdown_frac = v
+        elif k in fields:
+            setattr(out, k, v)
+        else:
+            raise KeyError(f"node override {k!r} is not a training option")
+    out.node_overrides = {str(k): v for k, v in table.items()}
+    return out
+
+
+class LayerBuckets:
+    """Gradient buffers grouped by the layer that writes them, as slices of the stacked arenas: the unit of the
+    reductions that run while the backward pass is still going (the reference gets this from DistributedDataParallel's
+    25 MB buckets, unlimited/train.py:1400, 1627-1630)."""
+
+    def __init__(self, model):
+        a = model.arena
+        owner = {}
+        for i, blk in enumerate(model.transformer.h):
+            for p in blk.parameters():
+                owner[id(p)] = i
+        for k, lin in model.ve_projs.items():
+            owner[id(lin.weight)] = int(k)
+        self.n_layer = len(model.transformer.h)
+        if model.mtp_weight > 0:
+            for p in list(model.mtp_block.parameters()) + list(model.mtp_proj.parameters()):
+                owner[id(p)] = self.n_layer
+        self.per_layer: Dict[int, List[torch.Tensor]] = {}
+        rest: List[torch.Tensor] = []
+        for g in a.groups.values():
+            start = 0
+            for s in range(1, g.n + 1):
+                if s == g.n or owner.get(id(g.params[s])) != owner.get(id(g.params[start])):
+                    L = owner.get(id(g.params[start]))
+                    (rest if L is None else self.per_layer.setdefault(L, [])).append(g.G[start:s])
+                    start = s
+        rest.append(a.head_grad)
+        if a.small_grads.numel():
+            rest.append(a.small_grads)
+        rest += [p.grad for p in a.other_params]
+        self.rest = rest
+
+    def all_buffers(self):
+        return [b for bs in self.per_layer.values() for b in bs] + self.rest
+
+
+class OverlappedAllReduce:
+    """Data-parallel gradient averaging that starts during the backward pass of the last micro-batch: when the
+    backward has moved past layer i, the buffers of layer i + 1 are final and their all-reduce is issued; what is left
+    (first layer, embeddings, head, small parameters) follows after the pass. One reduction per arena slice, not per
+    tensor."""
+
+    def __init__(self, model, comm: TorchComm):
+        self.model, self.comm = model, comm
+        self.buckets = LayerBuckets(model)
+        self.handles, self.launched = [], set()
+
+    def _launch(self, L):
+        if L in self.launched or L not in self.buckets.per_layer:
+            return
+        self.launched.add(L)
+        for b in self.buckets.per_layer[L]:
+            self.handles.append(self.comm.all_reduce_sum(b))
+
+    def arm(self):
+        self.handles, self.launched = [], set()
+        top = self.buckets.n_layer
+
+        def hook(i):
+            # layers are visited from the last to the first; everything above i has finished
+            for L in range(top, i, -1):
+                self._launch(L)
+        self.model.layer_done_hook = hook
+
+    def finish(self):
+        self.model.layer_done_hook = None
+        for L in sorted(self.buckets.per_layer, reverse=True):
+            self._launch(L)
+        self.handles += [self.comm.all_reduce_sum(b) for b in self.buckets.rest]
+        for h in self.handles:
+            h.wait()
+        inv = 1.0 / self.comm.world
+        for b in self.buckets.all_buffers():
+            b.mul_(inv)
+        self.handles = []
 
 
 class _Single(TorchComm):
@@ -58,7 +171,7 @@ class CyclePlan:
         self.lengths = [max(1, round(tokens_per_cycle / b)) for b in self.batch_sizes]
         self.grad_accums = [b // tokens_per_fwdbwd_node for b in self.batch_sizes]
         self.total_iterations = sum(self.lengths)
-        self.warmup_frac, self.warmdown_frac = cfg.warmup_ratio, 0.0
+        self.warmup_frac, self.warmdown_frac = cfg.warmup_ratio, float(getattr(cfg, "cycle_warmdown_frac", 0.0))
 
     def signature(self):
         return {"batch_sizes": self.batch_sizes, "lengths": self.lengths}
@@ -161,15 +274,16 @@ def target_probabilities(model, loader, steps: int) -> torch.Tensor:
 class UnlimitedTrainer:
     """Runs this node's chain of snapshots, then (all nodes) selection and ensemble evaluation."""
 
-    def __init__(self, cfg: TrainConfig, info: Optional[DistInfo] = None):
-        self.cfg = cfg
+    def __init__(self, cfg: TrainConfig, info: Optional[DistInfo] = None, node_overrides: Optional[Dict[int, dict]] = None,
+                 overlap_grad_reduce: bool = True):
         self.info = info or init_distributed(timeout_s=3 * 3600)     # nodes run unsynchronised for hours
         info = self.info
         self.device = info.device
-        c = cfg
-        gpn = min(c.gpus_per_node, info.world_size)
+        gpn = min(cfg.gpus_per_node, info.world_size)
         self.n_nodes = max(1, info.world_size // gpn)
         self.node_rank = info.rank // gpn
+        cfg = config_for_node(cfg, self.node_rank, node_overrides)
+        self.cfg = c = cfg
         self.node_local = info.rank % gpn
         self.is_leader = self.node_local == 0
         self.node_group, self.leader_group = None, None
@@ -197,6 +311,7 @@ class UnlimitedTrainer:
                                           seed=c.seed + self.node_rank, rank=self.node_local, world_size=gpn,
                                           fitness_tokens=c.fitness_tokens)
         self.plan = CyclePlan(c, len(self.model_indices), self.loader.total_tokens, c.device_batch_size * T * gpn)
+        self.reducer = OverlappedAllReduce(self.model, self.node_comm) if (overlap_grad_reduce and self.node_comm.active) else None
         self.teacher = None
         self.pgt: Dict[int, torch.Tensor] = {}
         self.results: List[dict] = []
@@ -294,8 +409,10 @@ class UnlimitedTrainer:
         c, model = self.cfg, self.model
         accum = self.plan.grad_accums[cyc]
         loss_t = None
-        for _ in range(accum):
+        for micro in range(accum):
             x, y, _ = next(self.loader)
+            if self.reducer is not None and micro == accum - 1:
+                self.reducer.arm()           # reductions of finished layers start under this micro-batch's backward
             if distilling:
                 s_logits, mtp_loss = model(x, y, distill=True)
                 with torch.no_grad():
@@ -306,7 +423,10 @@ class UnlimitedTrainer:
                 loss, _ = model(x, y, label_smoothing=c.model.label_smoothing)
             loss_t = loss.detach()
             (loss / accum).backward()
-        allreduce_gradients(model, self.node_comm)
+        if self.reducer is not None:
+            self.reducer.finish()
+        else:
+            allreduce_gradients(model, self.node_comm)
         clip_gradients(model, 1.0)
         L = self.plan.lengths[cyc]
         lrm, wdm = self.plan.lr_multiplier(step_in_cycle, L), self.plan.wd_multiplier(step_in_cycle, L)
@@ -388,58 +508,85 @@ class UnlimitedTrainer:
         out = {"models": self.results, "selection": {}, "ensemble": {}, "timing": self.timing}
         if sel is not None:
             t0 = time.time()
+            mixtures = {}
             for k, s in sel.by_k.items():
                 members = [ids[m] for m in s.members]
                 weights = s.weights if c.grad_weighted_eval else [1.0 / len(members)] * len(members)
-                bpb, loss = self.evaluate_ensemble(members, weights)
+                mixtures[k] = (members, weights)
                 out["selection"][k] = {"members": members, "weights": s.weights, "fit_loss": s.fit_loss}
+            for k, (bpb, loss) in self.evaluate_ensembles(mixtures).items():
                 out["ensemble"][k] = {"val_loss": loss, "val_bpb": bpb}
-                print0(f"ensemble K={k}: members {members} val loss {loss:.6f} bpb {bpb:.6f}")
+                print0(f"ensemble K={k}: members {mixtures[k][0]} val loss {loss:.6f} bpb {bpb:.6f}")
             self.timing["ensemble_eval"] += time.time() - t0
         if self.info.rank == 0:
             with open(os.path.join(self.ckpt_dir, "progress.json"), "w") as f:
-                json.dump(out, f, indent=2)
+                json.dump({"individual_models": self.results, **out}, f, indent=2)
             if c.save_result:
                 with open(c.save_result, "w") as f:
-                    json.dump(out, f, indent=2)
+                    json.dump(self.result_record(out), f, indent=2)
         return out
 
+    def result_record(self, out):
+        """The result file of the reference (unlimited/train.py:2161-2196): configuration, distillation and
+        perturbation settings, per-node overrides, every snapshot's validation numbers and the K sweep."""
+        c, m = self.cfg, self.cfg.model
+        rec = {
+            "config": {"n_layer": m.n_layer, "n_embd": m.n_embd, "n_head": m.n_head, "total_batch_size": c.total_batch_size,
+                       "epochs_per_cycle": c.epochs_per_cycle, "num_models": c.num_models,
+                       "dupe_layers": f"{c.dupe_layers_start}-{c.dupe_layers_end}", "dupe_after_n_models": c.dupe_after_n_models},
+            "chain_distillation": {"alpha": c.distill_alpha, "temperature": c.distill_temperature,
+                                   "after_cycles": c.distill_after_cycles, "teacher": "last_snapshot"},
+            "weight_perturbation": {"perturb_scale_max": c.perturb_scale, "perturb_scale_min": c.perturb_scale_min},
+            "node_overrides": getattr(c, "node_overrides", {}),
+            "individual_models": self.results,
+            "timing": self.timing,
+        }
+        if out["ensemble"]:
+            rec["grad_sweep"] = [{"k": k, "selected_models": [i + 1 for i in out["selection"][k]["members"]],
+                                  "weights": out["selection"][k]["weights"], "val_bpb": out["ensemble"][k]["val_bpb"],
+                                  "val_loss": out["ensemble"][k]["val_loss"], "fit_loss": out["selection"][k]["fit_loss"]}
+                                 for k in sorted(out["ensemble"])]
+            best = max(out["ensemble"])          # the largest K is the canonical final ensemble
+            rec["final_ensemble_bpb"] = out["ensemble"][best]["val_bpb"]
+            rec["final_ensemble_loss"] = out["ensemble"][best]["val_loss"]
+        return rec
+
     @torch.no_grad()
-    def evaluate_ensemble(self, members: List[int], weights: List[float]):
-        """Weighted probability mixture of snapshots on the validation set; members are sharded over all ranks and
-        their weighted target probabilities summed (unlimited/train.py:1036-1148)."""
+    def evaluate_ensembles(self, mixtures: Dict[int, tuple]):
+        """Validation loss / BPB of several weighted probability mixtures of snapshots at once
+        (unlimited/train.py:1036-1148 evaluates one mixture per call, keeping up to 64 models resident per GPU).
+        Here every snapshot that occurs in any mixture is loaded and run ONCE, by the rank it is dealt to; its
+        per-token p(target) over the evaluation batches is kept on the host (4 bytes per token), and each mixture is a
+        weighted sum of those vectors followed by one all-reduce. One model is resident per GPU at a time.
+        mixtures: {K: (member indices, weights)} -> {K: (bpb, loss)}"""
         c = self.cfg
         world, rank = self.info.world_size, self.info.rank
         if self.token_bytes is None:
             self.token_bytes = default_token_bytes(self.device, c.model.vocab_size)
         steps = max(1, c.eval_tokens // (c.device_batch_size * c.model.sequence_len))
         loader = TokenLoader(self.val_path, c.device_batch_size, c.model.sequence_len, device=self.device, prefetch=False)
-        xs, ys = [], []
-        for _ in range(steps):
-            x, y, _ = next(loader)
-            xs.append(x)
-            ys.append(y)
-        if self.teacher is None:
-            self._load_teacher(members[0])
-        acc = torch.zeros(steps, ys[0].numel(), device=self.device)
-        for m, w in list(zip(members, weights))[rank::world]:
+        batches = [next(loader)[:2] for _ in range(steps)]
+        union = sorted({m for members, _ in mixtures.values() for m in members})
+        mine = union[rank::world]
+        probs = {}
+        for m in mine:
             self._load_teacher(m)
-            for i, (x, y) in enumerate(zip(xs, ys)):
-                rows = self.teacher(x, y, loss_reduction="none").view(-1).float()
-                acc[i].add_(torch.exp(-rows), alpha=w)
-        if world > 1:
-            dist.all_reduce(acc)
-        nats = torch.zeros((), dtype=torch.float64, device=self.device)
-        nb = torch.zeros((), dtype=torch.float64, device=self.device)
-        tot = torch.zeros((), dtype=torch.float64, device=self.device)
-        ntok = 0
-        for i, y in enumerate(ys):
-            yf = y.view(-1)
-            lp = acc[i].clamp_min(1e-40).log().neg()
-            b = self.token_bytes[yf.clamp_min(0)]
-            nats += (lp * (b > 0)).sum().double()
-            nb += b.sum()
-            tot += lp[yf != -1].sum().double()
-            ntok += int((yf != -1).sum())
-        bpb = float(nats) / (math.log(2) * float(nb)) if float(nb) > 0 else float("inf")
-        return bpb, (float(tot) / ntok if ntok else float("inf"))
+            probs[m] = torch.stack([torch.exp(-self.teacher(x, y, loss_reduction="none").reshape(-1).float()) for x, y in batches]).cpu()
+        from .evaluate import _Tally
+        out = {}
+        for k, (members, weights) in mixtures.items():
+            acc = torch.zeros(steps, batches[0][1].numel(), device=self.device)
+            for m, w in zip(members, weights):
+                if m in probs:
+                    acc.add_(probs[m].to(self.device), alpha=float(w))
+            if world > 1:
+                dist.all_reduce(acc)
+            tally = _Tally(self.device, self.token_bytes)
+            for i, (_, y) in enumerate(batches):
+                tally.add(-torch.log(acc[i].clamp_min(1e-40)), y)
+            out[k] = tally.result(None)          # every rank holds the full mixture after the all-reduce
+        return out
+
+    def evaluate_ensemble(self, members: List[int], weights: List[float]):
+        """One mixture: (bpb, loss)."""
+        return self.evaluate_ensembles({0: (members, weights)})[0]
