@@ -48,10 +48,10 @@ def main():
     model = build_model(cfg.model, dev, seed=0, world_size=W, alloc=fused.alloc if fused else None)
     groups = build_param_groups(model, cfg)
     opts = {"nccl": ShardedMuonAdamW(model, groups, TorchComm())}
-    wire = os.environ.get("SLOWRUN_WIRE_DTYPE", "bf16")
     if fused is not None:
-        opts["fused"] = ShardedMuonAdamW(model, groups, fused)
+        opts["fused"] = ShardedMuonAdamW(model, groups, fused, wire_dtype="bf16")
         opts["fused_overlap"] = opts["fused"]
+        opts["fused_fp32_wire"] = ShardedMuonAdamW(model, groups, fused, wire_dtype="fp32")
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
     for ga in model.arena.groups.values():
         ga.G.normal_(0, 0.02, generator=gen)
@@ -81,7 +81,7 @@ def main():
     res = {}
     for k, o in opts.items():
         if k != "nccl":
-            o.mode = "fused_two_streams" if k == "fused_overlap" else "fused"
+            o.mode = "fused_two_streams" if k == "fused_overlap" else "fused"   # fused_fp32_wire: one stream, fp32 pulls
         res[k] = timed(o)
     if fused is not None:
         o = opts["fused"]
@@ -103,7 +103,7 @@ def main():
     # traffic and FLOPs per rank
     g_bytes = sum(ga.G.numel() * 4 for ga in model.arena.groups.values())            # fp32 stacked gradients
     u_bytes = g_bytes // 2                                                            # bf16 updates
-    rs_in = (g_bytes // W) * (W - 1) if W > 1 else 0                                  # own chunk from each of W-1 peers
+    rs_in = (g_bytes // 2 // W) * (W - 1) if W > 1 else 0                             # own chunk from each peer, bf16 wire
     ag_in = (u_bytes // W) * (W - 1) if W > 1 else 0
     ns_flops = 0.0
     for ga in model.arena.groups.values():

@@ -37,13 +37,18 @@ __device__ __forceinline__ float warp_sum(float v) {
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
 // flags: on every rank an array uint32[W]; slot s of rank d is written only by rank s.
+// mode 0: announce `epoch` to every rank, then wait until every rank has announced it (a barrier);
+// mode 1: announce only (a signal: "my work up to `epoch` is done and visible");  mode 2: wait only.
 __global__ void peer_barrier_kernel(PtrTable flags, int rank, int world, uint32_t epoch, int* status,
-                                    unsigned long long limit_ns) {
+                                    unsigned long long limit_ns, int mode) {
   const int t = threadIdx.x;
   if (t >= world) return;
   __threadfence_system();
-  uint32_t* remote = reinterpret_cast<uint32_t*>(const_cast<void*>(flags.p[t])) + rank;
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  if (mode != 2) {
+    uint32_t* remote = reinterpret_cast<uint32_t*>(const_cast<void*>(flags.p[t])) + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+  if (mode == 1) return;
   const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.p[rank]) + t;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t it = 0;
@@ -79,19 +84,49 @@ __device__ __forceinline__ float4 multimem_sum_f32x4(const float* mc_addr) {
   return v;
 }
 
+// same for a bf16 wire buffer: 16 bytes = eight gradients, summed in fp32 inside the switch, returned rounded to bf16
+__device__ __forceinline__ void multimem_sum_bf16x8(const __nv_bfloat16* mc_addr, float (&f)[8]) {
+  uint32_t a, b, c, d;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "l"(mc_addr));
+  const uint32_t w[4] = {a, b, c, d};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+__device__ __forceinline__ void add_bf16x8(const uint4& raw, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] += v.x;
+    f[2 * i + 1] += v.y;
+  }
+}
+
+// W16 = false: G_r are the ranks' fp32 gradient arenas. W16 = true: G_r (and mc) are bf16 copies of them (the wire
+// format: half the bytes over NVLink); `park` is then this rank's own fp32 arena, used as scratch as before.
+template <bool W16>
 __global__ void __launch_bounds__(kThreads, 2)
-muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int rank, long base, float* __restrict__ Mom,
+muon_pre_multi_kernel(PtrTable G, const void* __restrict__ mc_v, float* __restrict__ park_base, int world, int rank,
+                      long base, float* __restrict__ Mom,
                       __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
                       float gscale, int row_norm, const int* __restrict__ status) {
   if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;   // a barrier gave up: touch nothing
   const int lane = threadIdx.x & 31;
+  const float* mc = W16 ? nullptr : reinterpret_cast<const float*>(mc_v);
+  const __nv_bfloat16* mc16 = W16 ? reinterpret_cast<const __nv_bfloat16*>(mc_v) : nullptr;
   // at most one CTA per SM (the launcher caps the grid): the kernel is meant to share the SMs with the Newton-Schulz
   // GEMMs of the neighbouring shape group, which need one CTA's worth of registers and shared memory on every SM
   for (long row = (long)blockIdx.x * kWarps + (threadIdx.x >> 5); row < rows_total; row += (long)gridDim.x * kWarps) {
     float* m = Mom + row * c;
     __nv_bfloat16* x = X + row * c;
     const long off = base + row * c;
-    float* park = reinterpret_cast<float*>(const_cast<void*>(G.p[rank])) + off;
+    float* park = park_base + off;
     float ss = 0.f;
     // momentum update + Nesterov gradient of four reduced columns; the Nesterov value is parked in the local row
     auto consume = [&](int j, float4 gv) {
@@ -106,7 +141,50 @@ muon_pre_multi_kernel(PtrTable G, const float* __restrict__ mc, int world, int r
       ss += nv.x * nv.x + nv.y * nv.y + nv.z * nv.z + nv.w * nv.w;
       *reinterpret_cast<float4*>(park + j) = nv;
     };
-    if (mc != nullptr) {
+    if (W16) {
+      auto consume8 = [&](int j, const float (&f)[8]) {
+        consume(j, make_float4(f[0], f[1], f[2], f[3]));
+        consume(j + 4, make_float4(f[4], f[5], f[6], f[7]));
+      };
+      if (mc16 != nullptr) {
+        // NVLS: four in-switch reductions of eight gradients each in flight per lane
+        for (int j0 = lane * 8; j0 < c; j0 += 1024) {
+          float g[4][8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (j0 + u * 256 < c) multimem_sum_bf16x8(mc16 + off + j0 + u * 256, g[u]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (j0 + u * 256 < c) consume8(j0 + u * 256, g[u]);
+        }
+      } else {
+        for (int j0 = lane * 8; j0 < c; j0 += 512) {
+          const int j1 = j0 + 256;
+          const bool has1 = j1 < c;
+          float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int p0 = 0; p0 < world; p0 += kPullWorld) {
+            uint4 t0[kPullWorld], t1[kPullWorld];
+#pragma unroll
+            for (int p = 0; p < kPullWorld; ++p) {
+              if (p0 + p < world) {
+                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(G.p[p0 + p]) + off;
+                t0[p] = *reinterpret_cast<const uint4*>(src + j0);
+                if (has1) t1[p] = *reinterpret_cast<const uint4*>(src + j1);
+              }
+            }
+#pragma unroll
+            for (int p = 0; p < kPullWorld; ++p) {
+              if (p0 + p < world) {
+                add_bf16x8(t0[p], a0);
+                if (has1) add_bf16x8(t1[p], a1);
+              }
+            }
+          }
+          consume8(j0, a0);
+          if (has1) consume8(j1, a1);
+        }
+      }
+    } else if (mc != nullptr) {
       // NVLS path: eight independent in-switch reductions in flight per lane
       for (int j0 = lane * 4; j0 < c; j0 += 1024) {
         float4 g[8];
@@ -315,20 +393,38 @@ extern "C" int sr_peer_barrier(const unsigned long long* flag_ptrs, int rank, in
                                unsigned long long limit_ns, cudaStream_t s) {
   PtrTable t;
   if (!fill(t, flag_ptrs, world)) return -2;
-  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, epoch, status, limit_ns ? limit_ns : kWaitLimitNs);
+  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, epoch, status, limit_ns ? limit_ns : kWaitLimitNs, 0);
+  return rc();
+}
+// The two halves of the barrier as separate launches, on a second flag array of monotonically growing progress
+// counters: a rank signals "everything I enqueued before this on this stream is done" with a value, and a consumer on
+// any stream waits (bounded, same status reporting, site 900) until every rank's counter has reached a value.
+extern "C" int sr_peer_signal(const unsigned long long* flag_ptrs, int rank, int world, unsigned int value, cudaStream_t s) {
+  PtrTable t;
+  if (!fill(t, flag_ptrs, world)) return -2;
+  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, value, nullptr, 0, 1);
+  return rc();
+}
+extern "C" int sr_peer_wait(const unsigned long long* flag_ptrs, int rank, int world, unsigned int value, int* status,
+                            unsigned long long limit_ns, cudaStream_t s) {
+  PtrTable t;
+  if (!fill(t, flag_ptrs, world)) return -2;
+  peer_barrier_kernel<<<1, 32, 0, s>>>(t, rank, world, value, status, limit_ns ? limit_ns : kWaitLimitNs, 2);
   return rc();
 }
 
-// `rank`: index of the calling rank in g_ptrs; its own copy of the owned rows is overwritten (used as scratch).
+// `rank`: index of the calling rank in g_ptrs. `park`: this rank's own fp32 gradient arena of the group; its copy of the
+// owned rows is overwritten (used as scratch). `wire_bf16`: g_ptrs / mc address bf16 copies of the arenas (c % 8 == 0).
 // `mc`: multicast (NVLS) address of the same symmetric buffer, or null for plain peer loads.
 // `shared_sms`: 1 = at most one CTA per SM (the kernel runs beside the Newton-Schulz GEMMs on another stream),
 // 0 = two CTAs per SM (it has the GPU to itself).
-extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* mc, int world, int rank, long base,
-                                 float* Mom, void* X,
+extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const void* mc, float* park, int wire_bf16, int world,
+                                 int rank, long base, float* Mom, void* X,
                                  float* sumsq, int n, int r, int c, float mu, float gscale, int row_norm, int shared_sms,
                                  const int* status, cudaStream_t s) {
   if (n <= 0) return 0;
-  if (c % 4 || rank < 0 || rank >= world) return -2;
+  if (c % 4 || rank < 0 || rank >= world || park == nullptr) return -2;
+  if (wire_bf16 && c % 8) return -2;
   PtrTable t;
   if (!fill(t, g_ptrs, world)) return -2;
   const long rows = (long)n * r;
@@ -336,8 +432,12 @@ extern "C" int sr_muon_pre_multi(const unsigned long long* g_ptrs, const float* 
   long pull_grid = (rows + kWarps - 1) / kWarps;
   const long cap = shared_sms ? sm_count() : 2L * sm_count();
   if (pull_grid > cap) pull_grid = cap;
-  muon_pre_multi_kernel<<<(unsigned)pull_grid, kThreads, 0, s>>>(
-      t, mc, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, row_norm, status);
+  if (wire_bf16)
+    muon_pre_multi_kernel<true><<<(unsigned)pull_grid, kThreads, 0, s>>>(
+        t, mc, park, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, row_norm, status);
+  else
+    muon_pre_multi_kernel<false><<<(unsigned)pull_grid, kThreads, 0, s>>>(
+        t, mc, park, world, rank, base, Mom, reinterpret_cast<__nv_bfloat16*>(X), sumsq, rows, r, c, mu, gscale, row_norm, status);
   const long total = rows * c;
   fnorm_scale_kernel<<<grid_for(total / 2, kThreads), kThreads, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(X), sumsq, (long)r * c, total, status);
   return rc();

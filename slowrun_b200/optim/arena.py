@@ -7,6 +7,10 @@ Every Muon shape group lives in three contiguous buffers laid out in the optimiz
 so the per-rank chunk of a reduce-scatter, the owned stack of a Muon step and the fused [c_q;c_k;c_v] /
 [c_gate;c_fc] GEMM operands are all plain slices: nothing is stacked or copied per step. The reference re-stacks
 every gradient and every owned parameter on each step (train.py:677-680, 730, 760).
+With more than one rank the members of a group are ordered by (layer mod world, layer): rank r's contiguous chunk then
+holds layers r, r + world, ... instead of a block of neighbouring layers, so that while the backward pass walks down
+the network every rank's matrices become final at an even pace and their reduction can run under the rest of the
+pass (`ShardedMuonAdamW.begin_backward_overlap`). Which rank owns which matrix is internal; results do not depend on it.
 Small parameters (numel < 1024: scalars, IHA mixes, gates) share one flat gradient buffer so they need a single
 all-reduce (the reference issues one per tensor, train.py:660-662).
 """
@@ -21,10 +25,30 @@ from .groups import muon_shape_groups
 SMALL_NUMEL = 1024
 
 
+def layer_of_param(model) -> Dict[int, int]:
+    """id(parameter) -> index of the layer that writes its gradient (n_layer for the extra prediction block)."""
+    owner = {}
+    h = model.transformer.h
+    for i, blk in enumerate(h):
+        for p in blk.parameters():
+            owner[id(p)] = i
+    for k, lin in getattr(model, "ve_projs", {}).items():
+        owner[id(lin.weight)] = int(k)
+    if getattr(model, "mtp_weight", 0) > 0 and hasattr(model, "mtp_block"):
+        for p in list(model.mtp_block.parameters()) + list(model.mtp_proj.parameters()):
+            owner[id(p)] = len(h)
+    return owner
+
+
 class MuonGroupArena:
-    def __init__(self, shape, params: List[torch.nn.Parameter], world_size: int, make_shadow: bool, zeros=None):
+    def __init__(self, shape, params: List[torch.nn.Parameter], world_size: int, make_shadow: bool, zeros=None,
+                 layer_of=None):
         self.shape = tuple(shape)
+        if world_size > 1 and layer_of is not None:
+            key = {id(p): (layer_of.get(id(p), 0) % world_size, layer_of.get(id(p), 0), i) for i, p in enumerate(params)}
+            params = sorted(params, key=lambda p: key[id(p)])
         self.params = params
+        self.layers = [layer_of.get(id(p)) if layer_of is not None else None for p in params]
         n = len(params)
         r, c = self.shape
         dev = params[0].device
@@ -69,9 +93,11 @@ class ParamArena:
                 buf.copy_(p.data)
                 p.data = buf
         self.groups: Dict[tuple, MuonGroupArena] = {}
+        self.alloc = alloc
+        layer_of = layer_of_param(model) if hasattr(model, "transformer") else None
         for shape, ps in muon_shape_groups(model):
             big = cuda and shape[0] % 8 == 0 and shape[1] % 8 == 0 and shape[1] >= 64 and shape[0] >= 64
-            self.groups[tuple(shape)] = MuonGroupArena(shape, ps, world_size, make_shadow=big, zeros=zeros)
+            self.groups[tuple(shape)] = MuonGroupArena(shape, ps, world_size, make_shadow=big, zeros=zeros, layer_of=layer_of)
         # lm head
         head = model.lm_head.weight
         self.head_w16 = None

@@ -143,8 +143,12 @@ class ShardedMuonAdamW:
     """`param_groups` is the list from `groups.build_param_groups`; the training loop rewrites lr / weight_decay /
     momentum in it every step exactly as with a torch optimizer."""
 
-    def __init__(self, model, param_groups: List[dict], comm, use_cuda_kernels=None):
+    def __init__(self, model, param_groups: List[dict], comm, use_cuda_kernels=None, wire_dtype: str = "bf16"):
+        """`wire_dtype`: format in which gradients cross NVLink on the peer-memory path. "bf16": each rank rounds its
+        accumulated fp32 gradients once into a bf16 copy that the owners read (half the bytes; the sum is formed in
+        fp32); "fp32": the owners read the fp32 arenas directly. The torch.distributed path always reduces fp32."""
         self.model = model
+        self.wire_dtype = wire_dtype
         self.arena: ParamArena = model.arena
         self.param_groups = param_groups
         self.comm = comm
@@ -175,6 +179,8 @@ class ShardedMuonAdamW:
                              else torch.zeros((ga.chunk, r, c), dtype=torch.bfloat16, device=dev)),
                           U_all=torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev)
                           if (W > 1 and not (self.fused and ga.W16 is not None)) else None)
+                if self.fused and ga.W16 is not None and self.wire_dtype == "bf16" and c % 8 == 0:
+                    st["G16"] = self.comm.alloc((ga.n_pad, r, c), torch.bfloat16)
                 if self.cuda and ga.W16 is not None:
                     st["X"] = torch.empty((ga.chunk, r, c), dtype=torch.bfloat16, device=dev)
                     st["ws"] = _NSWorkspace(ga.chunk, r, c, dev)
@@ -229,6 +235,9 @@ class ShardedMuonAdamW:
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self):
+        if getattr(self, "_prepulled", False):
+            self._prepulled = False
+            return self._step_fused(prepulled=True)
         if self.fused and not self._inactive:
             return self._step_fused_tuned()
         return self._step_library()
@@ -338,9 +347,111 @@ class ShardedMuonAdamW:
             self.mode = min(times, key=times.get)
             self.tuned = {"ms": times, "mode": self.mode}
 
+    # ------------------------------------------------------------------ pieces of the peer-memory step
+    def _fast_groups(self):
+        muon = [(g, self.state[g["name"]]) for g in self.param_groups if g["kind"] == "muon"]
+        return [(g, st) for g, st in muon if "X" in st and st["arena"].W16 is not None]
+
+    def _pack_wire(self, st, slot0, n):
+        """Round this rank's fp32 gradients of slots [slot0, slot0 + n) into the bf16 wire buffer (no-op on an fp32 wire)."""
+        if "G16" not in st or n <= 0:
+            return
+        ga = st["arena"]
+        src, dst = ga.G[slot0:slot0 + n], st["G16"][slot0:slot0 + n]
+        rc = _lib.fn("sr_cast_f32_to_bf16", [c_void_p, c_void_p, c_long, c_void_p])(src.data_ptr(), dst.data_ptr(), src.numel(),
+                                                                                    _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_cast_f32_to_bf16")
+
+    def _pull(self, g, st, slot0, n, shared_sms):
+        """Owner side of the gradient reduce-scatter fused with the Muon prologue, for owned slots [slot0, slot0 + n) of
+        the group (absolute slot numbers): sum over all ranks, momentum, Nesterov, row norm, bf16 Newton-Schulz input."""
+        import ctypes
+        if n <= 0:
+            return
+        ga, comm = st["arena"], self.comm
+        r, c = ga.shape
+        cvp = ctypes.c_void_p
+        local = slot0 - self.rank * ga.chunk
+        wire16 = "G16" in st
+        src = st["G16"] if wire16 else ga.G
+        rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, cvp, c_int, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float,
+                                           c_float, c_int, c_int, cvp, cvp])(
+            ctypes.cast(comm.peer_ptrs(src), cvp), comm.multicast_ptr(src), ga.G.data_ptr(), int(wire16), self.world, self.rank,
+            slot0 * r * c, st["momentum"][local:].data_ptr(), st["X"][local:].data_ptr(), st["sumsq"][local:].data_ptr(), n, r, c,
+            float(g["momentum"]), 1.0 / self.world, int(bool(g.get("row_norm", True))), int(shared_sms),
+            _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_muon_pre_multi")
+
+    # ------------------------------------------------------------------ gradient reduction under the backward pass
+    def can_overlap_backward(self) -> bool:
+        return bool(self.fused and not self._inactive and hasattr(self.model, "layer_done_hook") and self._fast_groups())
+
+    def begin_backward_overlap(self):
+        """Call before the forward pass of the LAST micro-batch of a step (run eagerly, not from a captured graph).
+        While its backward pass walks down the network, every layer whose gradients have become final is released: this
+        rank rounds them into the wire buffer and raises its progress counter on the backward stream; on a side stream
+        the rank waits until all ranks have released that layer and pulls the matrices it owns (sum over ranks, momentum,
+        Nesterov, row norm -> Newton-Schulz input). The arenas order each shape group by (layer mod world, layer), so
+        every rank has something to pull every few layers. `finish_backward_overlap()` releases what is left; `step()`
+        then starts from the pulled inputs."""
+        if not self.can_overlap_backward():
+            return False
+        dev = self.device
+        if getattr(self, "_ov_side", None) is None:
+            self._ov_side = torch.cuda.Stream(device=dev)
+            self._progress_count = 0
+            # per layer: the runs of consecutive slots that hold its matrices, per fast group
+            self._layer_runs = {}
+            for g, st in self._fast_groups():
+                ga = st["arena"]
+                start = 0
+                for s_ in range(1, ga.n + 1):
+                    if s_ == ga.n or ga.layers[s_] != ga.layers[start]:
+                        self._layer_runs.setdefault(ga.layers[start], []).append((g, st, start, s_ - start))
+                        start = s_
+        self._ov_top = max(k for k in self._layer_runs if k is not None)
+        self._ov_next = self._ov_top          # highest layer not yet released
+        self._ov_side.wait_stream(torch.cuda.current_stream(dev))
+        self.model.layer_done_hook = self._on_layer_done
+        self._ov_active = True
+        return True
+
+    def _on_layer_done(self, i):
+        while self._ov_next > i:
+            self._release_layer(self._ov_next)
+            self._ov_next -= 1
+
+    def _release_layer(self, L):
+        runs = self._layer_runs.get(L, [])
+        for g, st, slot0, n in runs:
+            self._pack_wire(st, slot0, n)
+        self._progress_count += 1
+        value = self._progress_count
+        self.comm.signal(value)
+        with torch.cuda.stream(self._ov_side):
+            self.comm.wait_for(value)
+            for g, st, slot0, n in runs:
+                ga = st["arena"]
+                lo = max(slot0, self.rank * ga.chunk)
+                hi = min(slot0 + n, self.rank * ga.chunk + self.num_owned(ga))
+                self._pull(g, st, lo, hi - lo, shared_sms=True)
+
+    def finish_backward_overlap(self):
+        """Call after the backward pass returned: releases the layers no hook has released (the first ones)."""
+        if not getattr(self, "_ov_active", False):
+            return
+        self.model.layer_done_hook = None
+        while self._ov_next >= 0:
+            self._release_layer(self._ov_next)
+            self._ov_next -= 1
+        if None in self._layer_runs:                                # matrices outside the layer stack, if any
+            self._release_layer(None)
+        self._ov_active = False
+        self._prepulled = True
+
     # ------------------------------------------------------------------ fused peer-memory step
     @torch.no_grad()
-    def _step_fused(self):
+    def _step_fused(self, prepulled: bool = False):
         """Same update as `step()`, with every collective replaced by a kernel that reads the peers' symmetric buffers
         and consumes the data in the same pass (csrc/comm_fused.cu), pipelined over two streams:
 
@@ -363,14 +474,16 @@ class ShardedMuonAdamW:
         self._marks = []
         self._mark("start")
         main = torch.cuda.current_stream(self.device)
-        if getattr(self, "overlap", False) is True:
+        if prepulled:
+            side = self._ov_side   # the gradient pulls of this step are already queued there (begin_backward_overlap)
+        elif getattr(self, "overlap", False) is True:
             if getattr(self, "_side", None) is None:
                 self._side = torch.cuda.Stream(device=self.device)
             side = self._side
         else:
             side = main        # one stream: the same sequence, run back to back (every wait below is then a no-op)
         muon = [(g, self.state[g["name"]]) for g in self.param_groups if g["kind"] == "muon"]
-        fast = [(g, st) for g, st in muon if "X" in st and st["arena"].W16 is not None]
+        fast = self._fast_groups()
         slow = [(g, st) for g, st in muon if not ("X" in st and st["arena"].W16 is not None)]
         gathers = []
 
@@ -378,15 +491,8 @@ class ShardedMuonAdamW:
             """Side stream: gradient pull + Muon prologue of fast group i; returns the event that marks its end."""
             g, st = fast[i]
             ga = st["arena"]
-            r, c = ga.shape
-            n_own = self.num_owned(ga)
-            if n_own > 0:
-                rc = _lib.fn("sr_muon_pre_multi", [cvp, cvp, c_int, c_int, c_long, cvp, cvp, cvp, c_int, c_int, c_int, c_float, c_float, c_int, c_int, cvp, cvp])(
-                    ctypes.cast(comm.peer_ptrs(ga.G), cvp), comm.multicast_ptr(ga.G), W, rank, rank * ga.chunk * r * c,
-                    st["momentum"].data_ptr(),
-                    st["X"].data_ptr(), st["sumsq"].data_ptr(), n_own, r, c, float(g["momentum"]), gscale,
-                    int(bool(g.get("row_norm", True))), int(side is not main), status_ptr, _lib.stream_ptr())
-                _lib.check_rc(rc, "sr_muon_pre_multi")
+            if not prepulled:
+                self._pull(g, st, rank * ga.chunk, self.num_owned(ga), shared_sms=side is not main)
             ev = torch.cuda.Event()
             ev.record(side)
             return ev
@@ -418,6 +524,9 @@ class ShardedMuonAdamW:
 
         side.wait_stream(main)
         with torch.cuda.stream(side):
+            if not prepulled:
+                for g, st in fast:                       # bf16 wire: round this rank's gradients once, before the barrier
+                    self._pack_wire(st, 0, st["arena"].n)
             comm.device_barrier()                                                                  # A
             ev_a = torch.cuda.Event()
             ev_a.record(side)

@@ -46,6 +46,8 @@ class FusedComm(TorchComm):
         self.wait_limit_s = float(os.environ.get("SLOWRUN_PEER_WAIT_S", "60"))
         self.flags = self.alloc((64,), torch.int32)
         self.flag_ptrs = self.peer_ptrs(self.flags)
+        self.progress = self.alloc((64,), torch.int32)      # per-rank progress counters (signal / wait_for)
+        self.progress_ptrs = self.peer_ptrs(self.progress)
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
 
@@ -104,6 +106,22 @@ class FusedComm(TorchComm):
             ctypes.cast(self.flag_ptrs, ctypes.c_void_p), self.rank, self.world, self.epoch,
             _lib.status_buffer(self.device).data_ptr(), int(self.wait_limit_s * 1e9), _lib.stream_ptr())
         _lib.check_rc(rc, "sr_peer_barrier")
+
+    def signal(self, value: int):
+        """Publish on the current stream: everything this rank enqueued before is done; its counter becomes `value`
+        (values must grow monotonically over the run)."""
+        rc = _lib.fn("sr_peer_signal", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p])(
+            ctypes.cast(self.progress_ptrs, ctypes.c_void_p), self.rank, self.world, int(value) & 0xFFFFFFFF, _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_peer_signal")
+
+    def wait_for(self, value: int):
+        """Hold the current stream until every rank's counter has reached `value` (bounded; a wait that runs out sets
+        the status word and the kernels that follow skip their work)."""
+        rc = _lib.fn("sr_peer_wait", [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p,
+                                      ctypes.c_ulonglong, ctypes.c_void_p])(
+            ctypes.cast(self.progress_ptrs, ctypes.c_void_p), self.rank, self.world, int(value) & 0xFFFFFFFF,
+            _lib.status_buffer(self.device).data_ptr(), int(self.wait_limit_s * 1e9), _lib.stream_ptr())
+        _lib.check_rc(rc, "sr_peer_wait")
 
     # ------------------------------------------------------------------ fused primitives
     def reduce_from_peers(self, src: torch.Tensor, offset: int, out: torch.Tensor):

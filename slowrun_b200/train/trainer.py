@@ -95,7 +95,7 @@ class Trainer:
                                  alloc=self.comm.alloc if getattr(self.comm, "fused", False) else None,
                                  factory=self.model_factory())
         self.param_groups = build_param_groups(self.model, c)
-        self.optimizer = ShardedMuonAdamW(self.model, self.param_groups, self.comm)
+        self.optimizer = ShardedMuonAdamW(self.model, self.param_groups, self.comm, wire_dtype=c.wire_dtype)
         train_path = c.input_bin or os.path.join(c.data_dir, "fineweb_train.pt")
         self.val_path = c.input_val_bin or os.path.join(c.data_dir, "fineweb_val.pt")
         T = c.model.sequence_len
@@ -129,6 +129,9 @@ class Trainer:
         self._graph_key = None
         self._eager_micro = 0
         self.use_graphs = bool(c.cuda_graphs) and self.device.type == "cuda"
+        # gradient reduction under the last backward pass (peer-memory optimizer only); SLOWRUN_OVERLAP_BACKWARD=0 for A/B
+        self.overlap_backward = (os.environ.get("SLOWRUN_OVERLAP_BACKWARD", "1") != "0"
+                                 and self.optimizer.can_overlap_backward())
 
     # ------------------------------------------------------------------ one optimizer step
     def _maybe_switch_structure(self):
@@ -156,9 +159,12 @@ class Trainer:
         key = (self.dupe_active, n_iter, tuple(model.window_sizes), model.rotary.attn_scale, self.grad_accum)
         if key != self._graph_key:
             self._graph_key, self._eager_micro = key, 0
-        for _ in range(self.grad_accum):
-            graph = self._graphs.get(key) if self.use_graphs else None
-            if graph is None and self.use_graphs and self._eager_micro >= 3:
+        for micro in range(self.grad_accum):
+            # last micro-batch on the peer-memory path: run eagerly so that each layer's gradients can be released to
+            # their owners (and pulled by them on a side stream) while the backward pass is still walking down
+            overlapped = (self.overlap_backward and micro == self.grad_accum - 1 and self.optimizer.begin_backward_overlap())
+            graph = self._graphs.get(key) if (self.use_graphs and not overlapped) else None
+            if graph is None and self.use_graphs and not overlapped and self._eager_micro >= 3:
                 graph = self._capture(key, tiny, n_iter, mtp_w)
             if graph is not None:
                 graph["x"].copy_(self.x)
@@ -175,6 +181,8 @@ class Trainer:
                 loss_t = loss.detach()
                 (loss / self.grad_accum).backward()
                 self._eager_micro += 1
+                if overlapped:
+                    self.optimizer.finish_backward_overlap()
             self.x, self.y, epoch = next(self.train_loader)
         self._pending_epoch = epoch
         self.before_optimizer_step()

@@ -1,5 +1,7 @@
-"""Two-GPU checks of the peer-memory collectives: the fused optimizer step must produce the same parameters as the
-NCCL path and as a single-GPU run on the concatenated batch. Runs as child processes, one per GPU, with NVLS off."""
+"""Multi-GPU checks of the peer-memory optimizer step (one child process per GPU): every variant of the fused step
+(plain peer loads or in-switch multimem reads, bf16 or fp32 gradients on the wire, gradient pulls after the backward pass
+or under it) must leave identical parameters on all ranks and follow the torch.distributed (NCCL) step. The model has
+five layers, so the shape groups hold an odd number of matrices and the last rank owns fewer than the others."""
 import os
 import socket
 import sys
@@ -11,6 +13,18 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
+# name -> (multimem, wire dtype, pulls under the backward pass)
+VARIANTS = {
+    "nccl": None,
+    "p2p_fp32": (0, "fp32", False),
+    "p2p_bf16": (0, "bf16", False),
+    "p2p_bf16_overlap": (0, "bf16", True),
+    "mm_bf16": (1, "bf16", False),
+    "mm_bf16_overlap": (1, "bf16", True),
+    "mm_fp32_overlap": (1, "fp32", True),
+}
+STEPS, ACCUM = 3, 2
+
 
 def _free_port():
     with socket.socket() as s:
@@ -18,62 +32,121 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, mode, out):
+def _worker(rank, world, port, out):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                      MASTER_PORT=str(port), SLOWRUN_PEER_WAIT_S="20")
     from slowrun_b200.config import track_defaults
-    from slowrun_b200.models.gpt import build_model
-    from slowrun_b200.optim.groups import build_param_groups
-    from slowrun_b200.optim.muon_adamw import ShardedMuonAdamW
-    from slowrun_b200.parallel.comm import TorchComm, init_distributed, shutdown
-    from slowrun_b200.ops import _lib
+    from slowrun_b200.parallel.comm import init_distributed, shutdown
+    from slowrun_b200.parallel.fused import FusedComm
     info = init_distributed(timeout_s=120)
     cfg = track_defaults("limited")
     m = cfg.model
-    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 4, 256, 2, 2, 256
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 5, 256, 2, 2, 256
     m.dropout, m.stoch_depth = 0.0, 0.0
-    if mode == "fused":
-        from slowrun_b200.parallel.fused import FusedComm
-        comm = FusedComm()
-        model = build_model(m, info.device, seed=0, world_size=world, alloc=comm.alloc)
-    else:
-        comm = TorchComm()
-        model = build_model(m, info.device, seed=0, world_size=world)
-    opt = ShardedMuonAdamW(model, build_param_groups(model, cfg), comm)
-    assert opt.fused == (mode == "fused")
+    fused_comm = FusedComm()
     g = torch.Generator().manual_seed(7)
-    data = torch.randint(0, 50257, (3, world, 2, 257), generator=g)
-    losses = []
-    for s in range(3):
-        b = data[s, rank].to(info.device)
-        loss, _ = model(b[:, :-1], b[:, 1:])
-        loss.backward()
-        opt.step()
-        model.zero_grad_arena()
-        losses.append(float(loss.detach()))
+    data = torch.randint(0, 50257, (STEPS, ACCUM, world, 2, 257), generator=g)
+    results = {}
+    for name, var in VARIANTS.items():
+        # A failure on one rank must not leave the others behind: every rank reports after every variant, and all stop
+        # together (a rank never exits while the others still have kernels that read its memory in flight).
+        err = None
+        try:
+            _run_variant(results, name, var, info, cfg, m, fused_comm, data, rank, world)
+            torch.cuda.synchronize()
+        except Exception:  # noqa: BLE001
+            import traceback
+            err = traceback.format_exc()
+        flag = torch.tensor([1.0 if err else 0.0], device=info.device)
+        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX)
+        if flag.item() > 0:
+            results["error"] = err or "another rank failed"
+            break
+    torch.save(results, os.path.join(out, f"w{world}_r{rank}.pt"))
     torch.cuda.synchronize()
-    _lib.check_status()
-    torch.save({"losses": losses, "params": {n: p.detach().float().cpu() for n, p in model.named_parameters()}},
-               os.path.join(out, f"{mode}_r{rank}.pt"))
     torch.distributed.barrier()
     shutdown()
 
 
-@pytest.mark.timeout(600)
-def test_fused_peer_memory_step_matches_nccl_path(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+def _run_variant(results, name, var, info, cfg, m, fused_comm, data, rank, world):
+    from slowrun_b200.models.gpt import build_model
+    from slowrun_b200.optim.groups import build_param_groups
+    from slowrun_b200.optim.muon_adamw import ShardedMuonAdamW
+    from slowrun_b200.parallel.comm import TorchComm
+    from slowrun_b200.ops import _lib
+    if var is None:
+        comm = TorchComm()
+        model = build_model(m, info.device, seed=0, world_size=world)
+        opt = ShardedMuonAdamW(model, build_param_groups(model, cfg), comm)
+        overlap = False
+    else:
+        mm, wire, overlap = var
+        os.environ["SLOWRUN_MULTIMEM"] = str(mm)
+        model = build_model(m, info.device, seed=0, world_size=world, alloc=fused_comm.alloc)
+        opt = ShardedMuonAdamW(model, build_param_groups(model, cfg), fused_comm, wire_dtype=wire)
+        assert opt.fused
+        opt.mode = "fused"
+        some_group = next(iter(model.arena.groups.values()))
+        has_mc = bool(fused_comm.multicast_ptr(some_group.G))
+        if mm and not has_mc:
+            results[name] = {"skipped": "no multicast mapping"}
+            return
+        assert has_mc == bool(mm)
+        odd = [ga for ga in model.arena.groups.values() if ga.n % world]
+        assert odd, "the test model must have a shape group whose matrix count is not a multiple of the world size"
+    losses = []
+    for s in range(STEPS):
+        for a in range(ACCUM):
+            b = data[s, a, rank].to(info.device)
+            last = a == ACCUM - 1
+            if overlap and last:
+                assert opt.begin_backward_overlap()
+            loss, _ = model(b[:, :-1], b[:, 1:])
+            (loss / ACCUM).backward()
+            if overlap and last:
+                opt.finish_backward_overlap()
+        opt.step()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        model.zero_grad_arena()
+        losses.append(float(loss.detach()))
+    results[name] = {"losses": losses, "params": {n: p.detach().float().cpu() for n, p in model.named_parameters()}}
+
+
+def _rel(a, b):
+    num = sum((a[n] - b[n]).pow(2).sum() for n in a)
+    den = sum(a[n].pow(2).sum() for n in a)
+    return (num / den).sqrt().item()
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_peer_memory_step_variants_match_nccl_path(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     out = str(tmp_path)
-    for mode in ("nccl", "fused"):
-        mp.spawn(_worker, args=(2, _free_port(), mode, out), nprocs=2, join=True)
-    a0 = torch.load(os.path.join(out, "nccl_r0.pt"))
-    f0 = torch.load(os.path.join(out, "fused_r0.pt"))
-    f1 = torch.load(os.path.join(out, "fused_r1.pt"))
-    for n in f0["params"]:
-        assert torch.equal(f0["params"][n], f1["params"][n]), f"replicas diverged: {n}"
-    assert abs(a0["losses"][0] - f0["losses"][0]) < 1e-3
-    num = sum((a0["params"][n] - f0["params"][n]).pow(2).sum() for n in a0["params"])
-    den = sum(a0["params"][n].pow(2).sum() for n in a0["params"])
-    assert (num / den).sqrt().item() < 2e-2, (num / den).sqrt().item()
-    assert abs(a0["losses"][-1] - f0["losses"][-1]) < 5e-2      # both paths follow the same trajectory
+    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    res = [torch.load(os.path.join(out, f"w{world}_r{r}.pt")) for r in range(world)]
+    for r in range(world):
+        assert "error" not in res[r], f"rank {r}:\n{res[r]['error']}"
+    ref = res[0]["nccl"]
+    ran = []
+    for name in VARIANTS:
+        if name == "nccl" or "skipped" in res[0][name]:
+            continue
+        ran.append(name)
+        r0 = res[0][name]
+        for r in range(1, world):
+            for n in r0["params"]:
+                assert torch.equal(r0["params"][n], res[r][name]["params"][n]), f"{name}: replicas diverged in {n}"
+        assert abs(ref["losses"][0] - r0["losses"][0]) < 1e-3, name
+        assert _rel(ref["params"], r0["params"]) < 2e-2, (name, _rel(ref["params"], r0["params"]))
+        assert abs(ref["losses"][-1] - r0["losses"][-1]) < 5e-2, name      # same trajectory
+    assert "p2p_fp32" in ran and "p2p_bf16_overlap" in ran
+    # pulling under the backward pass changes the launch grouping, not the arithmetic
+    for a, b in (("p2p_bf16", "p2p_bf16_overlap"), ("mm_bf16", "mm_bf16_overlap")):
+        if a in ran and b in ran:
+            assert _rel(res[0][a]["params"], res[0][b]["params"]) < 2e-3, (a, b, _rel(res[0][a]["params"], res[0][b]["params"]))
+    # the bf16 wire costs at most bf16 rounding of the summed gradient
+    assert _rel(res[0]["p2p_fp32"]["params"], res[0]["p2p_bf16"]["params"]) < 1e-2
