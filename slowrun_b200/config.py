@@ -153,6 +153,7 @@ class TrainConfig:
     wire_dtype: str = "bf16"          # bf16 | fp32 : gradient reduce-scatter wire format
     cuda_graphs: bool = True          # replay each micro-batch's forward+backward as one captured CUDA graph
     max_steps: int = -1               # stop after this many optimizer steps (benchmarks/tests)
+    save_every: int = 0               # write a resume file (--resume PATH, default <run dir>/resume) every N optimizer steps
     eval_tokens: int = EVAL_TOKENS
     log_jsonl: str = ""
     wandb: bool = False
@@ -295,6 +296,9 @@ def build_parser(track: str) -> argparse.ArgumentParser:
     a("--wire-dtype", type=str, default="bf16", choices=["bf16", "fp32"])
     a("--no-cuda-graphs", action="store_false", dest="cuda_graphs")
     a("--max-steps", type=int, default=-1)
+    if track != "unlimited":
+        a("--resume", type=str, default=None, help="path prefix of the resume files (<prefix>.rank<r>); continue from them if present")
+        a("--save-every", type=int, default=0, help="write the resume files every N optimizer steps")
     a("--eval-tokens", type=int, default=EVAL_TOKENS)
     a("--log-jsonl", type=str, default="")
     a("--wandb", action="store_true")

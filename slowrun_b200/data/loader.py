@@ -158,9 +158,14 @@ class TokenLoader:
         return x, y, epoch
 
     # ------------------------------------------------------------------ resume support
-    def state(self) -> dict:
-        """Position of the next batch the CONSUMER will see (a prefetched but unconsumed batch is counted as unread)."""
-        pos = self.pos - (1 if self._next is not None else 0)
+    def state(self, rewind: int = 0) -> dict:
+        """Position of the next batch the CONSUMER will see (a prefetched but unconsumed batch is counted as unread).
+        `rewind=1`: the consumer still holds the batch it was given last and wants it delivered again after a restore
+        (a trainer that fetches one batch ahead). The epoch never rolls between a batch and the call that follows it,
+        so the rewound position lies in the current epoch."""
+        pos = self.pos - (1 if self._next is not None else 0) - int(rewind)
+        if pos < 0:
+            raise ValueError("cannot rewind past the start of the epoch")
         return {"epoch": self.epoch, "pos": pos, "order": self.order.clone()}
 
     def restore(self, st: dict):

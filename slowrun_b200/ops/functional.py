@@ -372,6 +372,20 @@ def dropout_state(device) -> torch.Tensor:
     return st
 
 
+def dropout_rng_state() -> dict:
+    """Everything the dropout masks depend on besides the call arguments, for a resume file."""
+    return {"salt": _dropout["salt"], "state": {k: int(v.item()) for k, v in _dropout["state"].items()}}
+
+
+def set_dropout_rng_state(st: dict):
+    _dropout["salt"] = int(st["salt"])
+    for key, val in st["state"].items():
+        dev = torch.device(key[0], key[1]) if key[0] == "cuda" else torch.device(key[0])
+        if key[0] == "cuda" and not torch.cuda.is_available():
+            continue
+        dropout_state(dev).fill_(int(val))
+
+
 def advance_dropout_state(device):
     """Call once per forward pass (inside the captured region when CUDA graphs are used)."""
     dropout_state(device).add_(1)

@@ -103,24 +103,40 @@ class WeightEMA:
         return True
 
 
-def save_full_state(path: str, model, optimizer, loader, step: int, extra=None, rank: int = 0):
-    """Per-rank resume file: weights (rank 0 only), this rank's optimizer shard, RNG states, loader position."""
+def save_full_state(path: str, model, optimizer, loader_state, step: int, extra=None, rank: int = 0, world_size: int = 1):
+    """Per-rank resume file `<path>.rank<r>`: weights (rank 0 only), this rank's optimizer shard, RNG states (torch CPU and
+    CUDA generators, the dropout kernels' call-site salt and device step counter), the loader position
+    (`TokenLoader.state()`), and whatever the trainer passes in `extra`. Written to a temporary name and renamed, so a run
+    killed while saving leaves the previous file intact."""
+    from ..ops import functional as ops
     state = {
         "step": step,
+        "world_size": world_size,
         "optimizer": optimizer.state_dict(),
         "rng_cpu": torch.get_rng_state(),
         "rng_cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
-        "loader": {"epoch": loader.epoch, "pos": loader.pos} if loader is not None else None,
+        "dropout": ops.dropout_rng_state(),
+        "loader": loader_state,
         "extra": extra or {},
     }
     if rank == 0:
         state["model"] = named_param_snapshot(model)
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
-    torch.save(state, f"{path}.rank{rank}")
+    tmp = f"{path}.rank{rank}.tmp"
+    torch.save(state, tmp)
+    os.replace(tmp, f"{path}.rank{rank}")
 
 
-def load_full_state(path: str, model, optimizer, rank: int = 0):
+def full_state_exists(path: str, rank: int = 0) -> bool:
+    return bool(path) and os.path.exists(f"{path}.rank{rank}") and os.path.exists(f"{path}.rank0")
+
+
+def load_full_state(path: str, model, optimizer, rank: int = 0, world_size: int = 1):
+    from ..ops import functional as ops
     state = torch.load(f"{path}.rank{rank}", map_location="cpu", weights_only=False)
+    if state.get("world_size", world_size) != world_size:
+        raise RuntimeError(f"resume file was written by {state['world_size']} ranks, this run has {world_size}: the "
+                           "optimizer state is sharded by rank and cannot be re-dealt")
     if rank == 0:
         weights = state["model"]
     else:
@@ -130,4 +146,6 @@ def load_full_state(path: str, model, optimizer, rank: int = 0):
     torch.set_rng_state(state["rng_cpu"])
     if state.get("rng_cuda") is not None and torch.cuda.is_available():
         torch.cuda.set_rng_state(state["rng_cuda"])
+    if state.get("dropout") is not None:
+        ops.set_dropout_rng_state(state["dropout"])
     return state

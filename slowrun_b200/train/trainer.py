@@ -27,7 +27,8 @@ from ..optim.muon_adamw import ShardedMuonAdamW
 from ..ops import _lib
 from ..parallel.comm import DistInfo, TorchComm, init_distributed, print0
 from ..utils.logging import RunLogger
-from .checkpoint import CheckpointRing, WeightEMA, average_checkpoints_into, recency_weights
+from .checkpoint import (CheckpointRing, WeightEMA, average_checkpoints_into, full_state_exists, load_full_state,
+                         recency_weights, save_full_state)
 from .evaluate import default_token_bytes, evaluate_bpb, evaluate_prob_avg
 from .schedules import Schedules, parse_window_schedule, window_stage_for_epoch
 
@@ -237,6 +238,45 @@ class Trainer:
         self._graphs[key] = entry
         return entry
 
+    # ------------------------------------------------------------------ stop and continue
+    def save_state(self, path: str, fit_state=None):
+        """Everything needed to continue this run at the current step on the same number of ranks: weights, this rank's
+        optimizer shard, RNG streams, the loader position (the batch already fetched for the next step is delivered
+        again), epoch / schedule flags, the weight EMA. The reference has this only for its unlimited track
+        (unlimited/train.py:1897-1918)."""
+        extra = {"current_epoch": self.current_epoch, "pending_epoch": self._pending_epoch, "smooth_loss": self.smooth_loss,
+                 "dupe_active": self.dupe_active, "fit": fit_state or {}}
+        if self.ema is not None and self.ema.ema is not None:
+            extra["ema"] = {"updates": self.ema.updates, "tensors": [e.detach().cpu() for e in self.ema.ema]}
+        save_full_state(path, self.model, self.optimizer, self.train_loader.state(rewind=1), self.step, extra,
+                        rank=self.info.rank, world_size=self.info.world_size)
+        self.comm.barrier()
+
+    def load_state(self, path: str) -> dict:
+        c = self.cfg
+        st = load_full_state(path, self.model, self.optimizer, rank=self.info.rank, world_size=self.info.world_size)
+        ex = st["extra"]
+        self.step = int(st["step"])
+        self.current_epoch, self.smooth_loss = int(ex["current_epoch"]), float(ex["smooth_loss"])
+        if ex.get("dupe_active") and not self.dupe_active:
+            self.model.set_dupe_layers(c.dupe_layers_start, c.dupe_layers_end, c.dupe_loops)
+            self.dupe_active = True
+            self.flops_per_token = self.model.estimate_flops()
+        for e in range(2, self.current_epoch + 1):       # replay the window stages: each longer window rescales the rotary
+            stage = window_stage_for_epoch(self.window_schedule, e)
+            if stage is not None and (stage.short_window != self.model.short_window or stage.long_window != self.model.long_window):
+                self.model.set_window_sizes(stage.short_window, stage.long_window, apply_yarn=True)
+                self.flops_per_token = self.model.estimate_flops()
+        if self.ema is not None and "ema" in ex:
+            self.ema.updates = int(ex["ema"]["updates"])
+            for e, saved in zip(self.ema.ema, ex["ema"]["tensors"]):
+                e.copy_(saved)
+        self.train_loader.restore(st["loader"])
+        self.x, self.y, self._pending_epoch = next(self.train_loader)
+        self._graphs, self._graph_key, self._eager_micro = {}, None, 0
+        self.comm.barrier()
+        return ex.get("fit", {})
+
     # ------------------------------------------------------------------ evaluation helpers
     def build_val_loader(self):
         c = self.cfg
@@ -282,7 +322,15 @@ class Trainer:
         ring_dir = c.logit_avg_dir if c.track in self.LOGIT_AVG_TRACKS else os.path.join(log.run_dir, "checkpoints")
         ring = CheckpointRing(ring_dir, keep, self.master)
         max_iters = c.model.num_iterations if c.track == "tiny" else None
-        if not c.eval_logit_avg:
+        resume_path = c.resume or os.path.join(log.run_dir, "resume")
+        resumed = False
+        if c.resume and full_state_exists(c.resume, info.rank):
+            fs = self.load_state(c.resume)
+            min_bpb, min_loss = fs.get("min_bpb", min_bpb), fs.get("min_loss", min_loss)
+            bad_epochs, ring.paths = fs.get("bad_epochs", 0), list(fs.get("ring_paths", []))
+            resumed = True
+            print0(f"Resumed from {c.resume} at step {self.step} (epoch {self.current_epoch})")
+        if not c.eval_logit_avg and not resumed:
             val_bpb, val_loss = self.evaluate(max_iters)
             print0(f"Step {self.step:05d} | Val BPB: {val_bpb:.6f} | Val Loss: {val_loss:.6f}")
             log.metrics({"step": self.step, "val/bpb": val_bpb, "val/loss": val_loss})
@@ -343,6 +391,9 @@ class Trainer:
                     print0(f"Updated window stage for epoch {epoch}: short={st.short_window}, long={st.long_window}, "
                            f"yarn_scale={self.model.rotary.attn_scale:.6f}")
                 self.current_epoch = epoch
+            if c.save_every > 0 and self.step % c.save_every == 0:
+                self.save_state(resume_path, {"min_bpb": min_bpb, "min_loss": min_loss, "bad_epochs": bad_epochs,
+                                              "ring_paths": list(ring.paths)})
             if c.track == "tiny" and c.max_train_steps > 0 and self.step >= c.max_train_steps:
                 print0(f"Reached max_train_steps={c.max_train_steps}")
                 break

@@ -103,3 +103,48 @@ def test_unlimited_chain_distills_selects_and_resumes(corpus, tmp_path):
     cfg.resume = "u"
     tr2 = UnlimitedTrainer(cfg, _info())
     assert tr2.try_resume() and tr2.cycle == 3 and len(tr2.results) == 3
+
+
+def test_resume_continues_bit_for_bit(corpus, tmp_path):
+    """Six steps in one go against three steps, a resume file, a fresh process-like trainer and three more: same
+    parameters, same optimizer state, same batches (dropout on, so the RNG streams are part of the state)."""
+    from slowrun_b200.train.trainer import Trainer
+
+    def make(sub):
+        cfg = _shrink(track_defaults("limited"), corpus, tmp_path / sub)
+        cfg.num_epochs, cfg.swa_last_epochs, cfg.logit_avg, cfg.dupe_start_epoch = 4, 0, 0, 2
+        cfg.dupe_layers_start, cfg.dupe_layers_end = 1, 2
+        cfg.model.dropout = 0.1
+        torch.manual_seed(1234)
+        return Trainer(cfg, _info(), quiet=True)
+
+    a = make("a")
+    losses_a = [a.train_step()["loss"] for _ in range(6)]
+    b = make("b")
+    losses_b = [b.train_step()["loss"] for _ in range(3)]
+    b.current_epoch = b._pending_epoch
+    path = str(tmp_path / "resume" / "state")
+    b.save_state(path, {"min_bpb": 1.5})
+    c = make("c")
+    torch.manual_seed(999)                       # whatever the fresh process had drawn is overwritten by the file
+    assert c.load_state(path) == {"min_bpb": 1.5}
+    assert c.step == 3 and c.dupe_active == b.dupe_active
+    losses_c = [c.train_step()["loss"] for _ in range(3)]
+    assert losses_b + losses_c == losses_a
+    for (n, p), (_, q) in zip(a.model.named_parameters(), c.model.named_parameters()):
+        assert torch.equal(p, q), n
+    sa, sc = a.optimizer.state_dict()["tensors"], c.optimizer.state_dict()["tensors"]
+    assert all(torch.equal(sa[k], sc[k]) for k in sa)
+
+
+def test_fit_writes_resume_files_and_picks_them_up(corpus, tmp_path):
+    from slowrun_b200.train.trainer import Trainer
+    cfg = _shrink(track_defaults("limited"), corpus, tmp_path)
+    cfg.num_epochs, cfg.swa_last_epochs, cfg.logit_avg, cfg.dupe_start_epoch = 2, 0, 0, 99
+    cfg.save_every, cfg.max_steps, cfg.resume = 2, 4, str(tmp_path / "r" / "state")
+    Trainer(cfg, _info(), quiet=True).fit()
+    assert os.path.exists(cfg.resume + ".rank0")
+    cfg.max_steps = 6
+    tr = Trainer(cfg, _info(), quiet=True)
+    res = tr.fit()
+    assert res["steps"] == 6 and tr.step == 6
