@@ -199,49 +199,44 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int k_hi = min(qg, p.T - 1);                              // last visible key
       const int k_lo = (p.window < 0) ? 0 : max(0, qg - p.window);    // first visible key
       const bool need_mask = (k0 + BKV - 1 > k_hi) || (k0 < k_lo);
-      // pass 1: row max
+      // The S row is read from TMEM once and stays in registers for both the maximum and the exponentials.
+      uint32_t sv[BKV];
+#pragma unroll
+      for (int ch = 0; ch < BKV / 32; ++ch)
+        tmem_ld_32x32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(sv + ch * 32));
+      tc_wait_ld();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int ch = 0; ch < BKV / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + ch * 32, v);
-        tc_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int kg = k0 + ch * 32 + j;
-            if (kg <= k_hi && kg >= k_lo) mx = fmaxf(mx, __uint_as_float(v[j]));
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+        for (int j = 0; j < BKV; ++j) {
+          const int kg = k0 + j;
+          if (!(kg <= k_hi && kg >= k_lo)) sv[j] = __float_as_uint(-INFINITY);
+          mx = fmaxf(mx, __uint_as_float(sv[j]));
         }
+      } else {
+#pragma unroll
+        for (int j = 0; j < BKV; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
+      // Lazy reference maximum: the reference point of the exponentials only moves when the row maximum has grown by
+      // more than 2^kLazyLog2 since it was set. In between, probabilities are at most 2^kLazyLog2 (exact in bf16's
+      // range), alpha is exactly 1 and O needs no rescaling; l and the log-sum-exp use the same reference, so the
+      // result is unchanged.
+      constexpr float kLazyLog2 = 8.f;
+      const float m_cand = fmaxf(m, mx * p.scale_log2);
+      const float m_new = (m == -INFINITY || m_cand - m > kLazyLog2) ? m_cand : m;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
-      // pass 2: probabilities, packed to bf16
+      // probabilities, packed to bf16 (masked entries are -inf -> 0)
       uint32_t pk[BKV / 2];
       float rs = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < BKV / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + ch * 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float e0 = exp2f(__uint_as_float(v[j]) * p.scale_log2 - m_use);
-          float e1 = exp2f(__uint_as_float(v[j + 1]) * p.scale_log2 - m_use);
-          if (need_mask) {
-            const int kg = k0 + ch * 32 + j;
-            if (!(kg <= k_hi && kg >= k_lo)) e0 = 0.f;
-            if (!(kg + 1 <= k_hi && kg + 1 >= k_lo)) e1 = 0.f;
-          }
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
-          const float2 back = __bfloat1622float2(pb);
-          rs += back.x + back.y;
-          pk[ch * 16 + j / 2] = *reinterpret_cast<const uint32_t*>(&pb);
-        }
+      for (int j = 0; j < BKV; j += 2) {
+        const float e0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -m_use));
+        const float e1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -m_use));
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
+        const float2 back = __bfloat1622float2(pb);
+        rs += back.x + back.y;
+        pk[j / 2] = *reinterpret_cast<const uint32_t*>(&pb);
       }
       l = l * alpha + rs;
       m = m_new;
