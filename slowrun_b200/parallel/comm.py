@@ -109,8 +109,12 @@ class TorchComm:
         return t
 
     def broadcast(self, t, src=0):
+        """`src` counts inside this communicator's group (rank 0 of a node group is that node's first rank)."""
         if self.active:
-            dist.broadcast(t, src=src, group=self.group)
+            if self.group is None:
+                dist.broadcast(t, src=src)
+            else:
+                dist.broadcast(t, group=self.group, group_src=src)
         return t
 
     def barrier(self):

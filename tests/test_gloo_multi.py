@@ -124,3 +124,46 @@ def test_node_overrides_apply_to_one_node_only():
     assert b.node_overrides == {"1": table[1]} and cfg.distill_alpha != 0.4
     with pytest.raises(KeyError):
         config_for_node(cfg, 0, {0: {"no_such_option": 1}})
+
+
+def _unlimited_worker(rank, world, port, corpus, work):
+    _env(rank, world, port)
+    from slowrun_b200.config import track_defaults
+    from slowrun_b200.parallel.comm import init_distributed, shutdown
+    from slowrun_b200.train.unlimited import UnlimitedTrainer
+    info = init_distributed("cpu", timeout_s=300)
+    cfg = _small(track_defaults("unlimited"), corpus, work)
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head = 2, 64, 2, 2
+    cfg.gpus_per_node = 2                                   # 4 ranks = 2 nodes of 2: two chains of 2 snapshots each
+    cfg.total_batch_size = 2 * 64 * 2
+    cfg.num_models, cfg.epochs_per_cycle, cfg.distill_after_cycles = 4, 0.1, 1
+    cfg.bs_floor = cfg.total_batch_size
+    cfg.fitness_tokens, cfg.pgt_steps, cfg.k_sweep, cfg.grad_opt_steps = 1000, 2, (2, 4), 20
+    cfg.checkpoint_base, cfg.run_name = os.path.join(work, "ck"), "u"
+    cfg.dupe_layers_start, cfg.dupe_layers_end, cfg.dupe_loops = 1, 2, 1
+    tr = UnlimitedTrainer(cfg, info, node_overrides={1: {"matrix_lr": cfg.matrix_lr * 0.5}})
+    out = tr.run()
+    torch.save({"node": tr.node_rank, "leader": tr.is_leader, "indices": tr.model_indices, "matrix_lr": tr.cfg.matrix_lr,
+                "models": out["models"], "ensemble": out["ensemble"], "selection": out["selection"]},
+               os.path.join(work, f"unl_r{rank}.pt"))
+    shutdown()
+
+
+@pytest.mark.timeout(1200)
+def test_unlimited_chains_on_two_nodes_meet_for_selection_and_ensemble(tmp_path):
+    """Ensemble training across nodes (unlimited/train.py:1870-1960, 2160-2290): each node trains its own chain with
+    data parallelism inside the node; all ranks then share the target probabilities, run the greedy selection and
+    evaluate the mixtures with the members dealt over every rank."""
+    from slowrun_b200.data.synthetic import write_synthetic_corpus
+    corpus = write_synthetic_corpus(str(tmp_path / "data"), train_tokens=12_000, val_tokens=6_000)
+    mp.spawn(_unlimited_worker, args=(4, _free_port(), corpus, str(tmp_path)), nprocs=4, join=True)
+    res = [torch.load(tmp_path / f"unl_r{r}.pt", weights_only=False) for r in range(4)]
+    assert [r["node"] for r in res] == [0, 0, 1, 1] and [r["leader"] for r in res] == [True, False, True, False]
+    assert res[0]["indices"] == [0, 1] and res[2]["indices"] == [2, 3]
+    assert res[2]["matrix_lr"] == pytest.approx(res[0]["matrix_lr"] * 0.5)          # per-node override
+    assert all(os.path.exists(tmp_path / "ck" / "u" / f"model_{i}.pt") for i in range(4))
+    for r in res[1:]:                                        # every rank ends with the same selection and the same numbers
+        assert r["selection"] == res[0]["selection"]
+        assert r["ensemble"] == res[0]["ensemble"]
+    assert set(res[0]["ensemble"]) == {2, 4} and res[0]["ensemble"][4]["val_loss"] < 11.0
