@@ -16,12 +16,15 @@ from concurrent.futures import ThreadPoolExecutor
 
 CSRC = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(CSRC)
-OUT = os.path.join(PKG, "_kernels.so")
-OBJ_DIR = os.path.join(CSRC, "build")
+# SLOWRUN_DEBUG_CHECKS=1 selects a second library built with -DSR_DEBUG_CHECKS (index and alignment checks inside the
+# kernels that report through the status word; see SR_DEBUG_CHECK in sm100_common.cuh). Both can sit side by side.
+DEBUG_CHECKS = os.environ.get("SLOWRUN_DEBUG_CHECKS", "0") == "1"
+OUT = os.path.join(PKG, "_kernels_debug.so" if DEBUG_CHECKS else "_kernels.so")
+OBJ_DIR = os.path.join(CSRC, "build_debug" if DEBUG_CHECKS else "build")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
-]
+] + (["-DSR_DEBUG_CHECKS"] if DEBUG_CHECKS else [])
 
 
 def sources() -> list[str]:

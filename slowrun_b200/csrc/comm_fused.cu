@@ -117,6 +117,13 @@ muon_pre_multi_kernel(PtrTable G, const void* __restrict__ mc_v, float* __restri
                       __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long rows_total, int r, int c, float mu,
                       float gscale, int row_norm, const int* __restrict__ status) {
   if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;   // a barrier gave up: touch nothing
+  // debug build: every peer's rows must start on a 16-byte boundary (the pulls are 16-byte vector loads)
+  {
+    const size_t esz = W16 ? 2 : 4;
+    bool aligned = ((static_cast<size_t>(base) * esz) & 15) == 0 && ((static_cast<size_t>(c) * esz) & 15) == 0;
+    for (int w = 0; w < world; ++w) aligned = aligned && (reinterpret_cast<uintptr_t>(G.p[w]) & 15) == 0;
+    if (!SR_DEBUG_CHECK(aligned, const_cast<int*>(status), 4200, c)) return;
+  }
   const int lane = threadIdx.x & 31;
   const float* mc = W16 ? nullptr : reinterpret_cast<const float*>(mc_v);
   const __nv_bfloat16* mc16 = W16 ? reinterpret_cast<const __nv_bfloat16*>(mc_v) : nullptr;

@@ -164,6 +164,8 @@ template <int BN>
 __device__ __forceinline__ void epilogue_store(const GemmParams& p, float (&f)[32], int r, int c0, bool partial,
                                                uint8_t* cbase, const uint8_t* cinbase) {
   const bool full = (c0 + 32 <= p.N);
+  // debug build: the row must lie inside the output and the column chunk must start inside it
+  if (!SR_DEBUG_CHECK(r >= 0 && r < p.M && c0 >= 0 && c0 < p.N, p.status, 4100, r)) return;
   if (partial) {
     // partial tile of an accumulate-into fp32 output: add it with 16-byte reductions
     float* dst = reinterpret_cast<float*>(cbase) + (size_t)r * p.ldc + c0;

@@ -21,6 +21,7 @@ enum StatusCode : int {
   SR_ERR_MBAR_TIMEOUT = 1,
   SR_ERR_PEER_TIMEOUT = 2,
   SR_ERR_BAD_ARG = 3,
+  SR_ERR_DEBUG_CHECK = 4,
 };
 
 // ~2 s of wall clock (globaltimer is in ns). Kernels here run for milliseconds.
@@ -43,6 +44,17 @@ __device__ __forceinline__ void report_error(int* status, int code, int site, in
     status[3] = detail;
   }
 }
+
+// Checks that only the debug build of the library carries (nvcc -DSR_DEBUG_CHECKS; `SLOWRUN_DEBUG_CHECKS=1` selects that
+// build): index and alignment invariants at the places where a wrong launch argument would turn into a stray access.
+// A failed check records code 4 with its site and a detail value in the status word, the same channel as the bounded
+// waits, and the access is skipped by the caller; nothing traps.
+#ifdef SR_DEBUG_CHECKS
+#define SR_DEBUG_CHECK(cond, status, site, detail) \
+  ((cond) ? true : (::sr::report_error((status), ::sr::SR_ERR_DEBUG_CHECK, (site), static_cast<int>(detail)), false))
+#else
+#define SR_DEBUG_CHECK(cond, status, site, detail) (true)
+#endif
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

@@ -13,7 +13,8 @@ import threading
 import torch
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-_SO = os.path.join(_PKG, "_kernels.so")
+# SLOWRUN_DEBUG_CHECKS=1 loads the library variant built with the in-kernel index/alignment checks (csrc/build.py)
+_SO = os.path.join(_PKG, "_kernels_debug.so" if os.environ.get("SLOWRUN_DEBUG_CHECKS", "0") == "1" else "_kernels.so")
 _lock = threading.Lock()
 _lib = None
 _status = {}
@@ -105,7 +106,7 @@ def check_status(device=None, reset: bool = True) -> None:
             buf.zero_()
         raise KernelStatusError(
             f"kernel status: code={vals[0]} site={vals[1]} block={vals[2]} detail={vals[3]} "
-            "(1 = mbarrier wait ran out, 2 = peer wait ran out, 3 = bad argument)")
+            "(1 = mbarrier wait ran out, 2 = peer wait ran out, 3 = bad argument, 4 = debug-build check failed)")
 
 
 def check_rc(rc: int, what: str) -> None:

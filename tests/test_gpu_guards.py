@@ -56,3 +56,32 @@ def test_forward_is_bit_reproducible_and_gradients_agree():
 
     # weight gradients leave the GEMM through split-K vector reductions whose order is not fixed
     repeat_check(grads, times=3, atol=2e-3)
+
+
+def test_debug_check_build_runs_a_step_clean():
+    """The library variant with the in-kernel index/alignment checks compiled in (SLOWRUN_DEBUG_CHECKS=1) runs a
+    ragged-shape training step without a single check firing."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import torch\n"
+        "from slowrun_b200.ops import _lib\n"
+        "assert _lib.library_path().endswith('_kernels_debug.so')\n"
+        "from slowrun_b200.config import track_defaults\n"
+        "from slowrun_b200.models.gpt import build_model\n"
+        "from slowrun_b200.optim.groups import build_param_groups\n"
+        "from slowrun_b200.optim.muon_adamw import ShardedMuonAdamW\n"
+        "from slowrun_b200.parallel.comm import TorchComm\n"
+        "cfg = track_defaults('limited'); m = cfg.model\n"
+        "m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 3, 256, 2, 2, 200\n"
+        "model = build_model(m, 'cuda:0', seed=0)\n"
+        "opt = ShardedMuonAdamW(model, build_param_groups(model, cfg), TorchComm())\n"
+        "idx = torch.randint(0, 50257, (3, 201), device='cuda:0')\n"
+        "for _ in range(2):\n"
+        "    loss, _ = model(idx[:, :-1], idx[:, 1:]); loss.backward(); opt.step(); model.zero_grad_arena()\n"
+        "torch.cuda.synchronize(); _lib.check_status(); print('debug-ok', float(loss))\n")
+    env = dict(os.environ, SLOWRUN_DEBUG_CHECKS="1")
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "debug-ok" in res.stdout, res.stdout + res.stderr
