@@ -6,12 +6,15 @@ that the ncu captures under profiles/ are taken on.
     python -m slowrun_b200.bench.kernels ce --m 8192 --v 50304
     python -m slowrun_b200.bench.kernels ns --n 4 --r 2560 --c 2560
     python -m slowrun_b200.bench.kernels lmhead_ce --m 16384 --d 2560 --v 50304 [--fp8]
+    python -m slowrun_b200.bench.kernels rowwise --m 8192 --d 2560        (memory-bound glue kernels, one line each)
+    python -m slowrun_b200.bench.kernels optim --n 8 --r 2560 --c 2560    (Muon prologue / apply, AdamW)
 Prints one JSON line per run with the achieved rate and its fraction of the measured peaks in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1590 TFLOP/s when the file is absent).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -137,9 +140,73 @@ def lmhead_ce_bench(a, hbm, tf):
     return res
 
 
+def rowwise_bench(a, hbm):
+    """The memory-bound kernels between the GEMMs on [m, d] activations; bytes = tensors each op must read and write once."""
+    from slowrun_b200.ops import functional as ops
+    M, d, dev = a.m, a.d, "cuda"
+    bf = lambda *s: torch.randn(*s, device=dev).bfloat16()
+    x, y, x0 = bf(M, d), bf(M, d), bf(M, d)
+    gf = bf(M, 2 * 4 * d // 2)                       # [gate | fc] for a SwiGLU of hidden size 2d (any even split works)
+    res = []
+
+    def add(name, fn, nbytes, bwd_of=None):
+        if bwd_of is not None:
+            outp = bwd_of()
+            g = torch.randn_like(outp)
+            fn = lambda: torch.autograd.grad(outp, inputs, g, retain_graph=True)
+        ms = timed(fn, a.iters, not a.no_flush)
+        res.append({"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+                    "frac_of_copy_peak": round(nbytes / ms / 1e6 / hbm, 3)})
+
+    e = 2.0 * M * d                                   # bytes of one bf16 [m, d] tensor
+    add("rms_norm_fwd", lambda: ops.rms_norm(x), 2 * e)
+    add("swiglu_fwd", lambda: ops.swiglu(gf), 2.0 * gf.numel() + gf.numel())
+    inputs = [gf.clone().requires_grad_(True)]
+    add("swiglu_bwd", None, 2.0 * gf.numel() * 2 + gf.numel(), bwd_of=lambda: ops.swiglu(inputs[0]))
+    add("dropout_add_fwd(p=0.1)", lambda: ops.dropout_add(x, y, 0.1, True), 3 * e)
+    lam = torch.ones(4, device=dev)
+    add("lambda_mix_fwd", lambda: ops.lambda_mix(x, x0, None, lam, lam, lam, 0, 0), 3 * e)
+    H = max(1, d // 128)
+    q = bf(1, M, H, 128)
+    cos, sin = torch.randn(1, M, 1, 64, device=dev).bfloat16(), torch.randn(1, M, 1, 64, device=dev).bfloat16()
+    add("rope_qknorm_fwd", lambda: ops.rope_qknorm(q, cos, sin), 2.0 * q.numel() * 2)
+    return {"shape": [M, d], "kernels": res}
+
+
+def optim_bench(a, hbm):
+    """Single-GPU optimizer kernels on a stack of n matrices [r, c]: bytes = every state tensor read and written once."""
+    from slowrun_b200.ops import _lib
+    P, I, F, L = _lib.c_void_p, _lib.c_int, _lib.c_float, ctypes.c_long
+    n, r, c, dev = a.n if a.n <= 64 else 8, a.r, a.c, "cuda"
+    N = n * r * c
+    G = torch.randn(n, r, c, device=dev) * 0.02
+    Mom, X, ss = torch.zeros_like(G), torch.empty(n, r, c, device=dev, dtype=torch.bfloat16), torch.zeros(n, device=dev)
+    Pm, U, W16 = torch.randn(n, r, c, device=dev), torch.randn(n, r, c, device=dev).bfloat16(), torch.empty(n, r, c, device=dev, dtype=torch.bfloat16)
+    res = []
+
+    def add(name, fn, nbytes):
+        ms = timed(fn, a.iters, not a.no_flush)
+        res.append({"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+                    "frac_of_copy_peak": round(nbytes / ms / 1e6 / hbm, 3)})
+
+    pre = _lib.fn("sr_muon_pre", [P] * 4 + [I, I, I, F, F, I, P])
+    add("muon_pre (grad -> momentum, Nesterov, row norm, bf16 X)",
+        lambda: pre(G.data_ptr(), Mom.data_ptr(), X.data_ptr(), ss.data_ptr(), n, r, c, 0.95, 1.0, 1, _lib.stream_ptr()),
+        N * (4 + 4 + 4 + 2.0))                        # G read, momentum read+write, X write (second pass served by L2 or re-read)
+    app = _lib.fn("sr_muon_apply", [P] * 3 + [L, F, F, P])
+    add("muon_apply (cautious weight decay + bf16 shadow)",
+        lambda: app(Pm.data_ptr(), U.data_ptr(), W16.data_ptr(), N, 0.02, 0.002, _lib.stream_ptr()), N * (4 + 4 + 2 + 2.0))
+    m_, v_ = torch.zeros(N, device=dev), torch.zeros(N, device=dev)
+    adam = _lib.fn("sr_adamw", [P] * 5 + [L, I] + [F] * 8 + [P])
+    add("adamw (fp32 state + bf16 shadow)",
+        lambda: adam(Pm.data_ptr(), G.data_ptr(), m_.data_ptr(), v_.data_ptr(), W16.data_ptr(), N, 0, 1e-3, 0.1, 0.8, 0.95, 1e-10,
+                     0.2, 0.05, 1.0, _lib.stream_ptr()), N * (4 * 2 + 4 + 4 * 2 + 4 * 2 + 2.0))
+    return {"shape": [n, r, c], "kernels": res}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "ce", "ns", "lmhead_ce"])
+    ap.add_argument("what", choices=["gemm", "attn", "ce", "ns", "lmhead_ce", "rowwise", "optim"])
     ap.add_argument("--d", type=int, default=2560)
     ap.add_argument("--fp8", action="store_true", help="lmhead_ce: e4m3 forward product (per-tensor scales)")
     ap.add_argument("--fwd-only", action="store_true", help="lmhead_ce: time only the forward (the small ncu workload)")
@@ -206,6 +273,10 @@ def main():
         out.update(shape=[a.m, a.v], ms=ms, gbs=byts / ms / 1e6, frac_of_peak=byts / ms / 1e6 / hbm)
     elif a.what == "lmhead_ce":
         out.update(lmhead_ce_bench(a, hbm, tf))
+    elif a.what == "rowwise":
+        out.update(rowwise_bench(a, hbm))
+    elif a.what == "optim":
+        out.update(optim_bench(a, hbm))
     else:
         from slowrun_b200.optim.muon_adamw import _NSWorkspace, newton_schulz_cuda, newton_schulz_ref
         X = (torch.randn(a.n, a.r, a.c, device="cuda") / (a.r * a.c) ** 0.5).bfloat16()

@@ -1,8 +1,8 @@
 """Where one micro-step (forward + loss + backward of one device batch) and one optimizer step spend their GPU time.
 
-    python -m slowrun_b200.bench.step_profile [--size 2.7b] [--batch 4] [--top 40]
+    python -m slowrun_b200.bench.step_profile [--track limited|tiny] [--size 2.7b] [--batch N] [--top 40]
 
-Runs the limited-track model eagerly (no CUDA graph, so kernels keep their names), times a micro-step and an optimizer
+Runs the limited-track (or tiny-track) model eagerly (no CUDA graph, so kernels keep their names), times a micro-step and an optimizer
 step with CUDA events, then records one of each with the CUPTI activity tracer (`torch.profiler`, device activities
 only) and prints per-kernel totals: name, launches, total µs, share. The times inside the traced pass are for shares
 only; the event-timed figures printed first are the ones to quote.
@@ -42,7 +42,8 @@ def kernel_table(fn, top):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--size", default="2.7b", choices=["2.7b", "default"])
-    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--track", default="limited", choices=["limited", "tiny"])
+    ap.add_argument("--batch", type=int, default=0, help="sequences per micro-batch (default: 4 limited, 32 tiny)")
     ap.add_argument("--top", type=int, default=40)
     a = ap.parse_args()
     sys.path.insert(0, ROOT)
@@ -52,8 +53,10 @@ def main():
     from slowrun_b200.optim.muon_adamw import ShardedMuonAdamW
     from slowrun_b200.parallel.comm import TorchComm
 
-    cfg = track_defaults("limited")
-    if a.size == "2.7b":
+    cfg = track_defaults(a.track)
+    tiny = a.track == "tiny"
+    a.batch = a.batch or (32 if tiny else 4)
+    if a.size == "2.7b" and not tiny:
         cfg.model.n_embd, cfg.model.n_head, cfg.model.n_kv_head = 2560, 20, 20
     model = build_model(cfg.model, "cuda", seed=0)
     opt = ShardedMuonAdamW(model, build_param_groups(model, cfg), TorchComm())
@@ -61,8 +64,13 @@ def main():
     idx = torch.randint(0, 50257, (a.batch, T), device="cuda")
     tgt = torch.randint(0, 50257, (a.batch, T), device="cuda")
 
+    mtp_w = torch.tensor([1.0, 0.5, 0.25], device="cuda") if (tiny and cfg.model.fused_mtp) else None
+
     def micro():
-        loss, _ = model(idx, tgt)
+        if tiny:
+            loss = model(idx, tgt, num_iterations=cfg.model.num_iterations, mtp_weights=mtp_w)
+        else:
+            loss, _ = model(idx, tgt)
         loss.backward()
 
     def timed(fn, n):
