@@ -1,7 +1,7 @@
 """Loss-curve parity: the unmodified reference script and this framework on the same synthetic corpus, same seed,
 same flags, dropout and stochastic depth off (their random streams differ by construction), one GPU.
 
-    python baseline/loss_parity.py [--n_layer 8 --n_embd 512 --n_head 4 --steps 20 --total-batch-size 32768]
+    python baseline/loss_parity.py [--track limited|tiny] [--n_layer 8 --n_embd 512 --n_head 4 --steps 20 --total-batch-size 32768]
 
 Each arm runs in its own process. The reference arm goes through `ref_runner` (stand-ins for tiktoken / wandb / the
 attention loader only) and its curve is what the script itself hands to `wandb_run.log` as "train/loss" (the
@@ -24,13 +24,14 @@ sys.path.insert(0, HERE)
 
 
 def flags(a):
-    return ["--n_layer", str(a.n_layer), "--n_embd", str(a.n_embd), "--n_head", str(a.n_head), "--device-batch-size",
-            str(a.device_batch_size), "--total-batch-size", str(a.total_batch_size), "--dropout", "0", "--stoch-depth", "0"]
+    f = ["--n_layer", str(a.n_layer), "--n_embd", str(a.n_embd), "--n_head", str(a.n_head), "--device-batch-size",
+         str(a.device_batch_size), "--total-batch-size", str(a.total_batch_size), "--dropout", "0"]
+    return f + (["--stoch-depth", "0"] if a.track == "limited" else [])      # the tiny script has no stochastic depth
 
 
 def arm_reference(a, data_dir):
     import ref_runner
-    res = ref_runner.run("limited", a.steps, 0, flags(a) + ["--run-name", "parity_ref"], data_dir,
+    res = ref_runner.run(a.track, a.steps, 0, flags(a) + ["--run-name", "parity_ref"], data_dir,
                          os.path.join(tempfile.gettempdir(), "slowrun_parity_work"))
     return [float(e["train/loss"]) for e in res["wandb_log"] if "train/loss" in e][:a.steps]
 
@@ -40,7 +41,7 @@ def arm_ours(a, data_dir):
     from slowrun_b200.train.trainer import Trainer
     argv = flags(a) + ["--input_bin", os.path.join(data_dir, "fineweb_train.pt"), "--input_val_bin",
                        os.path.join(data_dir, "fineweb_val.pt")]
-    cfg = config_from_args("limited", argv)
+    cfg = config_from_args(a.track, argv)
     tr = Trainer(cfg, quiet=True)
     out, smooth = [], 0.0
     for k in range(1, a.steps + 1):
@@ -53,6 +54,7 @@ def arm_ours(a, data_dir):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--arm", default="both", choices=["both", "reference", "ours"])
+    ap.add_argument("--track", default="limited", choices=["limited", "tiny"])
     ap.add_argument("--n_layer", type=int, default=8)
     ap.add_argument("--n_embd", type=int, default=512)
     ap.add_argument("--n_head", type=int, default=4)
@@ -71,7 +73,7 @@ def main():
         return
     curves = {}
     for arm in ("reference", "ours"):
-        cmd = [sys.executable, os.path.abspath(__file__), "--arm", arm, "--data-dir", data_dir] + \
+        cmd = [sys.executable, os.path.abspath(__file__), "--arm", arm, "--track", a.track, "--data-dir", data_dir] + \
               [x for kv in (("--n_layer", a.n_layer), ("--n_embd", a.n_embd), ("--n_head", a.n_head),
                             ("--device-batch-size", a.device_batch_size), ("--total-batch-size", a.total_batch_size),
                             ("--steps", a.steps)) for x in (kv[0], str(kv[1]))]

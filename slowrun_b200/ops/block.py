@@ -73,10 +73,36 @@ def iha_mix_weights(mixes, w16, H):
     return out
 
 
-def iha_mix_backward(mixes, w16, dwp, grad_w, H):
-    """grad_w (fp32) += bf16(mix)^T @ dW'; returns dmix [P, H, H] fp32."""
+def _stacked_mixes(model, attn, H, device):
+    """([3, H, H] fp32 mixing matrices, [3, H, H] view of their gradient accumulators or None). The three matrices of a
+    layer sit next to each other in the flat small-parameter arena, so both are views and nothing is launched; a model
+    without that layout (no v mix, unequal head counts) gets a stacked copy."""
+    arena = getattr(model, "arena", None)
+    if arena is not None and attn.iha_mix_v:
+        offs = [arena.small_offsets.get(id(p)) for p in (attn.q_mix, attn.k_mix, attn.v_mix)]
+        n = H * H
+        if all(o is not None and o[1] == n for o in offs) and offs[1][0] == offs[0][0] + n and offs[2][0] == offs[1][0] + n:
+            a0 = offs[0][0]
+            gacc = arena.small_grads[a0:a0 + 3 * n].view(3, H, H)
+            if attn.q_mix.grad is None or attn.q_mix.grad.data_ptr() != gacc.data_ptr():
+                gacc = None                     # the parameter's .grad no longer aliases the arena
+            return arena.small_P[a0:a0 + 3 * n].view(3, H, H), gacc
+    third = attn.v_mix.data if attn.iha_mix_v else torch.eye(H, device=device, dtype=torch.float32)
+    return torch.stack([attn.q_mix.data, attn.k_mix.data, third]), None
+
+
+def iha_mix_backward(mixes, w16, dwp, grad_w, H, dmix_acc=None):
+    """grad_w (fp32) += bf16(mix)^T @ dW'; returns dmix [P, H, H] fp32, or adds it into `dmix_acc` and returns None."""
     Pn = mixes.size(0)
     J = w16.numel() // (Pn * H)
+    if dmix_acc is not None and J % 8 == 0:
+        rc = _lib.fn("sr_iha_mix_bwd", [P, P, P, P, P, I, I, L, P])(mixes.data_ptr(), w16.data_ptr(), dwp.data_ptr(),
+                                                                   grad_w.data_ptr(), 0, Pn, H, J, _sp())
+        if rc == 0:
+            gemm(dwp.view(Pn, H, J), w16.view(Pn, H, J), out=dmix_acc, cin=dmix_acc, beta=1.0, bn=128)
+            return None
+        if rc != -7:
+            raise RuntimeError(f"sr_iha_mix_bwd: launcher returned {rc}")
     dmix = torch.zeros_like(mixes)
     # dmix[p] = dW'[p] W[p]^T: a [H x J] x [J x H] product with a very long K, done by the split-K tcgen05 GEMM
     # (every CTA takes a share of K and adds its partial H x H tile)
@@ -147,10 +173,7 @@ class _BlockFn(Function):
         fz = attn.fused
         mixes = None
         if attn.use_iha:
-            eye = None
-            if not attn.iha_mix_v:
-                eye = torch.eye(H, device=x.device, dtype=torch.float32)
-            mixes = torch.stack([attn.q_mix.data, attn.k_mix.data, attn.v_mix.data if attn.iha_mix_v else eye])
+            mixes, _ = _stacked_mixes(model, attn, H, x.device)
             w_qkv = iha_mix_weights(mixes, fz["qkv_w16"], H)
         else:
             w_qkv = fz["qkv_w16"]
@@ -251,11 +274,13 @@ class _BlockFn(Function):
         da = gemm(dqkv, w_qkv, b_mn=True)
         if mixes is not None:
             dwp = gemm(dqkv, a, a_mn=True, b_mn=True)
-            dmix = iha_mix_backward(mixes, fz["qkv_w16"], dwp, fz["qkv_grad"], H)
-            attn.q_mix.grad.add_(dmix[0])
-            attn.k_mix.grad.add_(dmix[1])
-            if attn.iha_mix_v:
-                attn.v_mix.grad.add_(dmix[2])
+            _, dmix_acc = _stacked_mixes(model, attn, H, x.device)
+            dmix = iha_mix_backward(mixes, fz["qkv_w16"], dwp, fz["qkv_grad"], H, dmix_acc)
+            if dmix is not None:
+                attn.q_mix.grad.add_(dmix[0])
+                attn.k_mix.grad.add_(dmix[1])
+                if attn.iha_mix_v:
+                    attn.v_mix.grad.add_(dmix[2])
         else:
             gemm(dqkv, a, out=fz["qkv_grad"], cin=fz["qkv_grad"], a_mn=True, b_mn=True, beta=1.0)
         # ---- gates (tiny)
