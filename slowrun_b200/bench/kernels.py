@@ -170,6 +170,38 @@ def rowwise_bench(a, hbm):
     q = bf(1, M, H, 128)
     cos, sin = torch.randn(1, M, 1, 64, device=dev).bfloat16(), torch.randn(1, M, 1, 64, device=dev).bfloat16()
     add("rope_qknorm_fwd", lambda: ops.rope_qknorm(q, cos, sin), 2.0 * q.numel() * 2)
+    # the fused block kernels, called as the block node calls them (T = 2048 tokens per sequence)
+    from slowrun_b200.ops import _lib
+    P, I, L, F32, ULL = _lib.c_void_p, _lib.c_int, ctypes.c_long, _lib.c_float, ctypes.c_ulonglong
+    sp = _lib.stream_ptr
+    T = 2048 if M % 2048 == 0 else M
+    C = H * 128
+    eps = 1e-6
+    scal = torch.tensor([1.1, 0.2, 0.7], device=dev)
+    xa, xb, sk = bf(M, d), bf(M, d), bf(M, d)
+    o1, o2 = torch.empty_like(xa), torch.empty_like(xa)
+    f = _lib.fn("sr_mix_norm_fwd", [P] * 8 + [L, I, F32, P])
+    add("mix_norm_fwd (lambda mix + skip + RMSNorm)",
+        lambda: f(xa.data_ptr(), xb.data_ptr(), sk.data_ptr(), o1.data_ptr(), o2.data_ptr(), scal.data_ptr(), scal.data_ptr() + 4,
+                  scal.data_ptr() + 8, M, d, eps, sp()), 5 * e)
+    f2 = _lib.fn("sr_add_norm_fwd", [P] * 4 + [L, I, F32, F32, ULL, P, P])
+    st = ops.dropout_state(dev)
+    add("add_norm_fwd (residual + dropout + RMSNorm)",
+        lambda: f2(xa.data_ptr(), xb.data_ptr(), o1.data_ptr(), o2.data_ptr(), M, d, eps, 0.1, 12345, st.data_ptr(), sp()), 4 * e)
+    qkv, ve = bf(M, 3 * C), bf(M, C)
+    gate = torch.rand(M, H, device=dev) * 2
+    ang = torch.rand(T, 64, device=dev) * 6.28
+    c2, s2 = ang.cos().bfloat16(), ang.sin().bfloat16()
+    qo, ko, vo = (torch.empty(M // T, T, H, 128, dtype=torch.bfloat16, device=dev) for _ in range(3))
+    f3 = _lib.fn("sr_qkv_prep_fwd", [P] * 8 + [L, I, I, F32, I, P])
+    add("qkv_prep_fwd (split + value residual + RoPE + QK-norm + key offset)",
+        lambda: f3(qkv.data_ptr(), ve.data_ptr(), gate.data_ptr(), c2.data_ptr(), s2.data_ptr(), qo.data_ptr(), ko.data_ptr(),
+                   vo.data_ptr(), M, H, T, eps, 1, sp()), 2.0 * M * C * (3 + 1 + 3))
+    alpha = torch.linspace(-0.5, 0.5, H, device=dev)
+    g01 = torch.rand(M, H, device=dev)
+    f4 = _lib.fn("sr_attn_post_fwd", [P] * 5 + [L, I, F32, P])
+    add("attn_post_fwd (head gate + XSA projection)",
+        lambda: f4(qo.data_ptr(), vo.data_ptr(), g01.data_ptr(), alpha.data_ptr(), ko.data_ptr(), M, H, 1e-4, sp()), 2.0 * M * C * 3)
     return {"shape": [M, d], "kernels": res}
 
 

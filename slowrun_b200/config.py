@@ -153,6 +153,7 @@ class TrainConfig:
     wire_dtype: str = "bf16"          # bf16 | fp32 : gradient reduce-scatter wire format
     cuda_graphs: bool = True          # replay each micro-batch's forward+backward as one captured CUDA graph
     max_steps: int = -1               # stop after this many optimizer steps (benchmarks/tests)
+    overlap_backward: bool = False    # pull each layer's gradients to their owners while the last backward pass still runs
     save_every: int = 0               # write a resume file (--resume PATH, default <run dir>/resume) every N optimizer steps
     eval_tokens: int = EVAL_TOKENS
     log_jsonl: str = ""
@@ -294,6 +295,7 @@ def build_parser(track: str) -> argparse.ArgumentParser:
     # framework switches
     a("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"])
     a("--wire-dtype", type=str, default="bf16", choices=["bf16", "fp32"])
+    a("--overlap-backward", action="store_true", help="peer-memory optimizer: gradient pulls under the last backward pass")
     a("--no-cuda-graphs", action="store_false", dest="cuda_graphs")
     a("--max-steps", type=int, default=-1)
     if track != "unlimited":

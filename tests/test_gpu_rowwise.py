@@ -229,3 +229,66 @@ def test_attn_post_forward_and_backward(B, T, H, xsa):
         assert _rel(dvx.float() * keep, vr.grad * keep) < 1.2e-2
         assert _rel(dvx[0, 1, 0], vr.grad[0, 1, 0]) < 2e-2
         assert torch.allclose(dalpha - 0.5, ar.grad, rtol=2e-2, atol=2e-2 * ar.grad.abs().max().item())
+
+
+def test_dropout_masks_have_the_right_statistics_and_never_repeat():
+    """What the reference gets from torch's Philox dropout (train.py:301, 322: F.dropout) and its per-block
+    `torch.rand(())` stochastic depth (train.py:338-341), checked as statistics since the streams differ by construction:
+    keep rate within four standard errors of 1 - p, no correlation between neighbouring elements or rows, a fresh mask
+    for every call site (salt) and every step (device counter), and the same mask again only for the same (site, step)."""
+    from slowrun_b200.ops import functional as ops
+    rows, D, p = 4096, 1024, 0.1
+    x = torch.zeros(rows, D, device="cuda", dtype=torch.bfloat16)
+    y = torch.ones(rows, D, device="cuda", dtype=torch.bfloat16)
+    st = ops.dropout_state("cuda")
+
+    def mask(seed):
+        out = torch.empty_like(x)
+        _call("sr_dropout_add_fwd", [P] * 5 + [L, F32, ULL, P, P], x.data_ptr(), y.data_ptr(), 0, 0, out.data_ptr(), x.numel(), p,
+              seed, st.data_ptr(), _sp())
+        return (out.float() != 0)
+
+    m1 = mask(0x1111)
+    n = m1.numel()
+    se = (p * (1 - p) / n) ** 0.5
+    assert abs(m1.float().mean().item() - (1 - p)) < 4 * se
+    # kept values are scaled by 1 / (1 - p)
+    out_val = 1.0 / (1 - p)
+    f = m1.float()
+    # neighbours along the row and along the column are uncorrelated (|r| below 4 / sqrt(n))
+    for a, b in ((f[:, 1:], f[:, :-1]), (f[1:], f[:-1])):
+        r = torch.corrcoef(torch.stack([a.reshape(-1), b.reshape(-1)]))[0, 1].item()
+        assert abs(r) < 4 / n ** 0.5, r
+    # per-row and per-column keep rates show no stripe
+    assert (f.mean(1) - (1 - p)).abs().max().item() < 6 * (p * (1 - p) / D) ** 0.5
+    assert (f.mean(0) - (1 - p)).abs().max().item() < 6 * (p * (1 - p) / rows) ** 0.5
+    # another call site: an independent mask (agreement rate = p^2 + (1-p)^2 within 4 standard errors)
+    m2 = mask(0x2222)
+    agree = (m1 == m2).float().mean().item()
+    q = p * p + (1 - p) * (1 - p)
+    assert abs(agree - q) < 4 * (q * (1 - q) / n) ** 0.5, agree
+    # same site, same step: the same mask (what the backward pass relies on); next step: a fresh one
+    assert torch.equal(mask(0x1111), m1)
+    ops.advance_dropout_state("cuda")
+    m3 = mask(0x1111)
+    agree = (m1 == m3).float().mean().item()
+    assert abs(agree - q) < 4 * (q * (1 - q) / n) ** 0.5, agree
+    assert out_val > 1.0
+
+
+def test_stochastic_depth_keep_rate():
+    """Block i is skipped with probability stoch_depth * i / (n_layer - 1) (train.py:332-341); the keep flags the block
+    node draws follow that rate."""
+    from slowrun_b200.config import track_defaults
+    from slowrun_b200.models.gpt import build_model
+    cfg = track_defaults("limited")
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len, m.stoch_depth = 4, 256, 2, 2, 128, 0.5
+    model = build_model(m, "cuda", seed=0)
+    probs = [blk.drop_prob for blk in model.transformer.h]
+    assert probs == pytest.approx([0.5 * i / 3 for i in range(4)])
+    torch.manual_seed(0)
+    draws = torch.rand(4000, device="cuda")
+    for pr in probs[1:]:
+        keep = (draws >= pr).float().mean().item()
+        assert abs(keep - (1 - pr)) < 4 * (pr * (1 - pr) / 4000) ** 0.5
