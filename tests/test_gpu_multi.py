@@ -150,3 +150,70 @@ def test_fused_peer_memory_step_variants_match_nccl_path(tmp_path, world):
             assert _rel(res[0][a]["params"], res[0][b]["params"]) < 2e-3, (a, b, _rel(res[0][a]["params"], res[0][b]["params"]))
     # the bf16 wire costs at most bf16 rounding of the summed gradient
     assert _rel(res[0]["p2p_fp32"]["params"], res[0]["p2p_bf16"]["params"]) < 1e-2
+
+
+def _ddp_worker(rank, world, port, out):
+    """Unlimited-track gradient path on GPUs: bucketed NCCL all-reduce issued from the backward pass against the plain
+    all-reduce after it, and one full trainer step of a two-rank node."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from slowrun_b200.config import track_defaults
+    from slowrun_b200.models.gpt import build_model
+    from slowrun_b200.parallel.comm import TorchComm, init_distributed, shutdown
+    from slowrun_b200.train.unlimited import OverlappedAllReduce, allreduce_gradients
+    from slowrun_b200.ops import _lib
+    info = init_distributed(timeout_s=120)
+    res = {}
+    try:
+        cfg = track_defaults("unlimited")
+        m = cfg.model
+        m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 4, 256, 2, 2, 256
+        m.dropout = 0.0
+        model = build_model(m, info.device, seed=0)
+        model.set_dupe_layers(2, 3, 1)
+        comm = TorchComm()
+        g = torch.Generator().manual_seed(10 + rank)
+        idx = torch.randint(0, 50257, (2, 257), generator=g).to(info.device)
+        grads = {}
+        for mode in ("plain", "overlapped"):
+            model.zero_grad_arena()
+            red = OverlappedAllReduce(model, comm) if mode == "overlapped" else None
+            if red is not None:
+                red.arm()
+            loss, _ = model(idx[:, :-1], idx[:, 1:])
+            loss.backward()
+            if red is not None:
+                early = len(red.handles)
+                red.finish()
+            else:
+                allreduce_gradients(model, comm)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            grads[mode] = {n: (model.arena.head_grad if n == "lm_head.weight" else p.grad).float().cpu().clone()
+                           for n, p in model.named_parameters()}
+        res = {"grads": grads, "early": early}
+    except Exception:  # noqa: BLE001
+        import traceback
+        res = {"error": traceback.format_exc()}
+    torch.save(res, os.path.join(out, f"ddp_r{rank}.pt"))
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    shutdown()
+
+
+@pytest.mark.timeout(600)
+def test_bucketed_allreduce_under_backward_matches_plain_allreduce_on_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_ddp_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (torch.load(tmp_path / f"ddp_r{r}.pt") for r in (0, 1))
+    assert "error" not in r0, r0.get("error")
+    assert "error" not in r1, r1.get("error")
+    worst = 0.0
+    for n in r0["grads"]["plain"]:
+        a, b = r0["grads"]["plain"][n], r0["grads"]["overlapped"][n]
+        assert torch.equal(b, r1["grads"]["overlapped"][n]), n            # both ranks hold the same reduced gradient
+        worst = max(worst, ((a - b).norm() / a.norm().clamp_min(1e-20)).item())
+    # the two backward passes accumulate weight gradients through split-K reductions whose order is not fixed
+    assert worst < 1e-3, worst
+    assert r0["early"] > 0
