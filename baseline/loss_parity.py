@@ -42,6 +42,8 @@ def arm_ours(a, data_dir):
     argv = flags(a) + ["--input_bin", os.path.join(data_dir, "fineweb_train.pt"), "--input_val_bin",
                        os.path.join(data_dir, "fineweb_val.pt")]
     cfg = config_from_args(a.track, argv)
+    if a.bf16_head:
+        cfg.model.fp8_lm_head = False      # noise floor of the fp8 head: the same run with bf16 operands in the loss head
     tr = Trainer(cfg, quiet=True)
     out, smooth = [], 0.0
     for k in range(1, a.steps + 1):
@@ -55,6 +57,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--arm", default="both", choices=["both", "reference", "ours"])
     ap.add_argument("--track", default="limited", choices=["limited", "tiny"])
+    ap.add_argument("--bf16-head", action="store_true",
+                    help="tiny: add a third curve, this framework with a bf16 loss head (how far fp8 rounding alone moves the curve)")
     ap.add_argument("--n_layer", type=int, default=8)
     ap.add_argument("--n_embd", type=int, default=512)
     ap.add_argument("--n_head", type=int, default=4)
@@ -83,10 +87,18 @@ def main():
             print(json.dumps({"arm": arm, "failed": (r.stderr or r.stdout)[-600:]}))
             return
         curves[arm] = json.loads(line[-1][6:])
+    if a.bf16_head:
+        cmd = [sys.executable, os.path.abspath(__file__), "--arm", "ours", "--bf16-head", "--track", a.track, "--data-dir", data_dir] + \
+              [x for kv in (("--n_layer", a.n_layer), ("--n_embd", a.n_embd), ("--n_head", a.n_head),
+                            ("--device-batch-size", a.device_batch_size), ("--total-batch-size", a.total_batch_size),
+                            ("--steps", a.steps)) for x in (kv[0], str(kv[1]))]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+        line = [ln for ln in r.stdout.splitlines() if ln.startswith("CURVE ")]
+        curves["ours_bf16_head"] = json.loads(line[-1][6:]) if line else None
     n = min(len(curves["reference"]), len(curves["ours"]))
     diff = [abs(curves["reference"][i] - curves["ours"][i]) for i in range(n)]
     print(json.dumps({"what": "loss_parity", "config": vars(a), "reference": curves["reference"], "ours": curves["ours"],
-                      "max_abs_diff": max(diff) if diff else None, "steps_compared": n}))
+                      "ours_bf16_head": curves.get("ours_bf16_head"), "max_abs_diff": max(diff) if diff else None, "steps_compared": n}))
 
 
 if __name__ == "__main__":

@@ -205,18 +205,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int ch = 0; ch < BKV / 32; ++ch)
         tmem_ld_32x32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(sv + ch * 32));
       tc_wait_ld();
-      float mx = -INFINITY;
+      // four independent running maxima (and sums below): one dependent chain of 64 would expose its latency, with only
+      // two softmax warps per scheduler there is nothing else to issue meanwhile
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
         for (int j = 0; j < BKV; ++j) {
           const int kg = k0 + j;
           if (!(kg <= k_hi && kg >= k_lo)) sv[j] = __float_as_uint(-INFINITY);
-          mx = fmaxf(mx, __uint_as_float(sv[j]));
+          mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < BKV; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
+        for (int j = 0; j < BKV; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // Lazy reference maximum: the reference point of the exponentials only moves when the row maximum has grown by
       // more than 2^kLazyLog2 since it was set. In between, probabilities are at most 2^kLazyLog2 (exact in bf16's
       // range), alpha is exactly 1 and O needs no rescaling; l and the log-sum-exp use the same reference, so the
@@ -228,16 +231,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
       // probabilities, packed to bf16 (masked entries are -inf -> 0)
       uint32_t pk[BKV / 2];
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < BKV; j += 2) {
         const float e0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -m_use));
         const float e1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -m_use));
         const __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
-        const float2 back = __bfloat1622float2(pb);
-        rs += back.x + back.y;
+        const float2 back = __bfloat1622float2(pb);      // the sum uses the rounded values the PV product will see
+        rs4[(j >> 1) & 3] += back.x + back.y;
         pk[j / 2] = *reinterpret_cast<const uint32_t*>(&pb);
       }
+      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l = l * alpha + rs;
       m = m_new;
       // O and the P buffer are free once the previous P V product has completed
