@@ -99,3 +99,115 @@ def test_checkpoint_roundtrip_into_reference_loader():
     load_named_params(model, rsnap)
     for n, p in model.named_parameters():
         assert torch.allclose(p.data.float(), rsnap[n])
+
+
+# ------------------------------------------------------------------ tiny track (tiny/train.py:378-946)
+def _tiny_pair(num_iterations=2):
+    from slowrun_b200.config import track_defaults
+    ref = refload.load_tiny(n_layer=4, n_embd=256, n_head=2, seq_len=64, num_iterations=num_iterations)
+    if ref is None:
+        pytest.skip("reference source not available")
+    rcfg = ref.GPTConfig(sequence_len=64, vocab_size=50257, n_layer=4, n_head=2, n_kv_head=2, n_embd=256, dropout=0.0,
+                         num_iterations=num_iterations)
+    torch.manual_seed(42)
+    with torch.device("meta"):
+        rmodel = ref.GPT(rcfg)
+    rmodel.to_empty(device="cpu")
+    rmodel.init_weights()
+    cfg = track_defaults("tiny")
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len, m.dropout, m.num_iterations = 4, 256, 2, 2, 64, 0.0, num_iterations
+    model = build_model(m, "cpu", seed=42)
+    # the tiny track starts with zero output projections, gates and XSA coefficients: move them (identically) so that every
+    # path carries signal and no gradient is pure rounding noise
+    torch.manual_seed(1)
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(rmodel.named_parameters(), model.named_parameters()):
+            if "c_proj" in n or "gate" in n or "xsa" in n or "lambdas" in n or "skip" in n:
+                d = (torch.randn(p.shape) * (0.02 if "c_proj" in n else 0.05)).to(p.dtype)
+                p.add_(d)
+                q.add_(d)
+    return ref, rmodel, model, cfg
+
+
+def test_tiny_same_seed_gives_identical_parameters():
+    ref = refload.load_tiny()
+    if ref is None:
+        pytest.skip("reference source not available")
+    from slowrun_b200.config import track_defaults
+    rcfg = ref.GPTConfig(sequence_len=64, vocab_size=50257, n_layer=4, n_head=2, n_kv_head=2, n_embd=256, dropout=0.0)
+    torch.manual_seed(7)
+    with torch.device("meta"):
+        rmodel = ref.GPT(rcfg)
+    rmodel.to_empty(device="cpu")
+    rmodel.init_weights()
+    cfg = track_defaults("tiny")
+    m = cfg.model
+    m.n_layer, m.n_embd, m.n_head, m.n_kv_head, m.sequence_len = 4, 256, 2, 2, 64
+    model = build_model(m, "cpu", seed=7)
+    rp, mp = dict(rmodel.named_parameters()), dict(model.named_parameters())
+    assert list(rp) == list(mp)
+    for k in rp:
+        assert rp[k].dtype == mp[k].dtype and torch.equal(rp[k].detach(), mp[k].detach()), k
+
+
+@pytest.mark.parametrize("iters", [1, 2])
+def test_tiny_loss_and_grads_match_reference(iters):
+    """Shifted-target multi-token loss through the shared head, XSA, key offset, truncated RoPE, recurrence with only the
+    last pass back-propagated: loss and every gradient against the reference's tiny model."""
+    _, rmodel, model, _ = _tiny_pair()
+    rmodel.train()
+    model.train()
+    g = torch.Generator().manual_seed(0)
+    idx = torch.randint(0, 50257, (2, 65), generator=g)
+    x, y = idx[:, :-1], idx[:, 1:]
+    w = torch.tensor([1.0, 0.5, 0.25])
+    rl = rmodel(x, y, num_iterations=iters, mtp_weights=w).mean()
+    ml = model(x, y, num_iterations=iters, mtp_weights=w)
+    assert torch.allclose(rl, ml, rtol=1e-5, atol=1e-5), (rl.item(), ml.item())
+    rl.backward()
+    ml.backward()
+    for (n, p), (_, q) in zip(rmodel.named_parameters(), model.named_parameters()):
+        gq = q.grad if q.grad is not None else model.arena.head_grad
+        rel = ((p.grad.float() - gq.float()).norm() / p.grad.float().norm().clamp_min(1e-20)).item()
+        assert rel < 3e-3, (n, rel)
+
+
+def test_tiny_first_optimizer_step_follows_reference():
+    """One step of the reference's tiny optimizer against ours from identical gradients. Newton-Schulz maps every
+    singular value to about one, so rounding-level differences in weak directions come back at the scale of the update;
+    AdamW's first step is lr * sign(g), so only the sign pattern and the step size are comparable element by element."""
+    ref, rmodel, model, cfg = _tiny_pair()
+    from slowrun_b200.optim.groups import build_param_groups
+    from slowrun_b200.optim.muon_adamw import ShardedMuonAdamW
+    from slowrun_b200.parallel.comm import TorchComm
+    ropt = rmodel.setup_optimizer()
+    groups = build_param_groups(model, cfg)
+    opt = ShardedMuonAdamW(model, groups, TorchComm())
+    for grp in list(ropt.param_groups) + list(groups):
+        if grp["kind"] == "muon":
+            grp["momentum"] = 0.85
+    rmodel.train()
+    model.train()
+    before = {n: p.detach().float().clone() for n, p in rmodel.named_parameters()}
+    g = torch.Generator().manual_seed(0)
+    idx = torch.randint(0, 50257, (2, 65), generator=g)
+    w = torch.tensor([1.0, 0.5, 0.25])
+    rmodel(idx[:, :-1], idx[:, 1:], num_iterations=1, mtp_weights=w).mean().backward()
+    model(idx[:, :-1], idx[:, 1:], num_iterations=1, mtp_weights=w).backward()
+    ropt.step()
+    opt.step()
+    for (n, p), (_, q) in zip(rmodel.named_parameters(), model.named_parameters()):
+        pf, qf = p.detach().float(), q.detach().float()
+        upd_r, upd_o = pf - before[n], qf - before[n]
+        assert upd_r.norm() > 0, n
+        if n in ("lm_head.weight", "transformer.wte.weight") or p.dim() < 2 or "attn_gate" in n:
+            # AdamW: same step size, same direction for all but the elements whose gradient is rounding noise
+            assert abs(upd_o.norm().item() / upd_r.norm().item() - 1) < 0.05, n
+            moved = upd_r != 0
+            agree = (upd_r.sign() == upd_o.sign())[moved].float().mean().item()
+            assert agree > 0.95, (n, agree)
+        else:
+            assert ((pf - qf).norm() / pf.norm()).item() < 2e-2, n
+            cos = (upd_r.flatten() @ upd_o.flatten() / (upd_r.norm() * upd_o.norm())).item()
+            assert cos > 0.97, (n, cos)
