@@ -1,20 +1,13 @@
 // Flash attention forward for sm_100a: causal with a left sliding window, head_dim 128, bf16, (B, T, H, D) layout.
 //
-// One CTA per (batch*head, 128-query tile). Warp roles (320 threads):
+// One CTA per (batch*head, 128-query tile). Warp roles (192 threads):
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles (128 keys) through a 2-stage ring
 //   warp 1      MMA issuer + TMEM owner:  S_j = Q K_j^T   (SS, both operands K-major, accumulator in TMEM)
 //                                          O  += P_j V_j   (SS, P from shared memory, V_j as an MN-major operand)
-//   warps 2..9  softmax: query row i (TMEM lane i) is shared by two threads, one in warp 2 + (i/32 + 2) % 4 ... for the
-//               first half of the key columns of a tile and one four warps further for the second half (a warp may
-//               only touch the TMEM lanes of its quarter, so the split is by columns). Both read the whole S_j row
-//               from TMEM and form the same row maximum (cheap, and it spares a hand-shake per tile), so both keep the
-//               same running reference maximum; each computes the exponentials of its own half only, sums them,
-//               rescales its half of O in TMEM when the reference moved, writes its half of P_j (bf16) into shared
-//               memory in the 128B-swizzled K-major layout, and at the end the two exchange their partial sums
-//               (through the then idle P buffer, one flag byte per thread, bounded spin) and write their half of
-//               O / l (the first also the log-sum-exp). Eight softmax warps instead of four put two warps of each CTA
-//               on every scheduler: the chain TMEM read -> exponentials -> conversion -> store is latency-bound,
-//               not issue-bound.
+//   warps 2..5  softmax: thread i owns query row i (TMEM lane i), so row max / row sum need no shuffles. They read
+//               S_j from TMEM, apply scale + mask, keep running (m, l), rescale O in TMEM when the max moved,
+//               write P_j (bf16) into shared memory in the 128B-swizzled K-major layout, and at the end write
+//               O / l and the log-sum-exp.
 // S is double buffered in TMEM so S_{j+1} is computed while the softmax of tile j runs.
 // Keys visible to query i: max(0, i - window) <= k <= i  (window < 0 means unlimited), the convention of
 // flash_attn's window_size=(window, 0) that the reference uses (train.py:211-213, 432-438).
@@ -25,8 +18,7 @@ namespace {
 using namespace sr;
 
 constexpr int BQ = 128, D = 128;
-constexpr int kThreads = 320;
-constexpr int kXchBytes = 2 * BQ;              // one flag byte per softmax thread for the final exchange of the row sums
+constexpr int kThreads = 192;
 constexpr uint32_t kQBytes = BQ * D * 2;           // 32 KB
 constexpr uint32_t kQHalf = BQ * 128;              // one 64-column half of a 128-row tile: 128 rows x 128 B
 
@@ -37,7 +29,7 @@ struct FwdCfg {
   static constexpr uint32_t kKVHalf = BKV * 128;          // 64 d-columns of a K/V tile
   static constexpr uint32_t kPBytes = BQ * BKV * 2;
   static constexpr uint32_t kTmemCols = (BKV == 128) ? 512 : 256;   // 2 S buffers + O
-  static constexpr int kSmemBytes = kQBytes + 4 * kKVBytes + kPBytes + 256 + kXchBytes;
+  static constexpr int kSmemBytes = kQBytes + 4 * kKVBytes + kPBytes + 256;
 };
 
 struct FwdParams {
@@ -73,12 +65,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* v_full = bars + 3;        // 2
   uint64_t* kv_empty = bars + 5;      // 2
   uint64_t* s_full = bars + 7;        // 2
-  uint64_t* p_full = bars + 9;        // 1 (count 256)
+  uint64_t* p_full = bars + 9;        // 1 (count 128)
   uint64_t* pv_done = bars + 10;      // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile uint8_t* xflag = reinterpret_cast<volatile uint8_t*>(sP + C_::kPBytes + 256);
-  for (int i = threadIdx.x; i < 2 * BQ; i += kThreads) xflag[i] = 0;      // 0 = partial row sum not yet published
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.T + BQ - 1) / BQ;
@@ -98,7 +88,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
-    mbar_init(p_full, 256);
+    mbar_init(p_full, 128);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
     if ((smem_u32(smem) & 1023u) != 0u) report_error(p.status, SR_ERR_BAD_ARG, 1000, 0);   // swizzle needs 1 KB alignment
@@ -193,13 +183,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
-    constexpr int HC = BKV / 2;                // key columns of a tile per thread
-    const int q = warp & 3;                    // TMEM lane quarter this warp may access
-    const int chalf = (warp - 2) >> 2;         // which half of the columns
+    const int q = warp & 3;
     const int r = q * 32 + lane;               // row inside the tile == TMEM lane
     const int qg = q0 + r;                     // global query index
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const int cbase = chalf * HC;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int it = 0; it < n_kv; ++it) {
@@ -207,62 +194,46 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tmem_S + lane_addr + static_cast<uint32_t>((it & 1) * BKV + cbase);
+      const uint32_t tS = tmem_S + lane_addr + static_cast<uint32_t>((it & 1) * BKV);
       const int k0 = (j_lo + it) * BKV;
       const int k_hi = min(qg, p.T - 1);                              // last visible key
       const int k_lo = (p.window < 0) ? 0 : max(0, qg - p.window);    // first visible key
       const bool need_mask = (k0 + BKV - 1 > k_hi) || (k0 < k_lo);
-      // This thread's half of the S row stays in registers for the exponentials; the partner's half is read as well,
-      // for the row maximum only.
-      uint32_t sv[HC];
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // independent chains
-      {
-        uint32_t ov[HC];
-        const uint32_t tOther = tmem_S + lane_addr + static_cast<uint32_t>((it & 1) * BKV + (HC - cbase));
+      // The S row is read from TMEM once and stays in registers for both the maximum and the exponentials.
+      uint32_t sv[BKV];
 #pragma unroll
-        for (int ch = 0; ch < HC / 32; ++ch) {
-          tmem_ld_32x32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(sv + ch * 32));
-          tmem_ld_32x32(tOther + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(ov + ch * 32));
-        }
-        tc_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int j = 0; j < HC; ++j) {
-            const int kg = k0 + (HC - cbase) + j;
-            if (kg <= k_hi && kg >= k_lo) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(ov[j]));
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < HC; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(ov[j]));
-        }
-      }
+      for (int ch = 0; ch < BKV / 32; ++ch)
+        tmem_ld_32x32(tS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(sv + ch * 32));
+      tc_wait_ld();
+      // four independent running maxima (and sums below): one dependent chain of 64 would expose its latency, with only
+      // two softmax warps per scheduler there is nothing else to issue meanwhile
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < HC; ++j) {
-          const int kg = k0 + cbase + j;
+        for (int j = 0; j < BKV; ++j) {
+          const int kg = k0 + j;
           if (!(kg <= k_hi && kg >= k_lo)) sv[j] = __float_as_uint(-INFINITY);
           mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < HC; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
+        for (int j = 0; j < BKV; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[j]));
       }
-      // max is exact and order-independent: both threads of the row obtain the same value
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // Lazy reference maximum: the reference point of the exponentials only moves when the row maximum has grown by
       // more than 2^kLazyLog2 since it was set. In between, probabilities are at most 2^kLazyLog2 (exact in bf16's
       // range), alpha is exactly 1 and O needs no rescaling; l and the log-sum-exp use the same reference, so the
-      // result is unchanged. Both threads of a row see the same maximum and take the same decision.
+      // result is unchanged.
       constexpr float kLazyLog2 = 8.f;
       const float m_cand = fmaxf(m, mx * p.scale_log2);
       const float m_new = (m == -INFINITY || m_cand - m > kLazyLog2) ? m_cand : m;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
       // probabilities, packed to bf16 (masked entries are -inf -> 0)
-      uint32_t pk[HC / 2];
+      uint32_t pk[BKV / 2];
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < HC; j += 2) {
+      for (int j = 0; j < BKV; j += 2) {
         const float e0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -m_use));
         const float e1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -m_use));
         const __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
@@ -270,7 +241,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         rs4[(j >> 1) & 3] += back.x + back.y;
         pk[j / 2] = *reinterpret_cast<const uint32_t*>(&pb);
       }
-      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));      // this thread's columns only
+      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      l = l * alpha + rs;
       m = m_new;
       // O and the P buffer are free once the previous P V product has completed
       if (it > 0) {
@@ -281,7 +253,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (!__all_sync(0xffffffffu, alpha == 1.f)) {
           const uint32_t tO = tmem_O + lane_addr;
 #pragma unroll 1
-          for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {          // this thread's 64 of the 128 output columns
+          for (int ch = 0; ch < 4; ++ch) {
             uint32_t v[32];
             tmem_ld_32x32(tO + ch * 32, v);
             tc_wait_ld();
@@ -292,52 +264,28 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           tc_wait_st();
         }
       }
-      // this thread's part of the P row -> shared memory (K-major, 128B swizzle), chunks of 8 keys
+      // P row -> shared memory (K-major, 128B swizzle): 16 chunks of 8 keys
 #pragma unroll
-      for (int c = 0; c < HC / 8; ++c) {
-        const uint32_t off = sw128_offset(r, cbase + c * 8, kQHalf);
+      for (int c = 0; c < BKV / 8; ++c) {
+        const uint32_t off = sw128_offset(r, c * 8, kQHalf);
         *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
     }
-    float l_other = 0.f;
     if (ok) {
       ok = mbar_wait(pv_done, (n_kv - 1) & 1u, abort_flag, p.status, 1302);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
-      // the last P V product is done: the P buffer is idle and carries the partial row sums across the two halves
-      volatile float* lsum = reinterpret_cast<volatile float*>(sP);
-      lsum[chalf * BQ + r] = l;
-      __threadfence_block();
-      xflag[chalf * BQ + r] = 1;
-      uint32_t spins = 0;
-      while (xflag[(chalf ^ 1) * BQ + r] == 0) {
-        if ((++spins & 1023u) == 0u) {
-          if (*abort_flag) { ok = false; break; }
-          if (spins > (1u << 25)) {
-            *abort_flag = 1;
-            report_error(p.status, SR_ERR_MBAR_TIMEOUT, 1310, r);
-            ok = false;
-            break;
-          }
-        }
-      }
-      __threadfence_block();
-      l_other = lsum[(chalf ^ 1) * BQ + r];
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
       tc_fence_after();
-      const float lt = l + l_other;
-      const float inv = (lt > 0.f) ? 1.f / lt : 0.f;
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
       const uint32_t tO = tmem_O + lane_addr;
       const bool row_ok = qg < p.T;
       __nv_bfloat16* orow = p.out + (((size_t)b * p.T + (row_ok ? qg : 0)) * p.H + h) * D;
 #pragma unroll 1
-      for (int ch = chalf * 2; ch < chalf * 2 + 2; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         uint32_t v[32];
         tmem_ld_32x32(tO + ch * 32, v);
         tc_wait_ld();
@@ -353,8 +301,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
         }
       }
-      if (row_ok && chalf == 0)
-        p.lse[((size_t)b * p.H + h) * p.T + qg] = (lt > 0.f) ? (m * 0.6931471805599453f + logf(lt)) : -INFINITY;
+      if (row_ok) p.lse[((size_t)b * p.H + h) * p.T + qg] = (l > 0.f) ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
     }
   }
 
