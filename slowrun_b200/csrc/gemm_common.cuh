@@ -46,8 +46,9 @@ struct GemmParams {
   int* status;
 };
 
-// Tile index -> (batch, mi, nj). In sym mode rows only hold the tiles that touch the upper triangle.
-template <int BN>
+// Tile index -> (batch, mi, nj). In sym mode rows only hold the tiles that touch the upper triangle. TM = tile height
+// (128 for one CTA, 256 for a CTA pair).
+template <int BN, int TM = BM>
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& b, int& mi, int& nj) {
   if (!p.sym) {
     const int per_batch = p.tiles_m * p.tiles_n;
@@ -64,12 +65,12 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     nj = tt / gm;
   } else {
     int per_batch = 0;
-    for (int r = 0; r < p.tiles_m; ++r) per_batch += p.tiles_n - (r * BM) / BN;
+    for (int r = 0; r < p.tiles_m; ++r) per_batch += p.tiles_n - (r * TM) / BN;
     b = tile / per_batch;
     int t = tile - b * per_batch;
     mi = 0;
     while (true) {
-      const int first = (mi * BM) / BN;
+      const int first = (mi * TM) / BN;
       const int cnt = p.tiles_n - first;
       if (t < cnt) {
         nj = first + t;
@@ -152,15 +153,15 @@ struct WorkIter {
   }
 };
 
-__device__ __forceinline__ bool sym_tile_skipped(int r, int c, int bn) {
-  // the tile that would own element (r, c): mi = r / BM, nj = c / bn; skipped iff it lies below the diagonal band
-  const int mi = r / BM, nj = c / bn;
-  return nj * bn + bn <= mi * BM;
+__device__ __forceinline__ bool sym_tile_skipped(int r, int c, int bn, int tm) {
+  // the tile that would own element (r, c): mi = r / tm, nj = c / bn; skipped iff it lies below the diagonal band
+  const int mi = r / tm, nj = c / bn;
+  return nj * bn + bn <= mi * tm;
 }
 
 
 // One 32-column chunk of one output row: f[] holds alpha * accumulator for columns c0..c0+31 of row r.
-template <int BN>
+template <int BN, int TM = BM>
 __device__ __forceinline__ void epilogue_store(const GemmParams& p, float (&f)[32], int r, int c0, bool partial,
                                                uint8_t* cbase, const uint8_t* cinbase) {
   const bool full = (c0 + 32 <= p.N);
@@ -244,7 +245,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, float (&f)[3
     // store instruction writes 32 consecutive elements of one output row.
     for (int j = 0; j < 32; ++j) {
       const int c = c0 + j;
-      if (c < p.N && c > r && sym_tile_skipped(c, r, BN)) {
+      if (c < p.N && c > r && sym_tile_skipped(c, r, BN, TM)) {
         if (p.c_fp32)
           reinterpret_cast<float*>(cbase)[(size_t)c * p.ldc + r] = f[j];
         else

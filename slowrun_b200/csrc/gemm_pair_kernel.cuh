@@ -125,7 +125,7 @@ struct EpiStore {
   template <int BN>
   static __device__ __forceinline__ void chunk(Row&, const GemmParams& p, float (&f)[32], int r, int c0, bool partial,
                                                uint8_t* cbase, const uint8_t* cinbase) {
-    epilogue_store<BN>(p, f, r, c0, partial, cbase, cinbase);
+    epilogue_store<BN, PM>(p, f, r, c0, partial, cbase, cinbase);
   }
   static __device__ __forceinline__ void end(Row&, const GemmParams&, int, bool, int) {}
 };
@@ -191,7 +191,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr uint32_t kBLoadBytes = C_::kBHalf * BK * 2;           // bytes actually loaded for B per CTA (K-major)
       while (ok && wi.next(tile, kb0, kb1, partial)) {
         int b, mi, nj;
-        tile_coords<BN>(p, tile, b, mi, nj);
+        tile_coords<BN, PM>(p, tile, b, mi, nj);
         const int m0 = mi * PM + (int)rank * BM;
         const int n0 = nj * BN + wi.n_off + (int)rank * (wi.n_w / 2);   // a column slice loads the same boxes, uses fewer rows
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -281,7 +281,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t tempty0 = map_to_cta(smem_u32(&tempty_bar[0]), 0);
     for (; ok && wi.next(tile, kb0, kb1, partial); ++local) {
       int b, mi, nj;
-      tile_coords<BN>(p, tile, b, mi, nj);
+      tile_coords<BN, PM>(p, tile, b, mi, nj);
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, 300);
@@ -343,6 +343,11 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int
   p.tiles_m = (p.M + PM - 1) / PM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
+  if (p.sym) {   // only the tiles that touch the upper triangle; the others are filled by mirrored stores
+    int per_batch = 0;
+    for (int r = 0; r < p.tiles_m; ++r) per_batch += p.tiles_n - (r * PM) / BN;
+    p.num_tiles = per_batch * p.batch;
+  }
   int pairs = num_sms() / 2;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
   if (pairs < 1) pairs = 1;
@@ -356,7 +361,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int
     // last, partial wave: when at most half of the pairs would have a tile, cut those tiles into two 128-wide
     // column slices so that the wave takes half as long
     const int rem = p.num_tiles % pairs;
-    if (allow_tail_split && BN == 256 && rem > 0 && 2 * rem <= pairs) p.tail_split = 2;
+    if (allow_tail_split && !p.sym && BN == 256 && rem > 0 && 2 * rem <= pairs) p.tail_split = 2;
     if (p.num_tiles < pairs) pairs = p.num_tiles * p.tail_split;
   }
   if (pairs <= 0) return 0;

@@ -247,7 +247,7 @@ extern "C" int sr_gemm_bf16_pair(const void* A, const void* B, void* C, const vo
                                  long long lda, long long ldb, long long ldc, long long ldcin, long long strideA,
                                  long long strideB, long long strideC, long long strideCin, int a_mn, int b_mn,
                                  int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr,
-                                 const float* row_scale, int splitk, int bn, int max_ctas, int* status,
+                                 const float* row_scale, int sym, int splitk, int bn, int max_ctas, int* status,
                                  cudaStream_t stream);
 
 // Process-wide handle of the driver's tensor-map encoder (see gemm_common.cuh). Resolved on first use and by
@@ -300,8 +300,8 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   // accumulate-into fp32 output (weight gradients): balance the k-loop over all SMs instead of whole tiles
   p.splitk = (c_fp32 && Cin == C && beta == 1.0f && !sym && ldcin == ldc && strideCin == strideC) ? 1 : 0;
   if (bn < 0) { p.splitk = 0; bn = -bn; }   // negative bn: caller forces the plain tile schedule
-  // CTA pairs (256-row tiles over 74 pairs) for everything but symmetric outputs and single-tile-high problems
-  const bool use_pair = g_pair_mode && !sym && M > BM;
+  // CTA pairs (256-row tiles over 74 pairs) for everything but single-tile-high problems
+  const bool use_pair = g_pair_mode && M > BM;
   const int rows = use_pair ? 2 * BM : BM;
   const int workers = use_pair ? num_sms() / 2 : num_sms();
   if (bn == 0 && p.splitk) bn = 256;
@@ -319,7 +319,7 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
       const long long tn = (N + w - 1) / w;
       if (!sym) return tm * tn;
       long long t = 0;
-      for (long long r = 0; r < tm; ++r) t += tn - (r * BM) / w;
+      for (long long r = 0; r < tm; ++r) t += tn - (r * rows) / w;
       return t;
     };
     const double eff256 = eff(tiles_of(256) * batch, use_pair);
@@ -335,7 +335,7 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   if (bn != 128 && bn != 160 && bn != 256) return -7;
   if (use_pair && !(bn == 160 && b_mn))
     return sr_gemm_bf16_pair(A, B, C, Cin, M, N, K, batch, lda, ldb, ldc, ldcin, strideA, strideB, strideC, strideCin,
-                             a_mn, b_mn, c_fp32, cin_fp32, alpha, beta, alpha_ptr, row_scale, p.splitk, bn, max_ctas,
+                             a_mn, b_mn, c_fp32, cin_fp32, alpha, beta, alpha_ptr, row_scale, sym, p.splitk, bn, max_ctas,
                              status, stream);
   CUtensorMap ma, mb;
   int rc;

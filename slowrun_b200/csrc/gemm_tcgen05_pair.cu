@@ -3,18 +3,20 @@
 // the training step) and for fp8 operands (K-major e4m3 / e5m2, fp32 accumulation; the reference reaches cuBLASLt
 // through torch._scaled_mm for these, tiny/cuda_kernels.py:345-352).
 //
-// Same contract as the single-CTA kernel (gemm_tcgen05.cu) except: no symmetric-output mode.
+// Same contract as the single-CTA kernel (gemm_tcgen05.cu), symmetric-output mode included (256-row tiles that touch the
+// upper triangle are computed, the rest is filled by mirrored stores).
 #include "gemm_pair_kernel.cuh"
 
-// CTA-pair GEMM; arguments as sr_gemm_bf16 (gemm_tcgen05.cu) without `sym`. bn in {128, 160, 256} (160 only with a
+// CTA-pair GEMM; arguments as sr_gemm_bf16 (gemm_tcgen05.cu). bn in {128, 160, 256} (160 only with a
 // K-major B), already chosen by the caller. Returns 0 on successful launch.
 extern "C" int sr_gemm_bf16_pair(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                                  long long lda, long long ldb, long long ldc, long long ldcin, long long strideA,
                                  long long strideB, long long strideC, long long strideCin, int a_mn, int b_mn,
                                  int c_fp32, int cin_fp32, float alpha, float beta, const float* alpha_ptr,
-                                 const float* row_scale, int splitk, int bn, int max_ctas, int* status,
+                                 const float* row_scale, int sym, int splitk, int bn, int max_ctas, int* status,
                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if (sym && (M != N || bn == 160)) return -6;
   if (bn != 128 && bn != 160 && bn != 256) return -7;
   if (bn == 160 && b_mn) return -7;
   GemmParams p{};
@@ -22,8 +24,8 @@ extern "C" int sr_gemm_bf16_pair(const void* A, const void* B, void* C, const vo
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.C = C; p.ldc = ldc; p.strideC = strideC; p.c_fp32 = c_fp32;
   p.Cin = Cin; p.ldcin = ldcin; p.strideCin = strideCin; p.cin_fp32 = cin_fp32;
-  p.alpha = alpha; p.beta = beta; p.alpha_ptr = alpha_ptr; p.row_scale = row_scale; p.sym = 0; p.status = status;
-  p.splitk = splitk;
+  p.alpha = alpha; p.beta = beta; p.alpha_ptr = alpha_ptr; p.row_scale = row_scale; p.sym = sym; p.status = status;
+  p.splitk = sym ? 0 : splitk;
   CUtensorMap ma, mb;
   int rc;
   if (!a_mn) rc = encode_bf16_map(&ma, A, K, M, batch, lda, strideA, BK, BM);

@@ -78,7 +78,7 @@ def test_gemm_pair_and_single_cta_kernels(pair, M, N, K, a_mn, b_mn, bn):
     _close(out, gemm_reference(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32))
 
 
-@pytest.mark.parametrize("n,g,k,bn", [(3, 768, 512, 0), (2, 640, 256, 128), (1, 2560, 1024, 0)])
+@pytest.mark.parametrize("n,g,k,bn", [(3, 768, 512, 0), (2, 640, 256, 128), (1, 2560, 1024, 0), (2, 904, 264, 0), (1, 1288, 320, 256)])
 def test_gemm_symmetric(n, g, k, bn):
     from slowrun_b200.ops.gemm import gemm, gemm_reference
     X = _bf(n, g, k, scale=0.05, seed=3)
