@@ -124,7 +124,7 @@ def parse_args():
 def ensure_corpus(args, rank, world, barrier):
     """Synthetic Zipf corpus in the reference's format, written once per job by rank 0."""
     from slowrun_b200.data.synthetic import write_synthetic_corpus
-    need = (args.warmup + 2 * args.steps + 3) * args.total_batch_size
+    need = (args.warmup + 2 * args.steps + 3 + 12) * args.total_batch_size
     d = os.path.join(tempfile.gettempdir(), f"slowrun_synth_{need}")
     if rank == 0 and not os.path.exists(os.path.join(d, "fineweb_train.pt")):
         write_synthetic_corpus(d + ".tmp", train_tokens=int(need * 1.02) + 2049 * 64, val_tokens=1_100_000)
@@ -191,6 +191,10 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
+        trainer.train_step(sync=True)
+    # On more than one GPU the optimizer measures its step formulations during its first steps and then keeps the
+    # fastest; the timed region below must see the kept one, so warm up until that choice is made.
+    while getattr(trainer.optimizer, "tuning_steps_left", 0) > 0:
         trainer.train_step(sync=True)
     # ---------------------------------------------------------------- device-timed region
     sampler = ClockSampler(physical_gpu_index(info.local_rank))

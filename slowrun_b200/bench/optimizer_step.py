@@ -85,8 +85,9 @@ def main():
         res[k] = timed(o)
     if fused is not None:
         o = opts["fused"]
-        o.mode = "auto"                      # six measuring steps, then the fastest formulation
-        for _ in range(6):
+        o.mode, o.overlap = "auto", "auto"   # measuring steps, then the fastest formulation
+        o.__dict__.pop("_tune", None)
+        while o.tuning_steps_left > 0:
             o.step()
         res["auto"] = timed(o)
     _lib.check_status()

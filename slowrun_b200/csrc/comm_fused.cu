@@ -12,6 +12,11 @@
 //   muon_apply_multi      all-gather of the orthogonalised update fused with the cautious-weight-decay apply: every
 //                         rank reads each owner's bf16 update chunk in place and updates its own fp32 replica and
 //                         bf16 shadow (reference: all_gather_into_tensor of fp32 parameters + copy, train.py:742-760)
+//   bcast_multi           the other form of that all-gather, for buffers with a multicast mapping: the owner pushes its
+//                         bf16 update chunk with multimem.st (one store, replicated by the switch into every rank's
+//                         copy of the gathered buffer); after the barrier every rank applies from its own memory.
+//                         Stores need no round trip, so the transfer is bound by the links and not by the number of
+//                         loads an SM can keep in flight.
 //   reduce_multi          out = sum over ranks of src_r[offset : offset+n]  (row-slice reduce-scatter for the AdamW
 //                         parameters, and the one-shot all-reduce of the packed small-parameter gradients)
 //   gather_multi          pull every other rank's slice of a sharded parameter into the local replica
@@ -326,6 +331,18 @@ __global__ void muon_apply_multi8_kernel(float* __restrict__ P, PtrTable U, long
   }
 }
 
+// Owner -> all ranks: src (this rank's memory, n 16-byte vectors) is written through the multicast address `mc_dst`, so
+// the same bytes land at the same offset of the symmetric buffer on every rank, this one included.
+__global__ void bcast_multi_kernel(const uint4* __restrict__ src, uint4* mc_dst, long n, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_dst + i), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+  }
+}
+
 template <bool BF16>
 __global__ void reduce_multi_kernel(PtrTable src, int world, long offset, float* __restrict__ out, long n,
                                     const int* __restrict__ status) {
@@ -460,6 +477,22 @@ extern "C" int sr_muon_apply_multi(float* P, const unsigned long long* u_ptrs, i
     muon_apply_multi8_kernel<<<grid_for(total / 16, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total, status);
   else
     muon_apply_multi_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, t, chunk_elems, reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total, status);
+  return rc();
+}
+
+// Pushes `bytes` bytes (a multiple of 16, 16-byte aligned on both sides) from `src` into every rank's copy of a
+// symmetric buffer through its multicast address `mc_dst`. `max_ctas` > 0 caps the grid (to leave SMs to a GEMM running
+// beside it). The data is visible on the peers after the next peer barrier on the same stream.
+extern "C" int sr_bcast_multi(const void* src, void* mc_dst, long bytes, int max_ctas, const int* status, cudaStream_t s) {
+  if (bytes <= 0) return 0;
+  if (bytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(mc_dst) & 15) || mc_dst == nullptr)
+    return -2;
+  const long n = bytes / 16;
+  long grid = (n + kThreads - 1) / kThreads;
+  const long cap = max_ctas > 0 ? max_ctas : 4L * sm_count();
+  if (grid > cap) grid = cap;
+  bcast_multi_kernel<<<(unsigned)grid, kThreads, 0, s>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(mc_dst), n,
+                                                         status);
   return rc();
 }
 

@@ -162,7 +162,10 @@ __global__ void muon_scale_update_kernel(const __nv_bfloat16* __restrict__ X, co
 
 // Cautious weight decay + apply:  P -= bf16(lr*u) + lrwd * P * [u*P >= 0];  shadow = bf16(P)
 __global__ void muon_apply_kernel(float* __restrict__ P, const __nv_bfloat16* __restrict__ U,
-                                  __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total) {
+                                  __nv_bfloat16* __restrict__ shadow, float lr_b, float lrwd_b, long total,
+                                  const int* __restrict__ status) {
+  // multi-GPU callers pass the status word: after a peer wait that gave up, the step must leave the parameters alone
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += (long)gridDim.x * blockDim.x * 4) {
     float4 p = *reinterpret_cast<float4*>(P + i);
     const float2 u0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(U + i));
@@ -288,7 +291,16 @@ extern "C" int sr_muon_apply(float* P, const void* U, void* shadow, long total, 
                              cudaStream_t s) {
   if (total <= 0) return 0;
   if (total % 4) return -2;
-  muon_apply_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, reinterpret_cast<const __nv_bfloat16*>(U), reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total);
+  muon_apply_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, reinterpret_cast<const __nv_bfloat16*>(U), reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total, nullptr);
+  return rc();
+}
+
+// Same, for a step whose update arrived from other ranks: does nothing when the status word is set.
+extern "C" int sr_muon_apply_status(float* P, const void* U, void* shadow, long total, float lr_b, float lrwd_b,
+                                    const int* status, cudaStream_t s) {
+  if (total <= 0) return 0;
+  if (total % 4) return -2;
+  muon_apply_kernel<<<grid_for(total / 4, kThreads), kThreads, 0, s>>>(P, reinterpret_cast<const __nv_bfloat16*>(U), reinterpret_cast<__nv_bfloat16*>(shadow), lr_b, lrwd_b, total, status);
   return rc();
 }
 

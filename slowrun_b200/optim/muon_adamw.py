@@ -16,6 +16,7 @@ What is organised differently:
 """
 from __future__ import annotations
 
+import os
 from typing import List
 
 import torch
@@ -149,6 +150,9 @@ class ShardedMuonAdamW:
         fp32); "fp32": the owners read the fp32 arenas directly. The torch.distributed path always reduces fp32."""
         self.model = model
         self.wire_dtype = wire_dtype
+        # all-gather of the updates by multicast stores (needs a multicast mapping; SLOWRUN_PUSH_UPDATES=0 keeps the pull)
+        self.push_updates = os.environ.get("SLOWRUN_PUSH_UPDATES", "1") != "0"
+        self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count if torch.cuda.is_available() else 0
         self.arena: ParamArena = model.arena
         self.param_groups = param_groups
         self.comm = comm
@@ -177,7 +181,10 @@ class ShardedMuonAdamW:
                           grad_chunk=torch.empty((ga.chunk, r, c), dtype=torch.float32, device=dev) if (W > 1 and not self.fused) else None,
                           U=(self.comm.alloc((ga.chunk, r, c), torch.bfloat16) if (self.fused and ga.W16 is not None)
                              else torch.zeros((ga.chunk, r, c), dtype=torch.bfloat16, device=dev)),
-                          U_all=torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev)
+                          # gathered updates: symmetric on the peer-memory path, so that owners can push their chunk into
+                          # every rank's copy through the multicast address
+                          U_all=(self.comm.alloc((ga.n_pad, r, c), torch.bfloat16) if (self.fused and ga.W16 is not None)
+                                 else torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev))
                           if (W > 1 and not (self.fused and ga.W16 is not None)) else None)
                 if self.fused and ga.W16 is not None and self.wire_dtype == "bf16" and c % 8 == 0:
                     st["G16"] = self.comm.alloc((ga.n_pad, r, c), torch.bfloat16)
@@ -303,6 +310,7 @@ class ShardedMuonAdamW:
 
     # ------------------------------------------------------------------ which formulation of the step: measured
     TUNE_MODES = ("fused", "fused_two_streams", "library")
+    TUNE_WARM, TUNE_TIMED = 2, 2       # per formulation: untimed steps (library collectives set themselves up lazily), timed steps
 
     def _run_mode(self, mode):
         if mode == "library":
@@ -311,10 +319,10 @@ class ShardedMuonAdamW:
         return self._step_fused()
 
     def _step_fused_tuned(self):
-        """`self.mode` is one of TUNE_MODES or "auto" (default). In "auto" the first six steps of the run try the three
-        formulations in turn (one warm-up step and one device-timed step each: peer-memory kernels back to back,
-        peer-memory kernels on two streams, the torch.distributed collectives), the maximum over ranks is compared
-        and the fastest is kept for the rest of the run. All three compute the same update from the same state, so
+        """`self.mode` is one of TUNE_MODES or "auto" (default). In "auto" the first twelve steps of the run try the three
+        formulations in turn (two warm-up steps and two device-timed steps each: peer-memory kernels back to back,
+        peer-memory kernels on two streams, the torch.distributed collectives), the maximum over ranks of the better
+        timed step is compared and the fastest is kept for the rest of the run. All three compute the same update from the same state, so
         switching between steps is harmless. Setting `self.overlap` to True / False (older interface) pins the
         two-stream / one-stream peer-memory order."""
         mode = getattr(self, "mode", "auto")
@@ -326,8 +334,9 @@ class ShardedMuonAdamW:
         if not hasattr(self, "_tune"):
             self._tune = []
         k = len(self._tune)
-        cand = self.TUNE_MODES[k // 2]
-        timed = k % 2 == 1
+        per = self.TUNE_WARM + self.TUNE_TIMED
+        cand = self.TUNE_MODES[k // per]
+        timed = k % per >= self.TUNE_WARM
         if timed:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -335,17 +344,25 @@ class ShardedMuonAdamW:
             self._run_mode(cand)
         finally:
             self.overlap = "auto"
-        ms = 0.0
+        ms = float("inf")
         if timed:
             e1.record()
             e1.synchronize()
             t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float32, device=self.device)
             ms = float(self.comm.all_reduce_max(t).item())
         self._tune.append(ms)
-        if len(self._tune) == 2 * len(self.TUNE_MODES):
-            times = {m: self._tune[2 * i + 1] for i, m in enumerate(self.TUNE_MODES)}
+        if len(self._tune) == per * len(self.TUNE_MODES):
+            times = {m: min(self._tune[per * i:per * (i + 1)]) for i, m in enumerate(self.TUNE_MODES)}
             self.mode = min(times, key=times.get)
             self.tuned = {"ms": times, "mode": self.mode}
+
+    @property
+    def tuning_steps_left(self) -> int:
+        """Optimizer steps until the measured choice among the step formulations is made (0 when nothing is being tuned)."""
+        if not (self.fused and not self._inactive) or getattr(self, "mode", "auto") != "auto" or \
+                getattr(self, "overlap", "auto") != "auto":
+            return 0
+        return (self.TUNE_WARM + self.TUNE_TIMED) * len(self.TUNE_MODES) - len(getattr(self, "_tune", []))
 
     # ------------------------------------------------------------------ pieces of the peer-memory step
     def _fast_groups(self):
@@ -573,12 +590,28 @@ class ShardedMuonAdamW:
             ev_post.record(main)
             with torch.cuda.stream(side):
                 side.wait_event(ev_post)
-                comm.device_barrier()                                                              # B_g
                 lr_b = _bf16(float(g["lr"]) * max(1.0, r / c) ** 0.5)
-                rc = _lib.fn("sr_muon_apply_multi", [cvp, cvp, c_int, c_long, cvp, c_long, c_float, c_float, cvp, cvp])(
-                    ga.P.data_ptr(), ctypes.cast(comm.peer_ptrs(st["U"]), cvp), W, ga.chunk * r * c, ga.W16.data_ptr(),
-                    ga.P.numel(), lr_b, _bf16(lr_b * _bf16(float(g["weight_decay"]))), status_ptr, _lib.stream_ptr())
-                _lib.check_rc(rc, "sr_muon_apply_multi")
+                lrwd_b = _bf16(lr_b * _bf16(float(g["weight_decay"])))
+                mc_all = comm.multicast_ptr(st["U_all"]) if self.push_updates else 0
+                if mc_all:
+                    # all-gather by push: the owner's chunk goes through the switch into every rank's U_all (one
+                    # multimem store per 16 bytes), then every rank applies from its own memory
+                    if n_own > 0:
+                        rc = _lib.fn("sr_bcast_multi", [cvp, cvp, c_long, c_int, cvp, cvp])(
+                            st["U"].data_ptr(), mc_all + rank * ga.chunk * r * c * 2, n_own * r * c * 2,
+                            self.sm_count if side is not main else 0, status_ptr, _lib.stream_ptr())
+                        _lib.check_rc(rc, "sr_bcast_multi")
+                    comm.device_barrier()                                                          # B_g
+                    rc = _lib.fn("sr_muon_apply_status", [cvp, cvp, cvp, c_long, c_float, c_float, cvp, cvp])(
+                        ga.P.data_ptr(), st["U_all"].data_ptr(), ga.W16.data_ptr(), ga.P.numel(), lr_b, lrwd_b, status_ptr,
+                        _lib.stream_ptr())
+                    _lib.check_rc(rc, "sr_muon_apply_status")
+                else:
+                    comm.device_barrier()                                                          # B_g
+                    rc = _lib.fn("sr_muon_apply_multi", [cvp, cvp, c_int, c_long, cvp, c_long, c_float, c_float, cvp, cvp])(
+                        ga.P.data_ptr(), ctypes.cast(comm.peer_ptrs(st["U"]), cvp), W, ga.chunk * r * c, ga.W16.data_ptr(),
+                        ga.P.numel(), lr_b, lrwd_b, status_ptr, _lib.stream_ptr())
+                    _lib.check_rc(rc, "sr_muon_apply_multi")
         # ---- side stream: shape groups without the kernel path (no bf16 shadow), then the AdamW slice gathers
         side.wait_stream(main)
         with torch.cuda.stream(side):
