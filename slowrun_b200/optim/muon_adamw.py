@@ -184,8 +184,7 @@ class ShardedMuonAdamW:
                           # gathered updates: symmetric on the peer-memory path, so that owners can push their chunk into
                           # every rank's copy through the multicast address
                           U_all=(self.comm.alloc((ga.n_pad, r, c), torch.bfloat16) if (self.fused and ga.W16 is not None)
-                                 else torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev))
-                          if (W > 1 and not (self.fused and ga.W16 is not None)) else None)
+                                 else (torch.empty((ga.n_pad, r, c), dtype=torch.bfloat16, device=dev) if W > 1 else None)))
                 if self.fused and ga.W16 is not None and self.wire_dtype == "bf16" and c % 8 == 0:
                     st["G16"] = self.comm.alloc((ga.n_pad, r, c), torch.bfloat16)
                 if self.cuda and ga.W16 is not None:
@@ -265,7 +264,8 @@ class ShardedMuonAdamW:
                 if W > 1 and st["grad_chunk"] is None:      # peer-memory job that runs this path (mode measurement)
                     r_, c_ = ga.shape
                     st["grad_chunk"] = torch.empty((ga.chunk, r_, c_), dtype=torch.float32, device=self.device)
-                    st["U_all"] = torch.empty((ga.n_pad, r_, c_), dtype=torch.bfloat16, device=self.device)
+                    if st["U_all"] is None:
+                        st["U_all"] = torch.empty((ga.n_pad, r_, c_), dtype=torch.bfloat16, device=self.device)
                 st["h"] = comm.reduce_scatter_sum(st["grad_chunk"], ga.G) if W > 1 else None
             else:
                 for p in g["params"]:
