@@ -301,9 +301,9 @@ extern "C" int sr_gemm_bf16(const void* A, const void* B, void* C, const void* C
   // accumulate-into fp32 output (weight gradients): balance the k-loop over all SMs instead of whole tiles
   p.splitk = (c_fp32 && Cin == C && beta == 1.0f && !sym && ldcin == ldc && strideCin == strideC) ? 1 : 0;
   if (bn < 0) { p.splitk = 0; bn = -bn; }   // negative bn: caller forces the plain tile schedule
-  // CTA pairs (256-row tiles over 74 pairs) for everything but single-tile-high problems; symmetric outputs take the
-  // pair kernel when SR_GEMM_SYM_PAIR=1 (read once)
-  static const bool sym_pair = [] { const char* e = getenv("SR_GEMM_SYM_PAIR"); return e != nullptr && e[0] == '1'; }();
+  // CTA pairs (256-row tiles over 74 pairs) for everything but single-tile-high problems; SR_GEMM_SYM_PAIR=0 (read
+  // once) keeps symmetric outputs on the single-CTA kernel
+  static const bool sym_pair = [] { const char* e = getenv("SR_GEMM_SYM_PAIR"); return e == nullptr || e[0] != '0'; }();
   const bool use_pair = g_pair_mode && M > BM && (!sym || sym_pair);
   const int rows = use_pair ? 2 * BM : BM;
   const int workers = use_pair ? num_sms() / 2 : num_sms();
