@@ -23,8 +23,27 @@ from ..config import BOS_ID
 class Corpus:
     """Tokens of a `.pt` corpus file (prepare_data.py format) and its document table."""
 
+    CHUNKED_KEYS = {"chunks", "valid_counts", "batch_size", "sequence_size"}
+    FLAT_KEYS = {"tokens", "doc_starts", "bos_id", "seq_shuffle_seed"}
+
     def __init__(self, filepath):
         data = torch.load(filepath, weights_only=True)
+        self.fixed_rows = None
+        if self.CHUNKED_KEYS.issubset(data):
+            # Legacy pre-chunked files (research/hybrid_attn/train.py:1146-1186): a list of [batch_size, sequence_size]
+            # chunks of which the first valid_counts[i] rows count. The windows are fixed, so there is no document
+            # table and nothing to shuffle but the order of a rank's steps.
+            B, S = int(data["batch_size"]), int(data["sequence_size"])
+            rows = [c.view(B, S)[:int(v)] for c, v in zip(data["chunks"], data["valid_counts"])]
+            self.fixed_rows = torch.cat(rows, 0).to(torch.int32)
+            self.tokens = self.fixed_rows.reshape(-1)
+            self.starts = torch.zeros(1, dtype=torch.int64)
+            self.lens = torch.tensor([self.tokens.numel()], dtype=torch.int64)
+            self.seq_shuffle_seed = 0
+            return
+        if not self.FLAT_KEYS.issubset(data):
+            raise ValueError(f"{filepath} is not a recognized dataset format. Expected flat keys {sorted(self.FLAT_KEYS)} or "
+                             f"chunked keys {sorted(self.CHUNKED_KEYS)}, found [{', '.join(sorted(data.keys()))}].")
         bos_id = int(data["bos_id"])
         if bos_id != BOS_ID:
             raise ValueError(f"corpus was tokenised with bos_id {bos_id}, this loader expects {BOS_ID}")
@@ -78,6 +97,13 @@ class TokenLoader:
         self.device = torch.device(device)
         self.B, self.T, self.seq_size = B, T, T + 1
         self.doc_shuffle = doc_shuffle
+        if self.corpus.fixed_rows is not None:
+            if self.corpus.fixed_rows.size(1) != self.seq_size:
+                raise ValueError(f"Data sequence_size {self.corpus.fixed_rows.size(1)} != T+1={T + 1}")
+            if doc_shuffle and int(os.environ.get("RANK", 0)) == 0:
+                print(f"Warning: {filepath} is a legacy chunked dataset; document shuffling is unavailable until the data "
+                      "is regenerated with prepare_data.py.")
+            self.doc_shuffle = False
         self.epoch = 1
         self.order = torch.arange(self.corpus.num_docs)
         self._cuda = self.device.type == "cuda"
@@ -88,6 +114,8 @@ class TokenLoader:
 
     # ------------------------------------------------------------------ what this rank reads in the current epoch
     def _window_permutation(self, num_seqs):
+        if self.corpus.fixed_rows is not None:
+            return torch.arange(num_seqs)                   # legacy chunked files: rows are used in file order
         if self.doc_shuffle:
             return torch.randperm(num_seqs, generator=_generator(self.epoch + 1000))
         return torch.from_numpy(np.random.RandomState(self.corpus.seq_shuffle_seed).permutation(num_seqs))

@@ -82,3 +82,31 @@ def test_loader_state_round_trip(corpus):
         xa, ya, ea = next(a)
         xb, yb, eb = next(b)
         assert ea == eb and torch.equal(xa, xb) and torch.equal(ya, yb)
+
+
+def test_legacy_chunked_dataset(tmp_path):
+    """research/hybrid_attn/train.py:1146-1186, 1208-1216, 1246-1250: rows of the pre-chunked file in file order, dealt
+    [step, rank, B]; later epochs only permute the order of a rank's steps (seed = epoch)."""
+    import torch
+    from slowrun_b200.data.loader import TokenLoader
+    B_file, S = 6, 9
+    g = torch.Generator().manual_seed(0)
+    chunks = [torch.randint(0, 1000, (B_file * S,), generator=g, dtype=torch.int32) for _ in range(4)]
+    valid = [6, 6, 4, 6]
+    path = str(tmp_path / "legacy.pt")
+    torch.save({"chunks": chunks, "valid_counts": valid, "batch_size": B_file, "sequence_size": S}, path)
+    rows = torch.cat([c.view(B_file, S)[:v] for c, v in zip(chunks, valid)], 0).long()      # 22 rows
+    for rank in (0, 1):
+        ld = TokenLoader(path, 2, S - 1, device="cpu", doc_shuffle=True, rank=rank, world_size=2)
+        assert ld.doc_shuffle is False and ld.num_steps == 5 and ld.total_tokens == 20 * (S - 1)
+        mine = rows[:20].view(5, 2, 2, S)[:, rank]
+        for s_ in range(5):
+            x, y, ep = next(ld)
+            assert ep == 1 and torch.equal(x, mine[s_][:, :-1]) and torch.equal(y, mine[s_][:, 1:])
+        perm = torch.randperm(5, generator=torch.Generator().manual_seed(2))
+        for s_ in range(5):
+            x, y, ep = next(ld)
+            assert ep == 2 and torch.equal(x, mine[perm[s_]][:, :-1])
+    with pytest.raises(ValueError, match="not a recognized dataset format"):
+        torch.save({"foo": torch.zeros(3)}, str(tmp_path / "bad.pt"))
+        TokenLoader(str(tmp_path / "bad.pt"), 2, 8, device="cpu")
