@@ -37,6 +37,7 @@ class FusedComm(TorchComm):
         self._pg = group if group is not None else dist.group.WORLD
         self.device = torch.device("cuda", torch.cuda.current_device())
         self._allocs = []          # (base address, bytes, handle)
+        self._guards = []          # (byte buffer, payload bytes, shape, dtype) of every allocation
         self._ptr_cache = {}
         self.epoch = 0
         # How long a device-side barrier waits for each peer before it gives up and reports through the status word.
@@ -52,13 +53,37 @@ class FusedComm(TorchComm):
         dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------ symmetric allocation
+    GUARD_BYTES = 256
+    GUARD_PATTERN = 0x5A
+
     def alloc(self, shape, dtype) -> torch.Tensor:
-        """Zero-filled tensor mapped by every rank (collective call: all ranks must allocate in the same order)."""
-        t = self._symm.empty(tuple(shape), dtype=dtype, device=self.device)
-        t.zero_()
-        hdl = self._symm.rendezvous(t, self._pg)
-        self._allocs.append((t.data_ptr(), t.numel() * t.element_size(), hdl))
-        return t
+        """Zero-filled tensor mapped by every rank (collective call: all ranks must allocate in the same order). Every
+        allocation ends in a guard region filled with a byte pattern: peers write into these buffers with plain and
+        multicast stores, and a store that ran past the end of a buffer would otherwise land in whatever the allocator put
+        next. `check_guards()` verifies them."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        item = torch.empty((), dtype=dtype).element_size()
+        payload = (n * item + 15) // 16 * 16
+        raw = self._symm.empty((payload + self.GUARD_BYTES,), dtype=torch.uint8, device=self.device)
+        raw.zero_()
+        raw[payload:] = self.GUARD_PATTERN
+        hdl = self._symm.rendezvous(raw, self._pg)
+        self._allocs.append((raw.data_ptr(), payload + self.GUARD_BYTES, hdl))
+        self._guards.append((raw, payload, tuple(int(d) for d in shape), dtype))
+        return raw[:n * item].view(dtype).view(tuple(int(d) for d in shape))
+
+    def check_guards(self) -> int:
+        """Synchronising check of the guard region behind every symmetric allocation of this rank; raises naming the
+        buffer whose guard was overwritten. Returns the number of buffers checked."""
+        for raw, payload, shape, dtype in self._guards:
+            g = raw[payload:]
+            if not bool((g == self.GUARD_PATTERN).all()):
+                first = int((g != self.GUARD_PATTERN).nonzero()[0])
+                raise AssertionError(f"rank {self.rank}: guard behind the symmetric buffer {shape} {dtype} was overwritten "
+                                     f"(first damaged byte at +{first})")
+        return len(self._guards)
 
     def peer_ptrs(self, t: torch.Tensor):
         """ctypes array with the address of `t` (or of a view into an allocated tensor) on every rank."""

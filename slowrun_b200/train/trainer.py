@@ -26,6 +26,7 @@ from ..optim.groups import build_param_groups
 from ..optim.muon_adamw import ShardedMuonAdamW
 from ..ops import _lib
 from ..parallel.comm import DistInfo, TorchComm, init_distributed, print0
+from ..utils.debug import nvtx_range
 from ..utils.logging import RunLogger
 from .checkpoint import (CheckpointRing, WeightEMA, average_checkpoints_into, full_state_exists, load_full_state,
                          recency_weights, save_full_state)
@@ -168,6 +169,7 @@ class Trainer:
             # last micro-batch on the peer-memory path: run eagerly so that each layer's gradients can be released to
             # their owners (and pulled by them on a side stream) while the backward pass is still walking down
             overlapped = (self.overlap_backward and micro == self.grad_accum - 1 and self.optimizer.begin_backward_overlap())
+            rng = nvtx_range("micro_step").__enter__()
             graph = self._graphs.get(key) if (self.use_graphs and not overlapped) else None
             if graph is None and self.use_graphs and not overlapped and self._eager_micro >= 3:
                 graph = self._capture(key, tiny, n_iter, mtp_w)
@@ -188,11 +190,13 @@ class Trainer:
                 self._eager_micro += 1
                 if overlapped:
                     self.optimizer.finish_backward_overlap()
+            rng.__exit__(None, None, None)
             self.x, self.y, epoch = next(self.train_loader)
         self._pending_epoch = epoch
         self.before_optimizer_step()
         self.sched.apply(self.param_groups, self.step)
-        self.optimizer.step()
+        with nvtx_range("optimizer_step"):
+            self.optimizer.step()
         if getattr(self.optimizer, "fused", False):
             # a device-side barrier that gave up leaves the status word set and every consumer kernel of the step
             # returned without writing: stop here, before the gradients are cleared, instead of training on

@@ -139,3 +139,25 @@ def repeat_check(fn: Callable[[], object], times: int = 3, atol: float = 0.0):
                 diff = (a.float() - b.float()).abs().max().item()
                 raise AssertionError(f"run {i} differs from run 0 in output {j} by {diff:g} > {atol:g}")
     return first
+
+
+class nvtx_range:
+    """`with nvtx_range("name"):` marks a range for timeline tools when SLOWRUN_NVTX=1 and CUDA is present; otherwise it
+    does nothing (and costs nothing: the environment is read once)."""
+    _on = None
+
+    def __init__(self, name: str):
+        if nvtx_range._on is None:
+            import os
+            nvtx_range._on = os.environ.get("SLOWRUN_NVTX", "0") == "1" and torch.cuda.is_available()
+        self.name = name
+
+    def __enter__(self):
+        if nvtx_range._on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if nvtx_range._on:
+            torch.cuda.nvtx.range_pop()
+        return False

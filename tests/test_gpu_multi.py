@@ -113,6 +113,8 @@ def _run_variant(results, name, var, info, cfg, m, fused_comm, data, rank, world
         _lib.check_status()
         model.zero_grad_arena()
         losses.append(float(loss.detach()))
+    if var is not None:
+        assert fused_comm.check_guards() > 10        # no kernel of any rank wrote past the end of a symmetric buffer
     results[name] = {"losses": losses, "params": {n: p.detach().float().cpu() for n, p in model.named_parameters()}}
 
 
