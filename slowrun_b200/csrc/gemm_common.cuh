@@ -49,7 +49,7 @@ struct GemmParams {
 // Tile index -> (batch, mi, nj). In sym mode rows only hold the tiles that touch the upper triangle. TM = tile height
 // (128 for one CTA, 256 for a CTA pair).
 template <int BN, int TM = BM>
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& b, int& mi, int& nj) {
+__host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& b, int& mi, int& nj) {
   if (!p.sym) {
     const int per_batch = p.tiles_m * p.tiles_n;
     b = tile / per_batch;
@@ -82,6 +82,8 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   }
 }
 
+// (init/next, tile_coords and sym_tile_skipped also compile for the host: tests/native/sched_model_test.cu replays them for
+// every worker of many problem shapes and checks that the work is covered exactly once.)
 // Work items of one CTA. Full waves of tiles are strided over the grid (concurrent CTAs work on neighbouring tiles, which
 // keeps their operand panels in L2). In splitk mode the tiles of the last, partial wave are cut along K instead: every
 // CTA gets an equal share of their (tile, k-block) units and adds its partial tile with reductions.
@@ -93,7 +95,7 @@ struct WorkIter {
   int n_off, n_w;       // column slice of the current item within its tile (set by next())
   int bn_full;
   // worker / nworkers: this CTA (or CTA pair) and how many of them share the problem
-  __device__ __forceinline__ void init(const GemmParams& p, int nkb, int worker, int nworkers, int bn) {
+  __host__ __device__ __forceinline__ void init(const GemmParams& p, int nkb, int worker, int nworkers, int bn) {
     num_kb = nkb;
     stride = nworkers;
     t = worker;
@@ -121,7 +123,7 @@ struct WorkIter {
     }
   }
   // partial = true: the item covers only part of K (or shares its tile with other CTAs) and must be added atomically
-  __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1, bool& partial) {
+  __host__ __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1, bool& partial) {
     if (t < full_tiles) {
       tile = t;
       kb0 = 0;
@@ -153,7 +155,7 @@ struct WorkIter {
   }
 };
 
-__device__ __forceinline__ bool sym_tile_skipped(int r, int c, int bn, int tm) {
+__host__ __device__ __forceinline__ bool sym_tile_skipped(int r, int c, int bn, int tm) {
   // the tile that would own element (r, c): mi = r / tm, nj = c / bn; skipped iff it lies below the diagonal band
   const int mi = r / tm, nj = c / bn;
   return nj * bn + bn <= mi * tm;
