@@ -148,3 +148,45 @@ def test_fit_writes_resume_files_and_picks_them_up(corpus, tmp_path):
     tr = Trainer(cfg, _info(), quiet=True)
     res = tr.fit()
     assert res["steps"] == 6 and tr.step == 6
+
+
+def test_resume_replays_window_stages_and_restores_the_ema(corpus, tmp_path):
+    """A run stopped in the second window stage of the two-hour track comes back with the long window, the rescaled rotary
+    table and the softmax scale of that stage; a tiny-track run comes back with its weight EMA."""
+    from slowrun_b200.train.trainer import Trainer
+    cfg = _shrink(track_defaults("two_hour"), corpus, tmp_path / "a")
+    cfg.num_epochs, cfg.swa_last_epochs, cfg.logit_avg, cfg.dupe_start_epoch = 3, 0, 0, 99
+    cfg.window_schedule = "1-1:16,32;2-3:32,64"
+    cfg.max_steps, cfg.save_every, cfg.resume = 1000, 0, None
+    tr = Trainer(cfg, _info(), quiet=True)
+    # run into epoch 2 through fit's own epoch handling
+    cfg.max_steps = tr.sched.steps_per_epoch and int(tr.sched.steps_per_epoch) + 2
+    tr.fit()
+    assert tr.current_epoch == 2 and tr.model.long_window == 64 and tr.model.rotary.yarn_active
+    path = str(tmp_path / "state" / "s")
+    tr.save_state(path)
+    want_cos, want_scale, want_step = tr.model.rotary.cos.clone(), tr.model.rotary.attn_scale, tr.step
+    want_loss = tr.train_step()["loss"]            # the step the resumed run has to reproduce (dropout is on: same RNG stream)
+    cfg2 = _shrink(track_defaults("two_hour"), corpus, tmp_path / "b")
+    cfg2.num_epochs, cfg2.swa_last_epochs, cfg2.logit_avg, cfg2.dupe_start_epoch = 3, 0, 0, 99
+    cfg2.window_schedule = cfg.window_schedule
+    tr2 = Trainer(cfg2, _info(), quiet=True)
+    assert tr2.model.long_window == 32 and not tr2.model.rotary.yarn_active
+    tr2.load_state(path)
+    assert tr2.step == want_step and tr2.current_epoch == 2 and tr2.model.long_window == 64
+    assert tr2.model.rotary.attn_scale == want_scale
+    assert torch.equal(tr2.model.rotary.cos, want_cos)
+    assert tr2.train_step()["loss"] == want_loss
+
+    tcfg = _shrink(track_defaults("tiny"), corpus, tmp_path / "t")
+    tcfg.update_ema_every, tcfg.model.dropout = 1, 0.0
+    tt = Trainer(tcfg, _info(), quiet=True)
+    for _ in range(3):
+        tt.train_step()
+    tt.save_state(str(tmp_path / "state" / "t"))
+    tcfg2 = _shrink(track_defaults("tiny"), corpus, tmp_path / "t2")
+    tcfg2.update_ema_every, tcfg2.model.dropout = 1, 0.0
+    tt2 = Trainer(tcfg2, _info(), quiet=True)
+    tt2.load_state(str(tmp_path / "state" / "t"))
+    assert tt2.ema.updates == tt.ema.updates == 3
+    assert all(torch.equal(a, b) for a, b in zip(tt.ema.ema, tt2.ema.ema))
