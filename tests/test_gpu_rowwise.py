@@ -241,6 +241,7 @@ def test_dropout_masks_have_the_right_statistics_and_never_repeat():
     x = torch.zeros(rows, D, device="cuda", dtype=torch.bfloat16)
     y = torch.ones(rows, D, device="cuda", dtype=torch.bfloat16)
     st = ops.dropout_state("cuda")
+    st.fill_(0x1234ABCD5)            # a fixed step counter: the checks below are then the same numbers on every run
 
     def mask(seed):
         out = torch.empty_like(x)
